@@ -1,0 +1,202 @@
+/*
+ * minuet_b200 -- C ABI of the B200-native sparse-convolution hot path.
+ *
+ * One shared library (libminuet_b200.so), plain pointers and sizes, no torch
+ * types.  Every entry point that touches the GPU only ENQUEUES work on the
+ * caller's stream and returns; it never allocates, frees or synchronises, and
+ * keeps no pointer after it returns.  Outputs and scratch ("workspace") are
+ * allocated by the caller.  Host-side planners are pure functions.
+ *
+ * Every function returns an mn_status; on failure mn_last_error() gives a
+ * thread-local message.  Each declaration cites the entry of the reference's
+ * pybind11 module (minuet.nn.functional._C) that it stands in for.
+ *
+ * Conventions
+ *   coordinates  int32 [n, ndim] row-major, ndim in 1..4, sorted cloud-major
+ *                then lexicographically (dimension 0 most significant)
+ *   batch_dims   int64 [num_clouds + 1] device prefix offsets, or NULL for one
+ *                cloud (num_clouds is then ignored)
+ *   kernel map   int32 [O, T] row-major; -1 marks "no source"
+ *   masks        int32 [O, S] and [O, T]
+ *   stream       a cudaStream_t passed as void*
+ */
+#ifndef MINUET_B200_H_
+#define MINUET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  MN_OK = 0,
+  MN_ERR_BAD_ARG = 1,     /* shape / pointer / range check failed            */
+  MN_ERR_UNSUPPORTED = 2, /* legal in the reference, not implemented here    */
+  MN_ERR_WORKSPACE = 3,   /* workspace smaller than mn_*_workspace_bytes     */
+  MN_ERR_CUDA = 4,        /* a CUDA runtime call or launch failed            */
+  MN_ERR_DEVICE = 5       /* a kernel reported a bounded-wait timeout        */
+} mn_status;
+
+typedef enum { MN_F32 = 0, MN_F16 = 1, MN_BF16 = 2 } mn_dtype;
+
+#define MN_MAX_NDIM 4
+#define MN_MAX_OFFSETS 128
+
+/* How coordinates are packed into one 64-bit sort/search key:
+ * key = cloud << cloud_shift | sum_k (c[k] - base[k]) << shift[k].
+ * A plain host struct; pass it by pointer (host memory). */
+typedef struct {
+  int32_t ndim;
+  int32_t total_bits;       /* bits used by the key, <= 63                    */
+  int32_t margin;           /* offsets up to +-margin never leave a field     */
+  int32_t cloud_shift;
+  int32_t cloud_bits;
+  int32_t shift[MN_MAX_NDIM];
+  int32_t bits[MN_MAX_NDIM];
+  int64_t base[MN_MAX_NDIM];   /* coordinate that maps to field value 0       */
+  int64_t extent[MN_MAX_NDIM]; /* largest legal field value                   */
+} mn_keyspec;
+
+const char *mn_last_error(void);
+int mn_version(void);
+
+/* ---- Map step ------------------------------------------------------------ */
+
+/* Bounding box of up to two coordinate arrays (b may be NULL):
+ * minmax_dev[0..3] = per-dimension min, [4..7] = max (int32, device).
+ * Stands in for GetCoordinatesMinMax, the first step of
+ * _C.cuda_arg_sort_coordinates (csrc/minuet/cuda/functions/arg_sort_coodrinates.cu:31-85). */
+mn_status mn_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,
+                  int ndim, int32_t *minmax_dev, void *ws, size_t ws_bytes,
+                  void *stream);
+
+/* Host: derive the key layout from a bounding box (host copy of mn_bbox's
+ * output), the number of clouds and the largest |offset| that will be added to
+ * a coordinate.  Plays the role of IsFlattenable + the flattening strides
+ * (arg_sort_coodrinates.cu:220-244, kernels/flatten_coordinates.cuh:23-38).
+ * MN_ERR_UNSUPPORTED when the box does not fit 63 bits. */
+mn_status mn_keyspec_make(const int32_t *minmax_host, int ndim,
+                          int64_t num_clouds, int32_t margin, mn_keyspec *spec);
+
+/* Pack coordinates into keys.  tstride (host, may be NULL) floors every
+ * coordinate to a multiple of tstride[k] first, as
+ * KernelMapCache.get_target_coordinates does (minuet/nn/convolutions.py:85-87).
+ * status_dev (int32, device, caller-zeroed) gets bit 1 set when a coordinate
+ * falls outside the spec's box. */
+mn_status mn_pack_keys(const int32_t *coords, int64_t n, int ndim,
+                       const int64_t *batch_dims, int64_t num_clouds,
+                       const int32_t *tstride, const mn_keyspec *spec,
+                       uint64_t *keys_out, int32_t *status_dev, void *stream);
+
+/* _C.cuda_arg_sort_coordinates / _C.cuda_multi_arg_sort_coordinates
+ * (csrc/minuet/torch/cuda_arg_sort_coordinates.cu:8-66): stable arg-sort,
+ * cloud-major then lexicographic.  index_out int64 [n]. */
+mn_status mn_arg_sort_coordinates(const int32_t *coords, int64_t n, int ndim,
+                                  const int64_t *batch_dims, int64_t num_clouds,
+                                  const mn_keyspec *spec, int64_t *index_out,
+                                  int32_t *status_dev, void *ws, size_t ws_bytes,
+                                  void *stream);
+
+/* _C.cuda_unique_coordinates / _C.cuda_multi_unique_coordinates
+ * (csrc/minuet/torch/cuda_unique_coordinates.cu:8-81) on SORTED coordinates:
+ * indices_out int64 [n+1] (indices[i+1] = #unique among rows 0..i),
+ * unique_out int32 [n, ndim] (first indices[n] rows valid). */
+mn_status mn_unique_coordinates(const int32_t *coords, int64_t n, int ndim,
+                                const int64_t *batch_dims, int64_t num_clouds,
+                                int32_t *unique_out, int64_t *indices_out,
+                                void *ws, size_t ws_bytes, void *stream);
+
+/* Fused target-coordinate build of a strided convolution
+ * (KernelMapCache.get_target_coordinates, minuet/nn/convolutions.py:85-96):
+ * floor to the target stride, sort, unique.  Outputs: unique_out int32
+ * [n, ndim], keys_out uint64 [n] (sorted unique keys), out_batch_dims int64
+ * [num_clouds+1] (only when batch_dims != NULL), count_dev int64 [1]. */
+mn_status mn_downsample_coordinates(const int32_t *coords, int64_t n, int ndim,
+                                    const int64_t *batch_dims, int64_t num_clouds,
+                                    const int32_t *tstride, const mn_keyspec *spec,
+                                    int32_t *unique_out, uint64_t *keys_out,
+                                    int64_t *out_batch_dims, int64_t *count_dev,
+                                    int32_t *status_dev, void *ws, size_t ws_bytes,
+                                    void *stream);
+
+/* _C.cuda_query_sorted_index_with_offsets / _C.cuda_multi_query_...
+ * (csrc/minuet/torch/cuda_sparse_convolution_mapping.cu:9-100) on packed keys:
+ * kernel_map[o, t] = s with source_keys[s] == target_keys[t] + offsets[o].
+ * offsets is a HOST array int32 [O, ndim]. */
+mn_status mn_query_sorted_index_with_offsets(const uint64_t *source_keys, int64_t S,
+                                             const uint64_t *target_keys, int64_t T,
+                                             const int32_t *offsets, int64_t O,
+                                             const mn_keyspec *spec,
+                                             int32_t *kernel_map_out, void *stream);
+
+/* _C.cuda_compute_kernel_map_sizes (cuda_sparse_convolution_mapping.cu:102-125). */
+mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int64_t O, int64_t T,
+                                      int32_t *sizes_out, void *stream);
+
+/* _C.cuda_compute_kernel_map_masks (cuda_sparse_convolution_mapping.cu:127-155). */
+mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int64_t O, int64_t S,
+                                      int64_t T, int32_t *source_masks_out,
+                                      int32_t *target_masks_out, void *ws,
+                                      size_t ws_bytes, void *stream);
+
+/* Fused KernelMapCache.get_kernel_map (minuet/nn/convolutions.py:149-170):
+ * query + sizes + stable ascending size order + both masks without ever
+ * materialising the [O, T] kernel map.  target_keys == source_keys (same
+ * pointer) selects the submanifold shortcut.  order_out int32 [O]
+ * (order[p] = offset index at mask row p; identity when reorder == 0),
+ * sizes_out int32 [O] (sizes of the mask rows, i.e. sorted). */
+mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
+                              const uint64_t *target_keys, int64_t T,
+                              const int32_t *offsets, int64_t O,
+                              const mn_keyspec *spec, int reorder,
+                              int32_t *source_masks_out, int32_t *target_masks_out,
+                              int32_t *order_out, int32_t *sizes_out, void *ws,
+                              size_t ws_bytes, void *stream);
+
+/* Upper bound of the workspace any Map-step entry point needs. */
+size_t mn_map_workspace_bytes(int64_t S, int64_t T, int64_t O);
+
+/* ---- Gather - grouped GEMM - Scatter ------------------------------------- */
+
+/* Host: GeneratePaddingBuckets + ComputeCumsumKernelPaddedSizes
+ * (csrc/minuet/cuda/functions/sparse_convolution.cu:17-43, 273-292).
+ * has_threshold == 0 means threshold None.  buckets_out int64 [O+1],
+ * cumsum_out int64 [O+1]; *num_buckets_out = number of buckets. */
+mn_status mn_plan_buckets(const int32_t *sizes, int64_t O, int has_threshold,
+                          double threshold, int64_t *buckets_out,
+                          int64_t *cumsum_out, int64_t *num_buckets_out);
+
+/* Workspace of mn_sparse_convolution_forward for host-known sorted sizes. */
+size_t mn_conv_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t S,
+                               int64_t T, int64_t c_in, int64_t c_out,
+                               mn_dtype dtype, int allow_shortcut,
+                               int has_threshold, double threshold);
+
+/* _C.cuda_sparse_convolution_forward
+ * (csrc/minuet/torch/cuda_sparse_convolution_forward.cu:136-213).
+ * sizes_host: HOST copy of the mask-row sizes; order: DEVICE int32 [O] or NULL. */
+mn_status mn_sparse_convolution_forward(
+    int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
+    const void *sources, const void *weights, const int32_t *source_masks,
+    const int32_t *target_masks, const int32_t *order, const int32_t *sizes_host,
+    int gather_tile, int scatter_tile, int allow_shortcut, int has_threshold,
+    double threshold, void *targets_out, void *ws, size_t ws_bytes, void *stream);
+
+/* _C.cuda_time_gather / cuda_time_scatter / cuda_time_gemm
+ * (cuda_sparse_convolution_forward.cu:8-134): enqueue only the named stage of
+ * the forward pass on the workspace (contents unspecified), so the caller can
+ * bracket it with events.  stage: 0 gather, 1 gemm, 2 scatter. */
+mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, int64_t c_in,
+                        int64_t c_out, mn_dtype dtype, const void *sources,
+                        const void *weights, const int32_t *source_masks,
+                        const int32_t *target_masks, const int32_t *order,
+                        const int32_t *sizes_host, int tile, int allow_shortcut,
+                        int has_threshold, double threshold, void *targets_out,
+                        void *ws, size_t ws_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINUET_B200_H_ */

@@ -1,0 +1,126 @@
+// Shared declarations of the CUDA side: error plumbing, launch helpers, the key
+// layout and the internal (C++-linkage) launchers that mn_api.cu wraps.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/minuet_b200.h"
+
+namespace mn {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+void set_error(const char *fmt, ...);
+
+#define MN_CHECK_ARG(cond, ...)                      \
+  do {                                               \
+    if (!(cond)) {                                   \
+      ::mn::set_error(__VA_ARGS__);                  \
+      return MN_ERR_BAD_ARG;                         \
+    }                                                \
+  } while (0)
+
+#define MN_CHECK_CUDA(expr)                                                   \
+  do {                                                                        \
+    cudaError_t e__ = (expr);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      ::mn::set_error("%s:%d CUDA error: %s", __FILE__, __LINE__,             \
+                      cudaGetErrorString(e__));                               \
+      return MN_ERR_CUDA;                                                     \
+    }                                                                         \
+  } while (0)
+
+#define MN_CHECK_LAUNCH() MN_CHECK_CUDA(cudaGetLastError())
+
+#define MN_RETURN_IF(expr)              \
+  do {                                  \
+    mn_status s__ = (expr);             \
+    if (s__ != MN_OK) return s__;       \
+  } while (0)
+
+inline int64_t div_up(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+
+// Bump allocator over the caller's workspace; never touches the driver.
+struct Workspace {
+  char *base;
+  size_t size;
+  size_t used = 0;
+  bool overflow = false;
+  Workspace(void *p, size_t n) : base(static_cast<char *>(p)), size(n) {}
+  template <typename T>
+  T *take(size_t count) {
+    size_t bytes = align_up(count * sizeof(T), 256);
+    if (base == nullptr || used + bytes > size) {
+      overflow = true;
+      used += bytes;
+      return nullptr;
+    }
+    T *p = reinterpret_cast<T *>(base + used);
+    used += bytes;
+    return p;
+  }
+};
+
+#define MN_CHECK_WS(ws)                                                        \
+  do {                                                                         \
+    if ((ws).overflow) {                                                       \
+      ::mn::set_error("workspace too small: need %zu bytes, have %zu",         \
+                      (ws).used, (ws).size);                                   \
+      return MN_ERR_WORKSPACE;                                                 \
+    }                                                                          \
+  } while (0)
+
+// Offsets regrouped for the search kernel: offsets that share every dimension
+// but the last form a group, and inside a group the queries of one row grow
+// with the member index, so one binary search serves the whole group.
+struct OffsetTable {
+  int32_t num_offsets;
+  int32_t num_groups;
+  int32_t ndim;
+  int32_t pad_;
+  int32_t off[MN_MAX_OFFSETS][MN_MAX_NDIM];  // effective (sign folded) offsets
+  uint8_t member[MN_MAX_OFFSETS];            // offset indices, group by group
+  uint8_t group_begin[MN_MAX_OFFSETS + 1];   // prefix into member[]
+};
+
+mn_status make_offset_table(const int32_t *offsets, int64_t O, int ndim, int sign,
+                            const mn_keyspec *spec, OffsetTable *out);
+
+// Problem table of the grouped GEMM over offsets, passed to the kernels by value.
+struct GemmTable {
+  int32_t num_problems;
+  int32_t tile_rows;                          // rows per tile the prefix was built for
+  int32_t tile_prefix[MN_MAX_OFFSETS + 2];    // prefix of row tiles over problems
+  int32_t rows[MN_MAX_OFFSETS + 1];
+  int32_t weight_row[MN_MAX_OFFSETS + 1];     // mask row whose weight matrix to use
+  const void *a[MN_MAX_OFFSETS + 1];          // first A row of the problem
+  void *c[MN_MAX_OFFSETS + 1];                // first C row of the problem
+};
+
+// Tensor-core grouped GEMM (mn_gemm_tc.cu); *handled = false when the shape or
+// dtype is outside what it covers and the caller must use the SIMT kernel.
+mn_status launch_gemm_tc(const GemmTable &tab, int c_in, int c_out, mn_dtype dtype,
+                         const void *weights, const int32_t *order, cudaStream_t st,
+                         bool *handled);
+
+// ---- launchers (defined in the .cu files) ---------------------------------
+mn_status launch_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,
+                      int ndim, int32_t *minmax_dev, Workspace &ws, cudaStream_t st);
+mn_status launch_pack(const int32_t *coords, int64_t n, int ndim,
+                      const int64_t *batch_dims, int64_t num_clouds,
+                      const int32_t *tstride, const mn_keyspec &spec,
+                      uint64_t *keys_out, int32_t *status_dev, cudaStream_t st);
+mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
+                            int32_t *vals_tmp, bool iota_vals, int64_t n, int begin_bit,
+                            int end_bit, Workspace &ws, bool *result_in_tmp,
+                            cudaStream_t st);
+size_t radix_sort_workspace_bytes(int64_t n);
+
+}  // namespace mn

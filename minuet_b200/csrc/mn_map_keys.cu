@@ -1,0 +1,276 @@
+// Map step, part 0: bounding box and coordinate packing.
+//
+// Every later Map-step kernel works on one 64-bit key per voxel
+//   key = cloud << cloud_shift | sum_k (c[k] - base[k]) << shift[k]
+// whose unsigned order equals the tensors' sorted order (cloud-major, then
+// lexicographic with dimension 0 most significant) and for which adding a
+// kernel offset is a single 64-bit add: each field carries `margin` spare values
+// on both sides, so target + offset never borrows from a neighbouring field.
+// This replaces the reference's per-cloud flattening
+// (csrc/minuet/cuda/kernels/flatten_coordinates.cuh:23-38) and its three-way
+// integer comparisons (csrc/minuet/common/functions.h:94-105).
+#include "mn_common.cuh"
+
+#include <algorithm>
+#include <climits>
+
+namespace mn {
+
+namespace {
+
+constexpr int kBBoxThreads = 256;
+constexpr int kBBoxMaxBlocks = kNumSMs * 4;
+
+__device__ __forceinline__ void fold(int v, int d, int (&mn_)[4], int (&mx_)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    if (d == k) {
+      mn_[k] = min(mn_[k], v);
+      mx_[k] = max(mx_[k], v);
+    }
+  }
+}
+
+__device__ __forceinline__ void scan_flat(const int32_t *__restrict__ p, int64_t count,
+                                          int ndim, int (&mn_)[4], int (&mx_)[4]) {
+  // flat int32 stream read with 128-bit loads; element j belongs to dim j % ndim
+  const bool aligned = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+  const int64_t nvec = aligned ? (count >> 2) : 0;
+  const int4 *pv = reinterpret_cast<const int4 *>(p);
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = gid; i < nvec; i += gsz) {
+    int4 v = __ldg(pv + i);
+    int d = (int)((i << 2) % ndim);
+    fold(v.x, d, mn_, mx_); d = (d + 1 == ndim) ? 0 : d + 1;
+    fold(v.y, d, mn_, mx_); d = (d + 1 == ndim) ? 0 : d + 1;
+    fold(v.z, d, mn_, mx_); d = (d + 1 == ndim) ? 0 : d + 1;
+    fold(v.w, d, mn_, mx_);
+  }
+  for (int64_t j = (nvec << 2) + gid; j < count; j += gsz) {
+    fold(__ldg(p + j), (int)(j % ndim), mn_, mx_);
+  }
+}
+
+// One partial box per block: partial[b][0..3] = min, [4..7] = max.
+__global__ void __launch_bounds__(kBBoxThreads)
+bbox_partial_kernel(const int32_t *__restrict__ a, int64_t na,
+                    const int32_t *__restrict__ b, int64_t nb, int ndim,
+                    int32_t *__restrict__ partial) {
+  int mn_[4] = {INT_MAX, INT_MAX, INT_MAX, INT_MAX};
+  int mx_[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  if (a != nullptr) scan_flat(a, na * ndim, ndim, mn_, mx_);
+  if (b != nullptr) scan_flat(b, nb * ndim, ndim, mn_, mx_);
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    mn_[k] = __reduce_min_sync(0xffffffffu, mn_[k]);
+    mx_[k] = __reduce_max_sync(0xffffffffu, mx_[k]);
+  }
+  __shared__ int s[kBBoxThreads / 32][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) { s[warp][k] = mn_[k]; s[warp][4 + k] = mx_[k]; }
+  }
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    int v = s[0][threadIdx.x];
+    for (int w = 1; w < kBBoxThreads / 32; w++)
+      v = threadIdx.x < 4 ? min(v, s[w][threadIdx.x]) : max(v, s[w][threadIdx.x]);
+    partial[blockIdx.x * 8 + threadIdx.x] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bbox_final_kernel(const int32_t *__restrict__ partial, int nblocks,
+                  int32_t *__restrict__ minmax) {
+  // 8 groups of 32 threads, one per output value
+  const int which = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int v = which < 4 ? INT_MAX : INT_MIN;
+  for (int b = lane; b < nblocks; b += 32) {
+    int p = partial[b * 8 + which];
+    v = which < 4 ? min(v, p) : max(v, p);
+  }
+  v = which < 4 ? __reduce_min_sync(0xffffffffu, v) : __reduce_max_sync(0xffffffffu, v);
+  if (lane == 0) minmax[which] = v;
+}
+
+__device__ __forceinline__ int floor_to(int c, int s) {
+  int q = c / s;
+  if ((c % s != 0) && (c < 0)) q--;
+  return q * s;
+}
+
+__device__ __forceinline__ int cloud_of(const int64_t *bd, int num_clouds, int64_t row) {
+  int lo = 0, hi = num_clouds;  // largest g with bd[g] <= row
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (bd[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+struct PackParams {
+  mn_keyspec spec;
+  int32_t tstride[4];
+  int32_t has_stride;
+};
+
+__device__ __forceinline__ uint64_t pack_one(const int (&c)[4], int ndim, uint64_t cloud,
+                                             const PackParams &p, bool &bad) {
+  uint64_t key = cloud << p.spec.cloud_shift;
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    if (k < ndim) {
+      int v = p.has_stride ? floor_to(c[k], p.tstride[k]) : c[k];
+      int64_t f = (int64_t)v - p.spec.base[k];
+      if (f < 0 || f > p.spec.extent[k]) {
+        bad = true;
+        f = f < 0 ? 0 : p.spec.extent[k];
+      }
+      key |= (uint64_t)f << p.spec.shift[k];
+    }
+  }
+  return key;
+}
+
+constexpr int kPackThreads = 256;
+constexpr int kMaxSmemClouds = 2048;
+
+// ndim == 3 fast path: 4 rows (48 bytes) per thread as three 128-bit loads and
+// two 128-bit stores; other ndim take the scalar path.
+__global__ void __launch_bounds__(kPackThreads)
+pack_kernel(const int32_t *__restrict__ coords, int64_t n, int ndim,
+            const int64_t *__restrict__ batch_dims, int num_clouds,
+            const __grid_constant__ PackParams p, uint64_t *__restrict__ keys,
+            int32_t *__restrict__ status) {
+  __shared__ int64_t s_bd[kMaxSmemClouds + 1];
+  const int64_t *bd = batch_dims;
+  if (batch_dims != nullptr && num_clouds <= kMaxSmemClouds) {
+    for (int i = threadIdx.x; i <= num_clouds; i += blockDim.x) s_bd[i] = batch_dims[i];
+    __syncthreads();
+    bd = s_bd;
+  }
+  bool bad = false;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  if (ndim == 3) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(coords) | reinterpret_cast<uintptr_t>(keys)) & 15) == 0;
+    const int64_t nquad = aligned ? (n >> 2) : 0;
+    const int4 *cv = reinterpret_cast<const int4 *>(coords);
+    for (int64_t q = gid; q < nquad; q += gsz) {
+      int4 v0 = __ldg(cv + 3 * q), v1 = __ldg(cv + 3 * q + 1), v2 = __ldg(cv + 3 * q + 2);
+      int c0[4] = {v0.x, v0.y, v0.z, 0}, c1[4] = {v0.w, v1.x, v1.y, 0};
+      int c2[4] = {v1.z, v1.w, v2.x, 0}, c3[4] = {v2.y, v2.z, v2.w, 0};
+      const int64_t r = q << 2;
+      uint64_t g0 = 0, g1 = 0, g2 = 0, g3 = 0;
+      if (bd != nullptr) {
+        g0 = cloud_of(bd, num_clouds, r);
+        g3 = cloud_of(bd, num_clouds, r + 3);
+        g1 = g0 == g3 ? g0 : cloud_of(bd, num_clouds, r + 1);
+        g2 = g0 == g3 ? g0 : cloud_of(bd, num_clouds, r + 2);
+      }
+      ulonglong2 lo, hi;
+      lo.x = pack_one(c0, 3, g0, p, bad);
+      lo.y = pack_one(c1, 3, g1, p, bad);
+      hi.x = pack_one(c2, 3, g2, p, bad);
+      hi.y = pack_one(c3, 3, g3, p, bad);
+      ulonglong2 *kv = reinterpret_cast<ulonglong2 *>(keys + r);
+      kv[0] = lo;
+      kv[1] = hi;
+    }
+    for (int64_t r = (nquad << 2) + gid; r < n; r += gsz) {
+      int c[4] = {coords[r * 3], coords[r * 3 + 1], coords[r * 3 + 2], 0};
+      uint64_t g = bd != nullptr ? cloud_of(bd, num_clouds, r) : 0;
+      keys[r] = pack_one(c, 3, g, p, bad);
+    }
+  } else {
+    for (int64_t r = gid; r < n; r += gsz) {
+      int c[4] = {0, 0, 0, 0};
+      for (int k = 0; k < ndim; k++) c[k] = coords[r * ndim + k];
+      uint64_t g = bd != nullptr ? cloud_of(bd, num_clouds, r) : 0;
+      keys[r] = pack_one(c, ndim, g, p, bad);
+    }
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, 2);
+}
+
+inline int bit_width_u64(uint64_t v) {
+  int b = 0;
+  while (v) { b++; v >>= 1; }
+  return b;
+}
+
+}  // namespace
+
+mn_status launch_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,
+                      int ndim, int32_t *minmax_dev, Workspace &ws, cudaStream_t st) {
+  int64_t elems = (na + nb) * ndim;
+  int blocks = (int)std::min<int64_t>(kBBoxMaxBlocks, std::max<int64_t>(1, div_up(elems, kBBoxThreads * 16)));
+  int32_t *partial = ws.take<int32_t>((size_t)kBBoxMaxBlocks * 8);
+  MN_CHECK_WS(ws);
+  bbox_partial_kernel<<<blocks, kBBoxThreads, 0, st>>>(na > 0 ? a : nullptr, na,
+                                                       nb > 0 ? b : nullptr, nb, ndim, partial);
+  MN_CHECK_LAUNCH();
+  bbox_final_kernel<<<1, 256, 0, st>>>(partial, blocks, minmax_dev);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}
+
+mn_status launch_pack(const int32_t *coords, int64_t n, int ndim,
+                      const int64_t *batch_dims, int64_t num_clouds,
+                      const int32_t *tstride, const mn_keyspec &spec,
+                      uint64_t *keys_out, int32_t *status_dev, cudaStream_t st) {
+  if (n == 0) return MN_OK;
+  PackParams p;
+  p.spec = spec;
+  p.has_stride = 0;
+  for (int k = 0; k < 4; k++) p.tstride[k] = 1;
+  if (tstride != nullptr) {
+    for (int k = 0; k < ndim; k++) {
+      MN_CHECK_ARG(tstride[k] >= 1, "pack_keys: stride must be >= 1, got %d", tstride[k]);
+      p.tstride[k] = tstride[k];
+      if (tstride[k] != 1) p.has_stride = 1;
+    }
+  }
+  if (batch_dims == nullptr) num_clouds = 1;
+  int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, kPackThreads * 4));
+  pack_kernel<<<blocks, kPackThreads, 0, st>>>(coords, n, ndim, batch_dims, (int)num_clouds,
+                                               p, keys_out, status_dev);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}
+
+}  // namespace mn
+
+extern "C" mn_status mn_keyspec_make(const int32_t *minmax_host, int ndim,
+                                     int64_t num_clouds, int32_t margin,
+                                     mn_keyspec *spec) {
+  using namespace mn;
+  MN_CHECK_ARG(minmax_host != nullptr && spec != nullptr, "keyspec_make: null pointer");
+  MN_CHECK_ARG(ndim >= 1 && ndim <= MN_MAX_NDIM, "keyspec_make: ndim %d not in 1..4", ndim);
+  MN_CHECK_ARG(margin >= 0, "keyspec_make: negative margin");
+  MN_CHECK_ARG(num_clouds >= 1, "keyspec_make: num_clouds must be >= 1");
+  *spec = mn_keyspec{};
+  spec->ndim = ndim;
+  spec->margin = margin;
+  int shift = 0;
+  for (int k = ndim - 1; k >= 0; k--) {
+    int64_t lo = minmax_host[k], hi = minmax_host[4 + k];
+    if (lo > hi) { lo = 0; hi = 0; }  // empty input
+    spec->base[k] = lo - margin;
+    spec->extent[k] = (hi + margin) - spec->base[k];
+    spec->bits[k] = std::max(1, bit_width_u64((uint64_t)spec->extent[k]));
+    spec->shift[k] = shift;
+    shift += spec->bits[k];
+  }
+  spec->cloud_shift = shift;
+  spec->cloud_bits = bit_width_u64((uint64_t)(num_clouds - 1));
+  spec->total_bits = shift + spec->cloud_bits;
+  if (spec->total_bits > 63) {
+    set_error("keyspec_make: bounding box needs %d key bits (> 63); coordinate "
+              "ranges this large are not supported", spec->total_bits);
+    return MN_ERR_UNSUPPORTED;
+  }
+  return MN_OK;
+}

@@ -1,0 +1,686 @@
+// Map step, part 2: kernel-map search, sizes, size order and masks.
+//
+// The reference builds the kernel map in two traversals
+// (csrc/minuet/cuda/functions/query_sorted_index.cu:14-119): a global binary
+// search per (256-source block, offset) for target borders, then a per-target
+// binary search inside one source block staged in shared memory
+// (kernels/query_sorted_index_with_offsets.cuh:60-76); sizes, order and masks
+// follow as a reduce-by-key, a torch.sort, a DeviceSelect, two memsets and a
+// scatter kernel (functions/scan.cu:221-365, minuet/nn/convolutions.py:156-170).
+//
+// Here both traversals live in one row-tile-stationary kernel over packed
+// 64-bit keys.  A block owns 1024 consecutive rows (targets) and, for every
+// group of offsets that differ only in the last dimension, (1) finds the window
+// of the sorted table (sources) that can match the tile with a warp-cooperative
+// 32-ary ballot search, (2) stages that window in shared memory (adjacent groups
+// share one staging pass when their union fits) and (3) lets every row do ONE
+// binary search per group followed by a short forward walk for the group's
+// other offsets, because inside a group the queries of a row are ascending.
+// The kernel either writes kernel-map rows or, for the fused build, a 32-bit
+// word of per-offset hit bits per row plus per-tile hit counts; ranks and both
+// masks are then produced by a scan over tile counts and one streaming kernel
+// that writes every mask element exactly once (no memset, no select, no
+// scatter).  For submanifold maps (sources == targets, symmetric offsets) the
+// source mask of offset o is read off the hit bits of the mirrored offset.
+#include "mn_common.cuh"
+
+#include <algorithm>
+#include <vector>
+
+namespace mn {
+
+namespace {
+
+constexpr int kQThreads = 256;
+constexpr int kQWarps = kQThreads / 32;
+constexpr int kQRows = 4;                    // rows per thread
+constexpr int kQTile = kQThreads * kQRows;   // 1024 rows per block
+constexpr int kQWindow = 3072;               // table keys staged per pass (24 KB)
+constexpr uint64_t kKeyInf = ~0ull;
+
+__device__ __forceinline__ unsigned lanemask_lt() {
+  unsigned m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// Warp-cooperative 32-ary search in global memory: lower bound (first index
+// with t[i] >= q) or upper bound (first index with t[i] > q).  Every lane
+// probes one pivot per round, a ballot narrows the range 32-fold; ~4 rounds for
+// half a million keys.  All 32 lanes must call with identical arguments.
+__device__ __forceinline__ int64_t warp_bound(const uint64_t *__restrict__ t, int64_t n,
+                                              uint64_t q, bool upper, int lane) {
+  int64_t lo = 0, hi = n;
+  for (int round = 0; round < 16; round++) {
+    const int64_t len = hi - lo;
+    if (len <= 0) break;
+    const int64_t stride = (len + 31) >> 5;
+    const int64_t idx = lo + (int64_t)(lane + 1) * stride - 1;
+    bool pred = false;
+    if (idx < hi) {
+      const uint64_t v = __ldg(t + idx);
+      pred = upper ? (v <= q) : (v < q);
+    }
+    const int c = __popc(__ballot_sync(0xffffffffu, pred));
+    if (stride == 1) return lo + c;
+    const int64_t nlo = min(lo + (int64_t)c * stride, hi);
+    hi = min(hi, nlo + stride - 1);
+    lo = nlo;
+  }
+  return lo;
+}
+
+struct SearchArgs {
+  const uint64_t *rows;
+  const uint64_t *table;
+  int64_t n_rows;
+  int64_t n_table;
+  int32_t *kernel_map;   // kMap:  [O, n_rows]
+  uint32_t *hit_words;   // kBits: [n_rows]
+  int32_t *tile_counts;  // kBits: [O, n_tiles]
+  int32_t n_tiles;
+  int32_t shift[4];
+};
+
+enum SearchMode { kMap = 0, kBits = 1 };
+
+// lower bound of q in win[a, b); trip count depends only on b - a (uniform)
+__device__ __forceinline__ int lower_bound_win(const uint64_t *win, int a, int b, uint64_t q) {
+  int base = a, len = b - a;
+  while (len > 1) {
+    const int half = len >> 1;
+    base = (win[base + half - 1] < q) ? base + half : base;
+    len -= half;
+  }
+  return (len == 1 && win[base] < q) ? base + 1 : base;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kQThreads)
+search_kernel(const SearchArgs a, const __grid_constant__ OffsetTable tab) {
+  __shared__ uint64_t s_win[kQWindow];
+  __shared__ int64_t s_delta[MN_MAX_OFFSETS];
+  __shared__ int64_t s_glo[MN_MAX_OFFSETS], s_ghi[MN_MAX_OFFSETS];
+  __shared__ int32_t s_stage_gbeg[MN_MAX_OFFSETS + 1];
+  __shared__ int32_t s_counts[MN_MAX_OFFSETS];
+  __shared__ int32_t s_num_stages;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int O = tab.num_offsets, G = tab.num_groups;
+  const int64_t tile0 = (int64_t)blockIdx.x * kQTile;
+  const int tile_rows = (int)min((int64_t)kQTile, a.n_rows - tile0);
+
+  for (int o = tid; o < O; o += kQThreads) {
+    int64_t d = 0;
+    for (int k = 0; k < tab.ndim; k++) d += (int64_t)tab.off[o][k] * ((int64_t)1 << a.shift[k]);
+    s_delta[o] = d;
+    s_counts[o] = 0;
+  }
+
+  uint64_t key[kQRows];
+  bool live[kQRows];
+#pragma unroll
+  for (int j = 0; j < kQRows; j++) {
+    const int r = j * kQThreads + tid;
+    live[j] = r < tile_rows;
+    key[j] = live[j] ? __ldg(a.rows + tile0 + r) : 0ull;
+  }
+  const uint64_t kfirst = __ldg(a.rows + tile0);
+  const uint64_t klast = __ldg(a.rows + tile0 + tile_rows - 1);
+  __syncthreads();
+
+  // (1) table window of every group
+  for (int g = warp; g < G; g += kQWarps) {
+    const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+    const uint64_t qlo = kfirst + (uint64_t)s_delta[tab.member[mb]];
+    const uint64_t qhi = klast + (uint64_t)s_delta[tab.member[me - 1]];
+    const int64_t lo = warp_bound(a.table, a.n_table, qlo, false, lane);
+    const int64_t hi = warp_bound(a.table, a.n_table, qhi, true, lane);
+    if (lane == 0) { s_glo[g] = lo; s_ghi[g] = max(lo, hi); }
+  }
+  __syncthreads();
+  // (2) merge adjacent groups into staging passes
+  if (tid == 0) {
+    int ns = 0, g = 0;
+    while (g < G) {
+      s_stage_gbeg[ns++] = g;
+      int64_t lo = s_glo[g], hi = s_ghi[g];
+      g++;
+      if (hi - lo <= kQWindow) {
+        while (g < G) {
+          const int64_t nlo = min(lo, s_glo[g]), nhi = max(hi, s_ghi[g]);
+          if (nhi - nlo > kQWindow) break;
+          lo = nlo; hi = nhi; g++;
+        }
+      }
+    }
+    s_stage_gbeg[ns] = G;
+    s_num_stages = ns;
+  }
+  __syncthreads();
+
+  uint32_t bits[kQRows] = {0u, 0u, 0u, 0u};
+  const int num_stages = s_num_stages;
+  for (int st = 0; st < num_stages; st++) {
+    const int gb = s_stage_gbeg[st], ge = s_stage_gbeg[st + 1];
+    int64_t lo = s_glo[gb], hi = s_ghi[gb];
+    for (int g = gb + 1; g < ge; g++) { lo = min(lo, s_glo[g]); hi = max(hi, s_ghi[g]); }
+    const int64_t wn = hi - lo;
+    const bool staged = wn <= kQWindow;
+    if (staged) {
+      for (int i = tid; i < (int)wn; i += kQThreads) s_win[i] = __ldg(a.table + lo + i);
+    }
+    __syncthreads();
+    for (int g = gb; g < ge; g++) {
+      const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+      const int64_t glo = s_glo[g], ghi = s_ghi[g];
+#pragma unroll
+      for (int j = 0; j < kQRows; j++) {
+        if (live[j]) {
+        const uint64_t q0 = key[j] + (uint64_t)s_delta[tab.member[mb]];
+        int64_t pos;  // absolute index into the table
+        if (staged) {
+          pos = lo + lower_bound_win(s_win, (int)(glo - lo), (int)(ghi - lo), q0);
+        } else {
+          int64_t l = glo, h = ghi;
+          while (l < h) {
+            const int64_t mid = (l + h) >> 1;
+            if (__ldg(a.table + mid) < q0) l = mid + 1; else h = mid;
+          }
+          pos = l;
+        }
+        for (int m = mb; m < me; m++) {
+          const int o = tab.member[m];
+          const uint64_t q = key[j] + (uint64_t)s_delta[o];
+          uint64_t v = kKeyInf;
+          while (pos < ghi) {
+            v = staged ? s_win[pos - lo] : __ldg(a.table + pos);
+            if (v >= q) break;
+            pos++;
+            v = kKeyInf;
+          }
+          const bool hit = (v == q);
+          if (kMode == kMap) {
+            a.kernel_map[(int64_t)o * a.n_rows + tile0 + j * kQThreads + tid] =
+                hit ? (int32_t)pos : -1;
+          } else {
+            bits[j] |= (hit ? 1u : 0u) << o;
+          }
+        }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  if (kMode == kBits) {
+#pragma unroll
+    for (int j = 0; j < kQRows; j++)
+      if (live[j]) a.hit_words[tile0 + j * kQThreads + tid] = bits[j];
+    for (int o = 0; o < O; o++) {
+      int c = 0;
+#pragma unroll
+      for (int j = 0; j < kQRows; j++) c += (bits[j] >> o) & 1u;
+      c = __reduce_add_sync(0xffffffffu, c);
+      if (lane == 0 && c != 0) atomicAdd(&s_counts[o], c);
+    }
+    __syncthreads();
+    for (int o = tid; o < O; o += kQThreads)
+      a.tile_counts[(int64_t)o * a.n_tiles + blockIdx.x] = s_counts[o];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// plan: scan tile counts -> sizes -> stable ascending order
+// ---------------------------------------------------------------------------
+struct PlanArgs {
+  int32_t *counts_a;  // [O, tiles_a] hit counts -> exclusive prefix, in place
+  int32_t *counts_b;  // optional second direction, [O, tiles_b]
+  int32_t tiles_a, tiles_b;
+  int32_t num_offsets;
+  int32_t reorder;
+  int32_t *sizes_raw;     // [O] unsorted (workspace)
+  int32_t *pos_of;        // [O] mask row of offset o (workspace)
+  int32_t *order_out;     // [O] offset at mask row p
+  int32_t *sizes_out;     // [O] size of mask row p
+};
+
+__device__ __forceinline__ int32_t warp_scan_row(int32_t *row, int n, int lane) {
+  int32_t carry = 0;
+  for (int b0 = 0; b0 < n; b0 += 32) {
+    const int b = b0 + lane;
+    const int32_t v = b < n ? row[b] : 0;
+    int32_t inc = v;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int32_t t = __shfl_up_sync(0xffffffffu, inc, s);
+      if (lane >= s) inc += t;
+    }
+    if (b < n) row[b] = carry + inc - v;
+    carry += __shfl_sync(0xffffffffu, inc, 31);
+  }
+  return carry;
+}
+
+__global__ void __launch_bounds__(1024) plan_kernel(const PlanArgs p) {
+  __shared__ int32_t s_size[MN_MAX_OFFSETS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int O = p.num_offsets;
+  for (int o = warp; o < O; o += 32) {
+    const int32_t total = warp_scan_row(p.counts_a + (int64_t)o * p.tiles_a, p.tiles_a, lane);
+    if (p.counts_b != nullptr) warp_scan_row(p.counts_b + (int64_t)o * p.tiles_b, p.tiles_b, lane);
+    if (lane == 0) s_size[o] = total;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < O; o += blockDim.x) {
+    const int32_t mine = s_size[o];
+    int pos = o;
+    if (p.reorder) {
+      pos = 0;
+      for (int j = 0; j < O; j++) {
+        const int32_t other = s_size[j];
+        pos += (other < mine) || (other == mine && j < o);
+      }
+    }
+    if (p.sizes_raw != nullptr) p.sizes_raw[o] = mine;
+    p.pos_of[o] = pos;
+    p.order_out[pos] = o;
+    p.sizes_out[pos] = mine;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// masks from hit words
+// ---------------------------------------------------------------------------
+struct EmitArgs {
+  const uint32_t *words_t;   // [T] hit bits of target rows
+  const uint32_t *words_s;   // [S] hit bits of source rows (== words_t when mirrored)
+  const int32_t *prefix_t;   // [O, tiles_t] exclusive tile prefix, target direction
+  const int32_t *prefix_s;   // [O, tiles_s] source direction (== prefix_t when mirrored)
+  const int32_t *pos_of;     // [O]
+  int32_t *target_masks;     // [O, T]
+  int32_t *source_masks;     // [O, S]
+  int64_t T, S;
+  int32_t tiles_t, tiles_s;
+  int32_t num_offsets;
+  uint8_t mirror[MN_MAX_OFFSETS];  // source direction: which offset's bit/prefix to read
+};
+
+// One block = 1024 consecutive rows of one direction; thread t owns rows
+// 4t..4t+3.  For every offset the rank of a hit row is
+//   tile prefix + hits in lower warps + hits in lower lanes + own earlier hits,
+// and the four results leave as one 128-bit store when the row pitch allows it.
+__global__ void __launch_bounds__(kQThreads)
+emit_masks_kernel(const __grid_constant__ EmitArgs e) {
+  __shared__ int32_t s_wtot[32][kQWarps + 1];  // offsets handled 32 at a time
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool src_dir = blockIdx.x >= (unsigned)e.tiles_t;
+  const int tile = src_dir ? blockIdx.x - e.tiles_t : blockIdx.x;
+  const uint32_t *words = src_dir ? e.words_s : e.words_t;
+  const int32_t *prefix = src_dir ? e.prefix_s : e.prefix_t;
+  const int n_tiles = src_dir ? e.tiles_s : e.tiles_t;
+  const int64_t n = src_dir ? e.S : e.T;
+  int32_t *out = src_dir ? e.source_masks : e.target_masks;
+  const int O = e.num_offsets;
+  const unsigned lt = lanemask_lt();
+
+  const int64_t row0 = (int64_t)tile * kQTile + tid * 4;
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
+  const bool vec_in = (row0 + 3 < n) && ((reinterpret_cast<uintptr_t>(words) & 15) == 0);
+  if (vec_in) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(words + row0));
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++) if (row0 + i < n) w[i] = __ldg(words + row0 + i);
+  }
+  const bool vec_out = ((n & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+
+  for (int o0 = 0; o0 < O; o0 += 32) {
+    const int oc = min(32, O - o0);
+    // warp totals of this chunk of offsets
+    for (int oo = 0; oo < oc; oo++) {
+      const int b = src_dir ? e.mirror[o0 + oo] : (o0 + oo);
+      int c = ((w[0] >> b) & 1u) + ((w[1] >> b) & 1u) + ((w[2] >> b) & 1u) + ((w[3] >> b) & 1u);
+      c = __reduce_add_sync(0xffffffffu, c);
+      if (lane == 0) s_wtot[oo][warp] = c;
+    }
+    __syncthreads();
+    if (tid < oc) {
+      int run = 0;
+#pragma unroll
+      for (int ww = 0; ww < kQWarps; ww++) {
+        const int t = s_wtot[tid][ww];
+        s_wtot[tid][ww] = run;
+        run += t;
+      }
+    }
+    __syncthreads();
+    for (int oo = 0; oo < oc; oo++) {
+      const int o = o0 + oo;
+      const int b = src_dir ? e.mirror[o] : o;
+      const int v0 = (w[0] >> b) & 1u, v1 = (w[1] >> b) & 1u, v2 = (w[2] >> b) & 1u,
+                v3 = (w[3] >> b) & 1u;
+      const int mine = v0 + v1 + v2 + v3;
+      // exclusive prefix of `mine` over the lanes of this warp
+      int inc = mine;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, s);
+        if (lane >= s) inc += t;
+      }
+      int r = __ldg(prefix + (int64_t)b * n_tiles + tile) + s_wtot[oo][warp] + inc - mine;
+      int4 res;
+      res.x = v0 ? r : -1; r += v0;
+      res.y = v1 ? r : -1; r += v1;
+      res.z = v2 ? r : -1; r += v2;
+      res.w = v3 ? r : -1;
+      int32_t *dst = out + (int64_t)__ldg(e.pos_of + o) * n + row0;
+      if (vec_out) {
+        if (row0 < n) *reinterpret_cast<int4 *>(dst) = res;
+      } else {
+        if (row0 + 0 < n) dst[0] = res.x;
+        if (row0 + 1 < n) dst[1] = res.y;
+        if (row0 + 2 < n) dst[2] = res.z;
+        if (row0 + 3 < n) dst[3] = res.w;
+      }
+    }
+    __syncthreads();
+  }
+  (void)lt;
+}
+
+// ---------------------------------------------------------------------------
+// reference-API pieces that start from a materialised kernel map
+// ---------------------------------------------------------------------------
+// counts[o, tile] = valid entries of kernel_map[o, tile*1024 ...)
+__global__ void __launch_bounds__(kQThreads)
+map_count_kernel(const int32_t *__restrict__ kernel_map, int64_t T, int n_tiles,
+                 int32_t *__restrict__ counts, int32_t *__restrict__ sizes_atomic) {
+  const int o = blockIdx.y, tile = blockIdx.x;
+  const int64_t t0 = (int64_t)tile * kQTile;
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < kQRows; j++) {
+    const int64_t t = t0 + j * kQThreads + threadIdx.x;
+    if (t < T) c += __ldg(kernel_map + (int64_t)o * T + t) != -1;
+  }
+  c = __reduce_add_sync(0xffffffffu, c);
+  __shared__ int s[kQWarps];
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int w = 0; w < kQWarps; w++) tot += s[w];
+    if (counts != nullptr) counts[(int64_t)o * n_tiles + tile] = tot;
+    if (sizes_atomic != nullptr && tot != 0) atomicAdd(sizes_atomic + o, tot);
+  }
+}
+
+// rank valid entries of row o by t; write the target mask densely and the
+// source mask (pre-filled with -1) by scatter
+__global__ void __launch_bounds__(kQThreads)
+map_masks_kernel(const int32_t *__restrict__ kernel_map, int64_t S, int64_t T, int n_tiles,
+                 const int32_t *__restrict__ prefix, int32_t *__restrict__ source_masks,
+                 int32_t *__restrict__ target_masks) {
+  const int o = blockIdx.y, tile = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t0 = (int64_t)tile * kQTile + threadIdx.x * 4;
+  int32_t s_idx[4];
+  int mine = 0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    s_idx[i] = (t0 + i < T) ? __ldg(kernel_map + (int64_t)o * T + t0 + i) : -1;
+    mine += s_idx[i] != -1;
+  }
+  int inc = mine;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, s);
+    if (lane >= s) inc += t;
+  }
+  __shared__ int s_w[kQWarps];
+  if (lane == 31) s_w[warp] = inc;
+  __syncthreads();
+  int r = prefix[(int64_t)o * n_tiles + tile] + inc - mine;
+  for (int w = 0; w < warp; w++) r += s_w[w];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    if (t0 + i < T) {
+      const bool v = s_idx[i] != -1;
+      target_masks[(int64_t)o * T + t0 + i] = v ? r : -1;
+      if (v) source_masks[(int64_t)o * S + s_idx[i]] = r;
+      r += v;
+    }
+  }
+}
+
+mn_status run_search(int mode, const uint64_t *rows, int64_t n_rows, const uint64_t *table,
+                     int64_t n_table, const OffsetTable &tab, const mn_keyspec &spec,
+                     int32_t *kernel_map, uint32_t *hit_words, int32_t *tile_counts,
+                     cudaStream_t st) {
+  if (n_rows == 0) return MN_OK;
+  SearchArgs a{};
+  a.rows = rows; a.table = table; a.n_rows = n_rows; a.n_table = n_table;
+  a.kernel_map = kernel_map; a.hit_words = hit_words; a.tile_counts = tile_counts;
+  a.n_tiles = (int)div_up(n_rows, kQTile);
+  for (int k = 0; k < 4; k++) a.shift[k] = spec.shift[k];
+  if (mode == kMap) search_kernel<kMap><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+  else search_kernel<kBits><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}
+
+}  // namespace
+
+mn_status make_offset_table(const int32_t *offsets, int64_t O, int ndim, int sign,
+                            const mn_keyspec *spec, OffsetTable *out) {
+  MN_CHECK_ARG(offsets != nullptr && spec != nullptr, "offset table: null pointer");
+  MN_CHECK_ARG(O >= 1 && O <= MN_MAX_OFFSETS, "offset table: %lld offsets (supported: 1..%d)",
+               (long long)O, MN_MAX_OFFSETS);
+  MN_CHECK_ARG(ndim == spec->ndim, "offset table: ndim %d differs from the key spec's %d", ndim,
+               spec->ndim);
+  *out = OffsetTable{};
+  out->num_offsets = (int32_t)O;
+  out->ndim = ndim;
+  for (int64_t o = 0; o < O; o++)
+    for (int k = 0; k < ndim; k++) {
+      const int64_t v = (int64_t)sign * offsets[o * ndim + k];
+      MN_CHECK_ARG(v >= -(int64_t)spec->margin && v <= (int64_t)spec->margin,
+                   "offset %lld exceeds the key margin %d", (long long)v, spec->margin);
+      out->off[o][k] = (int32_t)v;
+    }
+  std::vector<int> idx(O);
+  for (int64_t o = 0; o < O; o++) idx[o] = (int)o;
+  std::stable_sort(idx.begin(), idx.end(), [&](int x, int y) {
+    for (int k = 0; k < ndim; k++)
+      if (out->off[x][k] != out->off[y][k]) return out->off[x][k] < out->off[y][k];
+    return false;
+  });
+  int g = 0;
+  for (int64_t i = 0; i < O; i++) {
+    out->member[i] = (uint8_t)idx[i];
+    bool new_group = i == 0;
+    if (i > 0)
+      for (int k = 0; k + 1 < ndim; k++)
+        new_group |= out->off[idx[i]][k] != out->off[idx[i - 1]][k];
+    if (new_group) out->group_begin[g++] = (uint8_t)i;
+  }
+  out->group_begin[g] = (uint8_t)O;
+  out->num_groups = g;
+  return MN_OK;
+}
+
+}  // namespace mn
+
+using namespace mn;
+
+extern "C" size_t mn_map_workspace_bytes(int64_t S, int64_t T, int64_t O) {
+  const int64_t n = std::max<int64_t>(std::max(S, T), 1);
+  size_t sort = 2 * align_up((size_t)n * 8, 256) + 2 * align_up((size_t)n * 4, 256) +
+                radix_sort_workspace_bytes(n) + align_up((size_t)div_up(n, 2048) * 4, 256) + 512;
+  const int64_t tiles = div_up(S, kQTile) + div_up(T, kQTile) + 2;
+  size_t map = align_up((size_t)S * 4, 256) + align_up((size_t)T * 4, 256) +
+               2 * align_up((size_t)std::max<int64_t>(O, 1) * tiles * 4, 256) + 4 * 1024;
+  size_t bbox = (size_t)kNumSMs * 4 * 8 * 4 + 256;
+  return std::max(std::max(sort, map), bbox) + 4096;
+}
+
+extern "C" mn_status mn_query_sorted_index_with_offsets(
+    const uint64_t *source_keys, int64_t S, const uint64_t *target_keys, int64_t T,
+    const int32_t *offsets, int64_t O, const mn_keyspec *spec, int32_t *kernel_map_out,
+    void *stream) {
+  MN_CHECK_ARG(S >= 0 && T >= 0, "query: negative size");
+  MN_CHECK_ARG(spec != nullptr, "query: null key spec");
+  MN_CHECK_ARG(S < (1ll << 31) && T < (1ll << 31), "query: more than 2^31-1 rows");
+  OffsetTable tab;
+  MN_RETURN_IF(make_offset_table(offsets, O, spec->ndim, +1, spec, &tab));
+  if (T == 0) return MN_OK;
+  MN_CHECK_ARG(target_keys != nullptr && kernel_map_out != nullptr && (S == 0 || source_keys != nullptr),
+               "query: null pointer");
+  return run_search(kMap, target_keys, T, source_keys, S, tab, *spec, kernel_map_out, nullptr,
+                    nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int64_t O, int64_t T,
+                                                 int32_t *sizes_out, void *stream) {
+  MN_CHECK_ARG(O >= 0 && T >= 0 && O <= 65535, "sizes: bad shape");
+  if (O == 0) return MN_OK;
+  MN_CHECK_ARG(sizes_out != nullptr, "sizes: null output");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MN_CHECK_CUDA(cudaMemsetAsync(sizes_out, 0, sizeof(int32_t) * O, st));
+  if (T == 0) return MN_OK;
+  MN_CHECK_ARG(kernel_map != nullptr, "sizes: null kernel map");
+  const int n_tiles = (int)div_up(T, kQTile);
+  map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, nullptr,
+                                                                     sizes_out);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}
+
+extern "C" mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int64_t O, int64_t S,
+                                                 int64_t T, int32_t *source_masks_out,
+                                                 int32_t *target_masks_out, void *ws_ptr,
+                                                 size_t ws_bytes, void *stream) {
+  MN_CHECK_ARG(O >= 0 && S >= 0 && T >= 0, "masks: bad shape");
+  MN_CHECK_ARG(O <= MN_MAX_OFFSETS, "masks: %lld offsets (supported: up to %d)", (long long)O,
+               MN_MAX_OFFSETS);
+  if (O == 0) return MN_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (S > 0) {
+    MN_CHECK_ARG(source_masks_out != nullptr, "masks: null source mask");
+    MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
+  }
+  if (T == 0) return MN_OK;
+  MN_CHECK_ARG(kernel_map != nullptr && target_masks_out != nullptr, "masks: null pointer");
+  Workspace ws(ws_ptr, ws_bytes);
+  const int n_tiles = (int)div_up(T, kQTile);
+  int32_t *counts = ws.take<int32_t>((size_t)O * n_tiles);
+  int32_t *scratch = ws.take<int32_t>(4 * MN_MAX_OFFSETS);
+  MN_CHECK_WS(ws);
+  map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, counts,
+                                                                     nullptr);
+  MN_CHECK_LAUNCH();
+  PlanArgs p{};
+  p.counts_a = counts; p.tiles_a = n_tiles; p.num_offsets = (int)O; p.reorder = 0;
+  p.sizes_raw = nullptr; p.pos_of = scratch; p.order_out = scratch + MN_MAX_OFFSETS;
+  p.sizes_out = scratch + 2 * MN_MAX_OFFSETS;
+  plan_kernel<<<1, 1024, 0, st>>>(p);
+  MN_CHECK_LAUNCH();
+  map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
+      kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}
+
+extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
+                                         const uint64_t *target_keys, int64_t T,
+                                         const int32_t *offsets, int64_t O,
+                                         const mn_keyspec *spec, int reorder,
+                                         int32_t *source_masks_out, int32_t *target_masks_out,
+                                         int32_t *order_out, int32_t *sizes_out, void *ws_ptr,
+                                         size_t ws_bytes, void *stream) {
+  MN_CHECK_ARG(S >= 0 && T >= 0, "build_kernel_map: negative size");
+  MN_CHECK_ARG(spec != nullptr, "build_kernel_map: null key spec");
+  MN_CHECK_ARG(S < (1ll << 31) && T < (1ll << 31), "build_kernel_map: more than 2^31-1 rows");
+  if (O > 32) {
+    set_error("build_kernel_map: the fused build handles up to 32 offsets (got %lld); use "
+              "mn_query_sorted_index_with_offsets + mn_compute_kernel_map_masks", (long long)O);
+    return MN_ERR_UNSUPPORTED;
+  }
+  MN_CHECK_ARG(order_out != nullptr && sizes_out != nullptr, "build_kernel_map: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int ndim = spec->ndim;
+  OffsetTable fwd;
+  MN_RETURN_IF(make_offset_table(offsets, O, ndim, +1, spec, &fwd));
+
+  // mirrored offset of every offset, if the table is symmetric
+  bool symmetric = true;
+  uint8_t neg[MN_MAX_OFFSETS] = {0};
+  for (int64_t o = 0; o < O && symmetric; o++) {
+    int found = -1;
+    for (int64_t j = 0; j < O && found < 0; j++) {
+      bool same = true;
+      for (int k = 0; k < ndim; k++) same &= offsets[j * ndim + k] == -offsets[o * ndim + k];
+      if (same) found = (int)j;
+    }
+    if (found < 0) symmetric = false; else neg[o] = (uint8_t)found;
+  }
+  const bool mirrored = symmetric && source_keys == target_keys && S == T;
+
+  Workspace ws(ws_ptr, ws_bytes);
+  const int tiles_t = (int)div_up(T, kQTile), tiles_s = (int)div_up(S, kQTile);
+  uint32_t *words_t = ws.take<uint32_t>(std::max<int64_t>(T, 1));
+  int32_t *counts_t = ws.take<int32_t>((size_t)O * std::max(tiles_t, 1));
+  uint32_t *words_s = words_t;
+  int32_t *counts_s = counts_t;
+  if (!mirrored) {
+    words_s = ws.take<uint32_t>(std::max<int64_t>(S, 1));
+    counts_s = ws.take<int32_t>((size_t)O * std::max(tiles_s, 1));
+  }
+  int32_t *pos_of = ws.take<int32_t>(MN_MAX_OFFSETS);
+  MN_CHECK_WS(ws);
+
+  if (T == 0 || S == 0) {
+    // nothing can match: every mask entry is -1, every size 0
+    if (S > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
+    if (T > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(target_masks_out, 0xff, sizeof(int32_t) * O * T, st));
+    std::vector<int32_t> iota(O);
+    for (int64_t o = 0; o < O; o++) iota[o] = (int32_t)o;
+    MN_CHECK_CUDA(cudaMemsetAsync(sizes_out, 0, sizeof(int32_t) * O, st));
+    // order = identity; written by a plan launch over zero tiles
+    PlanArgs p{};
+    p.counts_a = counts_t; p.tiles_a = 0; p.num_offsets = (int)O; p.reorder = 0;
+    p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
+    plan_kernel<<<1, 1024, 0, st>>>(p);
+    MN_CHECK_LAUNCH();
+    return MN_OK;
+  }
+  MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
+                   target_masks_out != nullptr, "build_kernel_map: null pointer");
+
+  MN_RETURN_IF(run_search(kBits, target_keys, T, source_keys, S, fwd, *spec, nullptr, words_t,
+                          counts_t, st));
+  if (!mirrored) {
+    OffsetTable bwd;
+    MN_RETURN_IF(make_offset_table(offsets, O, ndim, -1, spec, &bwd));
+    MN_RETURN_IF(run_search(kBits, source_keys, S, target_keys, T, bwd, *spec, nullptr, words_s,
+                            counts_s, st));
+  }
+  PlanArgs p{};
+  p.counts_a = counts_t; p.tiles_a = tiles_t;
+  p.counts_b = mirrored ? nullptr : counts_s; p.tiles_b = tiles_s;
+  p.num_offsets = (int)O; p.reorder = reorder ? 1 : 0;
+  p.sizes_raw = nullptr; p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
+  plan_kernel<<<1, 1024, 0, st>>>(p);
+  MN_CHECK_LAUNCH();
+
+  EmitArgs e{};
+  e.words_t = words_t; e.words_s = words_s; e.prefix_t = counts_t; e.prefix_s = counts_s;
+  e.pos_of = pos_of; e.target_masks = target_masks_out; e.source_masks = source_masks_out;
+  e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s; e.num_offsets = (int)O;
+  for (int64_t o = 0; o < O; o++) e.mirror[o] = mirrored ? neg[o] : (uint8_t)o;
+  emit_masks_kernel<<<tiles_t + tiles_s, kQThreads, 0, st>>>(e);
+  MN_CHECK_LAUNCH();
+  return MN_OK;
+}

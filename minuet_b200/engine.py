@@ -1,0 +1,155 @@
+"""Torch-facing glue over the C ABI: pointers, streams, workspaces, key specs.
+
+PyTorch is used here only for device memory, the current stream and the final
+device-to-host reads.  All compute is in ``libminuet_b200.so``.
+"""
+import ctypes
+import weakref
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from minuet_b200 import _lib
+from minuet_b200._lib import KeySpec
+
+DEFAULT_MARGIN = 64
+_DTYPE_CODE = {torch.float32: _lib.MN_F32, torch.float16: _lib.MN_F16,
+               torch.bfloat16: _lib.MN_BF16}
+
+
+def lib():
+    return _lib.load()
+
+
+def require_cuda(*tensors):
+    """The reference raises NotImplementedError for non-CUDA tensors
+    (minuet/nn/functional/indexing.py:56,127); so does this engine."""
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NotImplementedError("minuet_b200 runs on CUDA tensors only (no CPU path)")
+
+
+def ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def np_ptr(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"Cannot find implementation of sparse convolution for {dtype}")
+    return _DTYPE_CODE[dtype]
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def as_i32_coords(coords: torch.Tensor) -> torch.Tensor:
+    """The kernels read int32 coordinates; int64 tensors are narrowed (their
+    values must fit, as the reference's subtraction-based comparisons already
+    require |c| < 2**30, csrc/minuet/common/functions.h:94-105)."""
+    if coords.dtype == torch.int32:
+        return coords.contiguous()
+    if coords.dtype == torch.int64:
+        return coords.to(torch.int32).contiguous()
+    raise ValueError(f"The coordinates tensor must be int32 or int64 but found {coords.dtype}")
+
+
+def as_i64(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    return t.to(torch.int64).contiguous()
+
+
+# ---------------------------------------------------------------------------
+# device status word (bit 1: a coordinate fell outside the key box)
+# ---------------------------------------------------------------------------
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    key = torch.device(device).index if torch.device(device).index is not None \
+        else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def raise_on_status(value: int, device):
+    if value != 0:
+        status_word(device).zero_()
+        raise RuntimeError(
+            "a coordinate lies outside the bounding box the sort/search keys were built for "
+            "(call KernelMapCache.reset() before feeding unrelated coordinates)")
+
+
+def check_status(device):
+    """Blocking read of the status word."""
+    raise_on_status(int(status_word(device).item()), device)
+
+
+# ---------------------------------------------------------------------------
+# key specs and keys
+# ---------------------------------------------------------------------------
+
+def make_keyspec(coord_tensors: Sequence[torch.Tensor], ndim: int, num_clouds: int,
+                 margin: int) -> KeySpec:
+    """Bounding box on the device, one small D2H read, layout on the host."""
+    tensors = [t for t in coord_tensors if t is not None and t.shape[0] > 0]
+    spec = KeySpec()
+    if not tensors:
+        mm = np.array([0, 0, 0, 0, 0, 0, 0, 0], dtype=np.int32)
+    else:
+        device = tensors[0].device
+        assert len(tensors) <= 2
+        a = tensors[0]
+        b = tensors[1] if len(tensors) > 1 else None
+        out = torch.empty(8, dtype=torch.int32, device=device)
+        ws = workspace(lib().mn_map_workspace_bytes(0, 0, 0), device)
+        _lib.check(lib().mn_bbox(ptr(a), a.shape[0], ptr(b), 0 if b is None else b.shape[0], ndim,
+                                 ptr(out), ptr(ws), ws.numel(), stream_ptr(device)), "bbox")
+        mm = out.cpu().numpy()
+    _lib.check(lib().mn_keyspec_make(np_ptr(mm), ndim, max(int(num_clouds), 1), int(margin),
+                                     ctypes.byref(spec)), "keyspec")
+    return spec
+
+
+def pack_keys(coords: torch.Tensor, batch_dims: Optional[torch.Tensor], spec: KeySpec,
+              tstride: Optional[Sequence[int]] = None) -> torch.Tensor:
+    n, ndim = coords.shape
+    keys = torch.empty(n, dtype=torch.int64, device=coords.device)
+    ts = None if tstride is None else np.asarray(tstride, dtype=np.int32)
+    nb = 1 if batch_dims is None else batch_dims.numel() - 1
+    _lib.check(lib().mn_pack_keys(ptr(coords), n, ndim, ptr(batch_dims), nb, np_ptr(ts),
+                                  ctypes.byref(spec), ptr(keys), ptr(status_word(coords.device)),
+                                  stream_ptr(coords.device)), "pack_keys")
+    return keys
+
+
+# ---------------------------------------------------------------------------
+# host copies of small device tensors (kernel-map sizes), keyed by tensor
+# ---------------------------------------------------------------------------
+_host_copies = {}
+
+
+def remember_host(t: torch.Tensor, values: np.ndarray):
+    key = id(t)
+    _host_copies[key] = (weakref.ref(t, lambda _r, k=key: _host_copies.pop(k, None)),
+                         np.ascontiguousarray(values))
+
+
+def host_copy(t: torch.Tensor, dtype=np.int32) -> np.ndarray:
+    """Host values of ``t``: the remembered copy when the tensor came from this
+    engine, otherwise a blocking device-to-host read."""
+    hit = _host_copies.get(id(t))
+    if hit is not None and hit[0]() is t:
+        return hit[1].astype(dtype, copy=False)
+    return np.ascontiguousarray(t.detach().cpu().numpy().astype(dtype, copy=False))

@@ -1,0 +1,7 @@
+from .indexing import *
+from .hash import *
+from .scan import *
+from .convolution import *
+from .memory import *
+from .pooling import *
+from .concat import *

@@ -1,0 +1,6 @@
+"""Type aliases used in signatures (minuet/utils/typing.py)."""
+from typing import Iterable, Tuple, TypeVar, Union
+
+T = TypeVar("T")
+ScalarOrTuple = Union[T, Tuple[T, ...]]
+ScalarOrIterable = Union[T, Iterable[T]]

@@ -1,0 +1,181 @@
+"""Gather - GEMM - Scatter on the GPU against the CPU oracle.
+
+Tolerances: fp32 within 1e-5 relative (of the output scale), fp16/bf16 within
+1e-2 relative / 1e-3 absolute of an fp32 computation on the same rounded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+import minuet_b200 as minuet
+from minuet_b200 import synth
+from minuet_b200.nn import functional as F
+from minuet_b200.utils.helpers import generate_kernel_offsets
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype=None):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype, device=DEV)
+
+
+def assert_close(got, want, dtype):
+    got = got.detach().float().cpu().numpy()
+    scale = max(float(np.abs(want).max()), 1e-6)
+    if dtype == torch.float32:
+        assert np.abs(got - want).max() <= 1e-5 * scale, np.abs(got - want).max() / scale
+    else:
+        rtol = 1e-2 if dtype == torch.float16 else 2e-2   # bf16 has 8 mantissa bits
+        np.testing.assert_allclose(got, want, rtol=rtol, atol=1e-3 * scale + 1e-3)
+
+
+def run_layer(oracle_lib, src, sbd, c_in, c_out, kernel, stride, dtype, seed=0, tiles=(1, 1),
+              threshold=-1, transposed_check=False):
+    rng = np.random.default_rng(seed)
+    ksize = int(np.prod(np.broadcast_to(kernel, 3)))
+    x = rng.standard_normal((len(src), c_in)).astype(np.float32)
+    w = synth.kaiming_normal((ksize, c_in, c_out), seed + 1)
+    xt, wt = dev(x).to(dtype), dev(w).to(dtype)
+    x_r, w_r = xt.float().cpu().numpy(), wt.float().cpu().numpy()   # rounded inputs
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    conv = minuet.nn.SparseConv3d(c_in, c_out, kernel, stride=stride, dtype=dtype, device=DEV)
+    conv.kernel.data.copy_(wt)
+    conv.tunable_config.update(gather_tile_size=tiles[0], scatter_tile_size=tiles[1],
+                               threshold=threshold)
+    minuet.set_kernel_map_cache(conv, cache)
+    inp = minuet.SparseTensor(xt, dev(src), batch_dims=None if sbd is None else dev(sbd))
+    out = conv(inp)
+    off = generate_kernel_offsets(3, kernel, 1, 1).astype(np.int32)
+    if stride == 1:
+        tgt, tbd = src, sbd
+    else:
+        tgt, tbd = oracle_lib.downsample(src, stride, sbd)
+    m = oracle_lib.build_kernel_map(src, tgt, off, sbd, tbd)
+    want = oracle_lib.conv_forward(x_r, w_r, m["source_masks"], m["target_masks"], m["order"],
+                                   acc64=True)
+    assert out.F.dtype == dtype and out.F.shape == (len(tgt), c_out)
+    assert np.array_equal(out.C.cpu().numpy(), tgt)
+    assert_close(out.F, want, dtype)
+    return conv, cache, inp, out, want
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("c_in,c_out", [(32, 32), (3, 16), (4, 20), (16, 64), (96, 48)])
+def test_submanifold_layer(oracle_lib, dtype, c_in, c_out):
+    rng = np.random.default_rng(1)
+    src, sbd = synth.random_small_batch(rng, 2, 4000, 24)
+    run_layer(oracle_lib, src, sbd, c_in, c_out, 3, 1, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("kernel,stride", [(2, 2), (3, 2), (2, 1)])
+def test_strided_layer(oracle_lib, dtype, kernel, stride):
+    rng = np.random.default_rng(2)
+    src, sbd = synth.random_small_batch(rng, 3, 3000, 30, low=-9)
+    run_layer(oracle_lib, src, sbd, 16, 32, kernel, stride, dtype)
+
+
+@pytest.mark.parametrize("tiles", [(2, 2), (4, 8), (16, 16), (32, 32)])
+def test_tile_sizes_and_threshold_do_not_change_results(oracle_lib, tiles):
+    rng = np.random.default_rng(3)
+    src, _ = synth.random_small_batch(rng, 1, 5000, 20)
+    for threshold in (-1, 0.3, None):
+        run_layer(oracle_lib, src, None, 32, 32, 3, 1, torch.float16, tiles=tiles,
+                  threshold=threshold)
+
+
+def test_transposed_layer_and_bias(oracle_lib):
+    rng = np.random.default_rng(4)
+    src, sbd = synth.random_small_batch(rng, 2, 3000, 26)
+    conv, cache, inp, down, _ = run_layer(oracle_lib, src, sbd, 8, 16, 2, 2, torch.float32)
+    up = minuet.nn.SparseConv(3, 16, 8, 2, stride=2, transposed=True, bias=True, device=DEV)
+    minuet.set_kernel_map_cache(up, cache)
+    out = up(down)
+    assert out.C is inp.C and out.stride == (1, 1, 1)
+    # oracle: same map with masks swapped, weights by the same offset index
+    off = generate_kernel_offsets(3, 2, 1, 1).astype(np.int32)
+    tgt, tbd = oracle_lib.downsample(src, 2, sbd)
+    m = oracle_lib.build_kernel_map(src, tgt, off, sbd, tbd)
+    want = oracle_lib.conv_forward(down.F.float().cpu().numpy(), up.kernel.detach().cpu().numpy(),
+                                   m["target_masks"], m["source_masks"], m["order"], acc64=True)
+    want = want + up.bias.detach().cpu().numpy()
+    assert_close(out.F, want, torch.float32)
+
+
+def test_trivial_conv_needs_no_cache():
+    conv = minuet.nn.SparseConv3d(8, 5, 1, device=DEV)
+    x = minuet.SparseTensor(torch.randn(10, 8, device=DEV),
+                            torch.arange(30, dtype=torch.int32, device=DEV).view(10, 3))
+    out = conv(x)
+    torch.testing.assert_close(out.F, x.F @ conv.kernel.view(8, 5))
+
+
+def test_empty_rows_and_no_shortcut(oracle_lib):
+    """A cache with reordering disabled takes the no-shortcut path; targets with
+    no neighbour at all must come out as zeros."""
+    src = synth.sort_unique(np.array([[0, 0, 0], [10, 10, 10], [10, 10, 11], [50, 0, 0]]))
+    x = np.arange(4 * 4, dtype=np.float32).reshape(4, 4)
+    w = synth.kaiming_normal((27, 4, 4), 0)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV, disable_reordering=True)
+    conv = minuet.nn.SparseConv3d(4, 4, 3, device=DEV)
+    conv.kernel.data.copy_(dev(w))
+    minuet.set_kernel_map_cache(conv, cache)
+    out = conv(minuet.SparseTensor(dev(x), dev(src)))
+    off = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    km = oracle_lib.query(src, src, off)
+    assert_close(out.F, oracle_lib.conv_bruteforce(x, w, km).astype(np.float32), torch.float32)
+
+
+def test_functional_forward_with_foreign_size_tensor(oracle_lib):
+    """sparse_convolution_forward on masks that did not come from the cache
+    (sizes are then read back from the device)."""
+    rng = np.random.default_rng(6)
+    src, _ = synth.random_small_batch(rng, 1, 2000, 16)
+    off = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    m = oracle_lib.build_kernel_map(src, src, off)
+    x = rng.standard_normal((len(src), 8)).astype(np.float32)
+    w = synth.kaiming_normal((27, 8, 8), 3)
+    out = F.sparse_convolution_forward(
+        sources=dev(x), weights=dev(w), source_masks=dev(m["source_masks"]),
+        target_masks=dev(m["target_masks"]), kernel_map_order=dev(m["order"]),
+        kernel_map_sizes=dev(m["sorted_sizes"]), gather_tile_size=1, scatter_tile_size=1,
+        allow_shortcut_matmul=True)
+    want = oracle_lib.conv_forward(x, w, m["source_masks"], m["target_masks"], m["order"], True)
+    assert_close(out, want, torch.float32)
+    with pytest.raises(RuntimeError):
+        F.sparse_convolution_forward(
+            sources=dev(x).half(), weights=dev(w), source_masks=dev(m["source_masks"]),
+            target_masks=dev(m["target_masks"]), kernel_map_order=dev(m["order"]),
+            kernel_map_sizes=dev(m["sorted_sizes"]), gather_tile_size=1, scatter_tile_size=1)
+
+
+def test_config0_single_layer_fp32(oracle_lib):
+    """50 000 uniform voxels, SparseConv3d(32, 32, 3), fp32."""
+    src = synth.uniform_cloud()
+    run_layer(oracle_lib, src, None, 32, 32, 3, 1, torch.float32)
+
+
+@pytest.mark.parametrize("c", [16, 64, 256])
+def test_outdoor_fp16_sweep_point(oracle_lib, c):
+    src, sbd = synth.outdoor_batch(2, n_voxels=60_000)
+    run_layer(oracle_lib, src, sbd, c, c, 3, 1, torch.float16)
+
+
+def test_stage_timers_and_autotune(oracle_lib):
+    rng = np.random.default_rng(8)
+    src, _ = synth.random_small_batch(rng, 1, 3000, 20)
+    conv, cache, inp, out, want = run_layer(oracle_lib, src, None, 16, 16, 3, 1, torch.float16)
+    sm, tm, order, sizes = cache.get_kernel_map(inp.C, 1, None, inp.C, 1, None, 3, 1)
+    for fn in (F.cuda_time_gather, F.cuda_time_scatter):
+        assert fn(conv.kernel, sm, tm, sizes, tile_size=8, allow_shortcut_matmul=True) > 0
+    assert F.cuda_time_gemm(conv.kernel, sm, tm, sizes, allow_shortcut_matmul=True) > 0
+    conv.__class__.__NUM_TUNING_ROUNDS__ = 1
+    try:
+        minuet.autotune(conv, cache, inp)
+    finally:
+        conv.__class__.__NUM_TUNING_ROUNDS__ = 10
+    cfg = conv.tunable_config
+    assert 16 % cfg["gather_tile_size"] == 0 and 16 % cfg["scatter_tile_size"] == 0
+    cache.reset()
+    assert_close(conv(inp).F, want, torch.float16)

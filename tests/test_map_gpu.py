@@ -1,0 +1,255 @@
+"""Map step on the GPU against the CPU oracle: bit-exact integers."""
+import numpy as np
+import pytest
+import torch
+
+import minuet_b200 as minuet
+from minuet_b200 import synth
+from minuet_b200.nn import functional as F
+from minuet_b200.utils.helpers import generate_kernel_offsets
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype=None):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype, device=DEV)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+# ---------------------------------------------------------------------------
+# arg sort
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("ndim,n", [(3, 1), (3, 5), (3, 4097), (3, 100_003), (1, 1000), (2, 5000),
+                                    (4, 3000)])
+def test_arg_sort_single(oracle_lib, ndim, n):
+    rng = np.random.default_rng(n + ndim)
+    coords = rng.integers(-50, 50, size=(n, ndim)).astype(np.int32)   # many duplicates: stability
+    got = host(F.arg_sort_coordinates(dev(coords)))
+    assert got.dtype == np.int32
+    assert np.array_equal(got, oracle_lib.arg_sort(coords))
+    got64 = F.build_sorted_index(dev(coords))
+    assert got64.dtype == torch.int64 and np.array_equal(host(got64), oracle_lib.arg_sort(coords))
+
+
+def test_arg_sort_batched_with_empty_cloud(oracle_lib):
+    rng = np.random.default_rng(11)
+    coords = rng.integers(-300, 300, size=(20_000, 3)).astype(np.int32)
+    bd = np.array([0, 7000, 7000, 12_345, 20_000], np.int64)
+    got = F.arg_sort_coordinates(dev(coords), batch_dims=dev(bd))
+    assert got.dtype == torch.int64
+    assert np.array_equal(host(got), oracle_lib.arg_sort(coords, bd))
+    got32 = F.arg_sort_coordinates(dev(coords), batch_dims=dev(bd, torch.int32))
+    assert got32.dtype == torch.int32
+    assert np.array_equal(host(got32), oracle_lib.arg_sort(coords, bd))
+
+
+def test_arg_sort_empty_and_int64_coords(oracle_lib):
+    assert F.arg_sort_coordinates(torch.empty((0, 3), dtype=torch.int32, device=DEV)).numel() == 0
+    rng = np.random.default_rng(2)
+    coords = rng.integers(-10**6, 10**6, size=(3000, 3)).astype(np.int64)
+    got = host(F.arg_sort_coordinates(dev(coords)))
+    assert np.array_equal(got, oracle_lib.arg_sort(coords.astype(np.int32)))
+
+
+def test_arg_sort_rejects_unpackable_range():
+    coords = np.array([[-2**30, -2**30, -2**30], [2**30, 2**30, 2**30]], np.int32)
+    with pytest.raises(NotImplementedError):
+        F.arg_sort_coordinates(dev(coords))
+
+
+# ---------------------------------------------------------------------------
+# unique
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 2, 2047, 2048, 2049, 50_000])
+def test_unique_single(oracle_lib, n):
+    rng = np.random.default_rng(n)
+    coords = rng.integers(0, 12, size=(n, 3)).astype(np.int32)
+    coords = coords[oracle_lib.arg_sort(coords)]
+    uniq, indices = F.unique_coordinates(dev(coords))
+    want_u, want_i = oracle_lib.unique(coords)
+    assert indices.dtype == torch.int64
+    assert np.array_equal(host(uniq), want_u) and np.array_equal(host(indices), want_i)
+
+
+def test_unique_batched_and_empty(oracle_lib):
+    rng = np.random.default_rng(5)
+    coords = rng.integers(0, 6, size=(9000, 3)).astype(np.int32)
+    bd = np.array([0, 3000, 3000, 3001, 9000], np.int64)
+    coords = coords[oracle_lib.arg_sort(coords, bd)]
+    uniq, indices = F.unique_coordinates(dev(coords), batch_dims=dev(bd, torch.int32))
+    want_u, want_i = oracle_lib.unique(coords, bd)
+    assert indices.dtype == torch.int32
+    assert np.array_equal(host(uniq), want_u) and np.array_equal(host(indices), want_i)
+    uniq, indices = F.unique_coordinates(torch.empty((0, 3), dtype=torch.int32, device=DEV))
+    assert uniq.shape == (0, 3) and host(indices).tolist() == [0]
+
+
+# ---------------------------------------------------------------------------
+# kernel map query, sizes, masks (reference-style API)
+# ---------------------------------------------------------------------------
+def _targets(oracle_lib, src, sbd, stride):
+    if stride == 1:
+        return src, sbd
+    return oracle_lib.downsample(src, stride, sbd)
+
+
+@pytest.mark.parametrize("kernel,stride,dilation", [(3, 1, 1), (2, 1, 1), (3, 2, 1), (2, 2, 1),
+                                                    (3, 1, 2), (5, 1, 1), ((3, 1, 2), 1, 1)])
+@pytest.mark.parametrize("batched", [False, True])
+def test_query_sizes_masks(oracle_lib, kernel, stride, dilation, batched):
+    rng = np.random.default_rng(17)
+    src, sbd = synth.random_small_batch(rng, 3 if batched else 1, 6000, 40, low=-13)
+    if not batched:
+        sbd = None
+    tgt, tbd = _targets(oracle_lib, src, sbd, stride)
+    off = generate_kernel_offsets(3, kernel, 1, dilation).astype(np.int32)
+    want = oracle_lib.query(src, tgt, off, sbd, tbd)
+    got = F.query_sorted_index_with_offsets(dev(src), dev(tgt), dev(off),
+                                            None if sbd is None else dev(sbd),
+                                            None if tbd is None else dev(tbd))
+    assert got.dtype == (torch.int64 if batched else torch.int32)
+    assert np.array_equal(host(got), want)
+    sizes = F.compute_kernel_map_sizes(got)
+    want_sizes = oracle_lib.sizes(want)
+    assert np.array_equal(host(sizes), want_sizes)
+    order, _ = oracle_lib.order(want_sizes)
+    sm, tm = F.compute_kernel_map_masks(len(src), got[dev(order, torch.int64)], sizes)
+    want_sm, want_tm = oracle_lib.masks(want[order], len(src))
+    assert np.array_equal(host(sm), want_sm) and np.array_equal(host(tm), want_tm)
+
+
+def test_query_edge_cases(oracle_lib):
+    off = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    one = np.array([[5, -7, 3]], np.int32)
+    got = host(F.query_sorted_index_with_offsets(dev(one), dev(one), dev(off)))
+    assert np.array_equal(got, oracle_lib.query(one, one, off))
+    empty = torch.empty((0, 3), dtype=torch.int32, device=DEV)
+    assert F.query_sorted_index_with_offsets(dev(one), empty, dev(off)).shape == (27, 0)
+    got = host(F.query_sorted_index_with_offsets(empty, dev(one), dev(off)))
+    assert (got == -1).all()
+    # a dense block: every interior voxel has all 27 neighbours
+    g = np.stack(np.meshgrid(*[np.arange(12)] * 3, indexing="ij"), -1).reshape(-1, 3).astype(np.int32)
+    got = host(F.query_sorted_index_with_offsets(dev(g), dev(g), dev(off)))
+    assert np.array_equal(got, oracle_lib.query(g, g, off))
+
+
+@pytest.mark.parametrize("ndim", [1, 2, 4])
+def test_query_other_ndim(oracle_lib, ndim):
+    rng = np.random.default_rng(ndim)
+    src, _ = synth.random_small_batch(rng, 1, 3000, 30 if ndim > 1 else 5000, ndim=ndim)
+    off = generate_kernel_offsets(ndim, 3, 1, 1).astype(np.int32)
+    got = host(F.query_sorted_index_with_offsets(dev(src), dev(src), dev(off)))
+    assert np.array_equal(got, oracle_lib.query(src, src, off))
+
+
+# ---------------------------------------------------------------------------
+# KernelMapCache: fused target coordinates + fused map build
+# ---------------------------------------------------------------------------
+def _check_map(oracle_lib, result, src, tgt, off, sbd, tbd, reorder=True):
+    sm, tm, order, sizes = result
+    want = oracle_lib.build_kernel_map(src, tgt, off, sbd, tbd, reorder=reorder)
+    assert np.array_equal(host(sizes), want["sorted_sizes"])
+    if reorder:
+        assert np.array_equal(host(order), want["order"])
+    else:
+        assert order is None
+    assert np.array_equal(host(tm), want["target_masks"])
+    assert np.array_equal(host(sm), want["source_masks"])
+
+
+@pytest.mark.parametrize("batched", [False, True])
+@pytest.mark.parametrize("n", [3, 1500, 30_000])
+def test_cache_submanifold_and_strided(oracle_lib, batched, n):
+    rng = np.random.default_rng(n)
+    src, sbd = synth.random_small_batch(rng, 4 if batched else 1, n, 64, low=-20)
+    if not batched:
+        sbd = None
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    d_src = dev(src)
+    d_sbd = None if sbd is None else dev(sbd)
+    # 3^3 stride 1
+    off3 = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    c1 = cache.get_target_coordinates(d_src, d_sbd, 1, 1)
+    assert c1[0] is d_src
+    r = cache.get_kernel_map(d_src, 1, d_sbd, c1[0], c1[1], c1[2], 3, 1)
+    _check_map(oracle_lib, r, src, src, off3, sbd, sbd)
+    assert cache.get_kernel_map(d_src, 1, d_sbd, c1[0], c1[1], c1[2], 3, 1)[0] is r[0]
+    # 2^3 stride 2 down, then 3^3 at stride 2, then transposed back up
+    tgt_c, tgt_s, tgt_bd = cache.get_target_coordinates(d_src, d_sbd, 1, 2)
+    want_c, want_bd = oracle_lib.downsample(src, 2, sbd)
+    assert tgt_s == (2, 2, 2) and np.array_equal(host(tgt_c), want_c)
+    if batched:
+        assert np.array_equal(host(tgt_bd), want_bd)
+    off2 = generate_kernel_offsets(3, 2, 1, 1).astype(np.int32)
+    down = cache.get_kernel_map(d_src, 1, d_sbd, tgt_c, tgt_s, tgt_bd, 2, 1)
+    _check_map(oracle_lib, down, src, want_c, off2, sbd, want_bd)
+    assert int(host(down[3]).sum()) == len(src)
+    off3s2 = generate_kernel_offsets(3, 3, 2, 1).astype(np.int32)
+    r2 = cache.get_kernel_map(tgt_c, 2, tgt_bd, tgt_c, tgt_s, tgt_bd, 3, 1)
+    _check_map(oracle_lib, r2, want_c, want_c, off3s2, want_bd, want_bd)
+    up_c = cache.get_target_coordinates(tgt_c, tgt_bd, 2, 2, transposed=True)
+    assert up_c[0] is d_src and up_c[1] == (1, 1, 1)
+    up = cache.get_kernel_map(tgt_c, 2, tgt_bd, d_src, 1, d_sbd, 2, 1, transposed=True)
+    assert up[0] is down[1] and up[1] is down[0]
+    # 3^3 stride 2 strided map and a no-reorder cache
+    cache.reset()
+    t2 = cache.get_target_coordinates(d_src, d_sbd, 1, 2)
+    r3 = cache.get_kernel_map(d_src, 1, d_sbd, t2[0], t2[1], t2[2], 3, 1)
+    _check_map(oracle_lib, r3, src, want_c, off3, sbd, want_bd)
+    plain = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV, disable_reordering=True)
+    r4 = plain.get_kernel_map(d_src, 1, d_sbd, d_src, 1, d_sbd, 3, 1)
+    _check_map(oracle_lib, r4, src, src, off3, sbd, sbd, reorder=False)
+
+
+def test_cache_large_kernel_takes_unfused_path(oracle_lib):
+    rng = np.random.default_rng(9)
+    src, _ = synth.random_small_batch(rng, 1, 4000, 24)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    d_src = dev(src)
+    r = cache.get_kernel_map(d_src, 1, None, d_src, 1, None, 5, 1)
+    _check_map(oracle_lib, r, src, src, generate_kernel_offsets(3, 5, 1, 1).astype(np.int32),
+               None, None)
+
+
+def test_cache_rejects_foreign_coordinates():
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    a = dev(synth.sort_unique(np.random.default_rng(0).integers(0, 50, size=(500, 3))))
+    cache.get_kernel_map(a, 1, None, a, 1, None, 3, 1)
+    far = dev(np.array([[10_000, 0, 0]], np.int32))
+    with pytest.raises(RuntimeError):
+        cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)
+    cache.reset()
+    cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)
+
+
+@pytest.mark.parametrize("kind", ["uniform50k", "outdoor4"])
+def test_config_scale_maps(oracle_lib, kind):
+    """Benchmark-size inputs: the 50 000-voxel uniform cloud and the 4 x 120 000
+    outdoor batch, all four kernel/stride combinations."""
+    if kind == "uniform50k":
+        src, sbd = synth.uniform_cloud(), None
+    else:
+        src, sbd = synth.outdoor_batch(4)
+    d_src, d_sbd = dev(src), None if sbd is None else dev(sbd)
+    want_c, want_bd = oracle_lib.downsample(src, 2, sbd)
+    for kernel, stride in [(3, 1), (2, 1), (3, 2), (2, 2)]:
+        cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+        tc, ts, tbd = cache.get_target_coordinates(d_src, d_sbd, 1, stride)
+        r = cache.get_kernel_map(d_src, 1, d_sbd, tc, ts, tbd, kernel, 1)
+        off = generate_kernel_offsets(3, kernel, 1, 1).astype(np.int32)
+        if stride == 1:
+            _check_map(oracle_lib, r, src, src, off, sbd, sbd)
+        else:
+            assert np.array_equal(host(tc), want_c)
+            _check_map(oracle_lib, r, src, want_c, off, sbd, want_bd)
+        # size-independent properties
+        sm, tm, order, sizes = (host(t) for t in r)
+        assert np.array_equal((sm >= 0).sum(1), sizes) and np.array_equal((tm >= 0).sum(1), sizes)
+        if kernel == 3 and stride == 1:
+            assert sizes[-1] == len(src) and order[-1] == 13
+        if kernel == 2 and stride == 2:
+            assert sizes.sum() == len(src)
