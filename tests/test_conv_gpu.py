@@ -1,7 +1,8 @@
 """Gather - GEMM - Scatter on the GPU against the CPU oracle.
 
-Tolerances: fp32 within 1e-5 relative (of the output scale), fp16/bf16 within
-1e-2 relative / 1e-3 absolute of an fp32 computation on the same rounded inputs.
+Tolerances: fp32 within 1e-5 relative (of the output scale), fp16 within 1e-2
+relative / 1e-3 absolute of an fp64-accumulated computation on the same rounded
+inputs (bf16: four times those bounds).
 """
 import numpy as np
 import pytest
@@ -26,8 +27,10 @@ def assert_close(got, want, dtype):
     if dtype == torch.float32:
         assert np.abs(got - want).max() <= 1e-5 * scale, np.abs(got - want).max() / scale
     else:
-        rtol = 1e-2 if dtype == torch.float16 else 2e-2   # bf16 has 8 mantissa bits
-        np.testing.assert_allclose(got, want, rtol=rtol, atol=1e-3 * scale + 1e-3)
+        # fp16: 1e-2 relative / 1e-3 absolute (of the output scale); bf16 keeps
+        # 8 mantissa bits (eps = 3.9e-3), so its bounds are 4x wider
+        k = 1.0 if dtype == torch.float16 else 4.0
+        np.testing.assert_allclose(got, want, rtol=k * 1e-2, atol=k * (1e-3 * scale + 1e-3))
 
 
 def run_layer(oracle_lib, src, sbd, c_in, c_out, kernel, stride, dtype, seed=0, tiles=(1, 1),
