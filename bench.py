@@ -1,0 +1,378 @@
+"""Benchmark of the Map step (kernel-map build) on synthetic outdoor clouds.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: a batch of 4 outdoor-scan-like clouds of 120 000 voxels per GPU; one
+step builds, on a cold KernelMapCache, the four kernel maps
+(kernel 3^3 / 2^3) x (stride 1 / 2), including the strided target coordinates
+(floor, sort, unique).  The metric is source voxels processed per second, summed
+over the four maps (Mvoxels/s).  With N > 1 every rank owns its own batch (weak
+scaling, no collective on the data path); the time is the max over ranks.
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+MAPS = [(3, 1), (2, 1), (3, 2), (2, 2)]       # (kernel size, kernel stride)
+CLOUDS_PER_GPU = 4
+VOXELS_PER_CLOUD = 120_000
+METRIC = "kernel-map Mvoxels/s"
+UNIT = "Mvoxels/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle restatement on the host cores
+# ---------------------------------------------------------------------------
+def oracle_step(oracle, coords, bd, offsets):
+    tgt2, tbd2 = oracle.downsample(coords, 2, bd)
+    out = []
+    for kernel, stride in MAPS:
+        tgt, tbd = (coords, bd) if stride == 1 else (tgt2, tbd2)
+        out.append(oracle.build_kernel_map(coords, tgt, offsets[kernel], bd, tbd))
+    return out
+
+
+def run_cpu(steps, warmup, coords, bd, min_seconds=0.0):
+    import oracle
+    from minuet_b200.utils.helpers import generate_kernel_offsets
+    oracle.build()
+    offsets = {k: generate_kernel_offsets(3, k, 1, 1).astype(np.int32) for k in (2, 3)}
+    for _ in range(warmup):
+        oracle_step(oracle, coords, bd, offsets)
+    t0 = time.perf_counter()
+    done = 0
+    while done < steps or time.perf_counter() - t0 < min_seconds:
+        oracle_step(oracle, coords, bd, offsets)
+        done += 1
+    dt = time.perf_counter() - t0
+    voxels = len(MAPS) * len(coords) * done
+    return voxels / dt / 1e6, dt / done * 1e3, done, oracle.num_threads()
+
+
+def reference_arm(args):
+    """The reference has no CPU implementation of this path (every functional
+    wrapper raises NotImplementedError off-GPU), so its CPU arm is the oracle
+    restatement, all host threads, on the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from minuet_b200 import synth
+    coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000, n_voxels=VOXELS_PER_CLOUD)
+    value, ms, done, cores = run_cpu(args.steps, args.warmup, coords, bd)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+        "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
+        "data": "synthetic",
+        "config": workload_config(len(coords)),
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{done} full steps (4 cold map builds of one 4-cloud batch)"},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_voxels_per_gpu):
+    return {"workload": "C1 kernel-map build: 4 outdoor clouds x ~120k voxels per GPU, maps "
+                        "(3^3,s1) (2^3,s1) (3^3,s2) (2^3,s2), cold cache, int32 coords",
+            "voxels_per_gpu": int(n_voxels_per_gpu), "maps_per_step": len(MAPS),
+            "l2": "flushed between timed steps (512 MiB write); per-step outputs ~0.5 GB > L2"}
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.path = None
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.out = open(self.path, "w")
+        self.proc = subprocess.Popen([exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader",
+                                      "-i", str(gpu_index), "-lms", "100"],
+                                     stdout=self.out, stderr=subprocess.DEVNULL)
+
+    def stop(self, windows=()):
+        """Median SM clock and throttle reasons over the samples that fall inside
+        the given (start, end) wall-clock windows; all samples when none does."""
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        import datetime
+        rows = []
+        with open(self.path) as f:
+            for row in f:
+                cols = [c.strip() for c in row.split(",")]
+                if len(cols) < 9:
+                    continue
+                try:
+                    ts = datetime.datetime.strptime(cols[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(cols[1].split()[0]), float(cols[2].split()[0]),
+                                 [c.lower().startswith("active") for c in cols[5:9]]))
+                except ValueError:
+                    continue
+        os.unlink(self.path)
+        if not rows:
+            return None
+        inside = [r for r in rows if any(a <= r[0] <= b for a, b in windows)]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = rows, "whole run (timed region shorter than the sampling period)"
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({n for r in inside for n, on in zip(names, r[3]) if on})
+        return {"sm_mhz": float(np.median([r[1] for r in inside])),
+                "sm_max_mhz": float(max(r[2] for r in inside)), "reasons": reasons,
+                "samples": len(inside), "window": window}
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def kernel_bytes(name, S, T_by_stride, num_clouds):
+    """Algorithmic bytes per step of one kernel name, summed over its launches.
+    S source voxels; T target voxels per kernel stride; O = k^3."""
+    total = 0
+    for kernel, stride in MAPS:
+        O, T = kernel ** 3, T_by_stride[stride]
+        mirrored = stride == 1 and kernel % 2 == 1
+        if name == "emit_masks_kernel":
+            total += 4 * O * (S + T) + 4 * (S + T)          # masks written, hit words read
+        elif name == "search_kernel<bits>":
+            total += 8 * (S + T) + 4 * T + 4 * O * ((T + 1023) // 1024)   # keys read, words + counts written
+            if not mirrored:
+                total += 8 * (S + T) + 4 * S + 4 * O * ((S + 1023) // 1024)
+    if name == "pack_kernel":
+        total = (12 + 8) * S * 2                              # source keys + floored keys
+    return total
+
+
+def gpu_arm(args):
+    import torch
+    import minuet_b200 as minuet
+    from minuet_b200 import _lib, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    lib = _lib.load()
+    coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000 + 100 * rank,
+                                     n_voxels=VOXELS_PER_CLOUD)
+    S = len(coords)
+    h_coords = torch.from_numpy(coords).pin_memory()
+    h_bd = torch.from_numpy(bd).pin_memory()
+    d_coords, d_bd = h_coords.to(dev), h_bd.to(dev)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def step(c, b):
+        cache.reset()
+        out = []
+        for kernel, stride in MAPS:
+            tc, ts, tbd = cache.get_target_coordinates(c, b, 1, stride)
+            out.append(cache.get_kernel_map(c, 1, b, tc, ts, tbd, kernel, 1))
+        return out
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """Per-step CUDA events on the current stream; L2 flushed between steps."""
+        total = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            total += a.elapsed_time(b)
+        return total
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step(d_coords, d_bd)
+    T_by_stride = {1: S, 2: int(cache.get_target_coordinates(d_coords, d_bd, 1, 2)[0].shape[0])}
+
+    # ---- device-resident inputs ------------------------------------------------
+    barrier()
+    launches0 = lib.mn_launch_count()
+    w0 = time.time()
+    ms_total = timed(lambda: step(d_coords, d_bd), args.steps)
+    barrier()
+    w1 = time.time()
+    t_wall = w1 - w0
+    launches = lib.mn_launch_count() - launches0
+
+    # ---- host buffers in, sizes/order out (end to end) ---------------------------
+    def e2e_step():
+        c = h_coords.to(dev, non_blocking=True)
+        b = h_bd.to(dev, non_blocking=True)
+        out = step(c, b)
+        # the masks stay on the GPU for the convolutions; what the host consumes
+        # per map is the size-sorted order
+        return [o[2].cpu() for o in out]
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    w2 = time.time()
+    ms_e2e = timed(e2e_step, args.steps)
+    barrier()
+    w3 = time.time()
+    clocks = sampler.stop([(w0, w1), (w2, w3)]) if sampler is not None else None
+
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = (float(v) for v in times.cpu())
+    voxels_all = len(MAPS) * S * world      # every rank holds S voxels (same generator sizes)
+    if dist is not None:
+        counts = torch.tensor([len(MAPS) * S], dtype=torch.int64, device=dev)
+        dist.all_reduce(counts)
+        voxels_all = int(counts.item())
+    value = voxels_all * args.steps / (ms_total * 1e-3) / 1e6
+    e2e_value = voxels_all * args.steps / (ms_e2e * 1e-3) / 1e6
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- per-kernel times (separate, untimed pass) ---------------------------------
+    lib.mn_profile_enable(1)
+    prof_steps = 5
+    for _ in range(prof_steps):
+        flush.zero_()
+        step(d_coords, d_bd)
+    torch.cuda.synchronize()
+    lib.mn_profile_enable(0)
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.mn_profile_report(buf, len(buf))
+    kernels = {}
+    for row in buf.value.decode().splitlines():
+        name, count, ms = row.rsplit(" ", 2)
+        kernels[name] = {"launches_per_step": int(count) / prof_steps,
+                         "ms_per_step": float(ms) / prof_steps}
+    top = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
+    peaks, peak_kind = measured_peaks()
+    top_bytes = kernel_bytes(top, S, T_by_stride, CLOUDS_PER_GPU)
+    top_ms = kernels[top]["ms_per_step"]
+    achieved = top_bytes / (top_ms * 1e-3) / 1e9 if top_bytes else None
+    stage_bytes = sum(12 * (S + T_by_stride[s]) + 4 * k ** 3 * (S + T_by_stride[s]) for k, s in MAPS)
+    stage_bytes_with_map = stage_bytes + sum(4 * k ** 3 * T_by_stride[s] for k, s in MAPS)
+    gpu_ms = sum(v["ms_per_step"] for v in kernels.values())
+    roofline = {
+        "bound": "hbm", "kernel": top,
+        "achieved": None if achieved is None else round(achieved, 1),
+        "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": None if achieved is None else round(achieved / peaks["hbm_gbs"], 4),
+        "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured"
+        else "fallback 6650 GB/s",
+        "traffic": None,
+        "algorithmic_bytes_per_step": top_bytes,
+        "kernel_ms_per_step": round(top_ms, 4),
+        "launches_per_step": kernels[top]["launches_per_step"],
+        "whole_step": {
+            "algorithmic_bytes_fused": stage_bytes,
+            "algorithmic_bytes_with_kernel_map": stage_bytes_with_map,
+            "gpu_busy_ms": round(gpu_ms, 4),
+            "gbs_over_gpu_busy_time": round(stage_bytes / (gpu_ms * 1e-3) / 1e9, 1),
+            "gbs_over_step_time": round(stage_bytes / (ms_total / args.steps * 1e-3) / 1e9, 1),
+        },
+        "kernels": {k: {"ms_per_step": round(v["ms_per_step"], 4),
+                        "launches_per_step": v["launches_per_step"]}
+                    for k, v in sorted(kernels.items(), key=lambda kv: -kv[1]["ms_per_step"])},
+    }
+
+    # ---- CPU baseline on this box's host cores (bounded) ---------------------------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        v, ms, done, cores = run_cpu(3, 1, coords, bd, min_seconds=10.0)
+        cpu = {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{done} full steps of the same 4-cloud batch ({ms:.1f} ms/step)"}
+
+    h2d = h_coords.numel() * 4 + h_bd.numel() * 8
+    d2h = sum((k ** 3 + 1) * 4 + k ** 3 * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8 + 32
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": workload_config(S),
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / args.steps, 4)},
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "wall_s": round(t_wall, 3),
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,17 @@ typedef struct {
 const char *mn_last_error(void);
 int mn_version(void);
 
+/* Instrumentation (no counterpart in the reference, which only times whole
+ * stages in TimeGather/TimeGEMM/TimeScatter): number of kernels this library
+ * has launched so far; and, while enabled, a CUDA-event pair around every
+ * launch.  mn_profile_report waits for the recorded events, writes one text
+ * line "kernel launches total_ms" per kernel name into buf, clears the record
+ * and returns the bytes written.  Profiling creates events, so keep it off
+ * inside timed regions and stream captures. */
+long long mn_launch_count(void);
+void mn_profile_enable(int on);
+int mn_profile_report(char *buf, int buf_bytes);
+
 /* ---- Map step ------------------------------------------------------------ */
 
 /* Bounding box of up to two coordinate arrays (b may be NULL):

@@ -41,6 +41,9 @@ class KeySpec(ctypes.Structure):
 PROTOTYPES = {
     "mn_last_error": (ctypes.c_char_p, []),
     "mn_version": (c_int, []),
+    "mn_launch_count": (ctypes.c_longlong, []),
+    "mn_profile_enable": (None, [c_int]),
+    "mn_profile_report": (c_int, [ctypes.c_char_p, c_int]),
     "mn_bbox": (c_int, [c_ptr, c_i64, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_keyspec_make": (c_int, [c_ptr, c_int, c_i64, ctypes.c_int32, ctypes.POINTER(KeySpec)]),
     "mn_pack_keys": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr, ctypes.POINTER(KeySpec),

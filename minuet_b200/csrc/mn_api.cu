@@ -2,7 +2,11 @@
 // live in mn_map_keys.cu.
 #include "mn_common.cuh"
 
+#include <atomic>
 #include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
 
 namespace mn {
 
@@ -15,9 +19,77 @@ void set_error(const char *fmt, ...) {
   va_end(ap);
 }
 
+// ---- launch counter and optional per-kernel event timing -------------------
+namespace {
+constexpr int kMaxProfiled = 4096;
+struct ProfEntry {
+  const char *name;
+  cudaEvent_t begin, end;
+};
+std::atomic<long long> g_launches{0};
+bool g_profiling = false;
+std::mutex g_prof_mutex;
+std::vector<ProfEntry> g_prof;
+}  // namespace
+
+LaunchScope::LaunchScope(const char *name, cudaStream_t st) : st_(st), slot_(-1) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!g_profiling) return;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  if ((int)g_prof.size() >= kMaxProfiled) return;
+  ProfEntry e{name, nullptr, nullptr};
+  if (cudaEventCreate(&e.begin) != cudaSuccess || cudaEventCreate(&e.end) != cudaSuccess) return;
+  cudaEventRecord(e.begin, st);
+  slot_ = (int)g_prof.size();
+  g_prof.push_back(e);
+}
+
+LaunchScope::~LaunchScope() {
+  if (slot_ < 0) return;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  cudaEventRecord(g_prof[slot_].end, st_);
+}
+
 }  // namespace mn
 
 using namespace mn;
+
+extern "C" long long mn_launch_count(void) { return g_launches.load(); }
+
+extern "C" void mn_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_profiling = on != 0;
+}
+
+// Waits for the recorded events and writes one line per distinct kernel name:
+// "name launches total_ms".  Returns the number of bytes written and clears
+// the record.
+extern "C" int mn_profile_report(char *buf, int buf_bytes) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  std::vector<std::string> names;
+  std::vector<int> counts;
+  std::vector<double> totals;
+  for (auto &e : g_prof) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(e.end) == cudaSuccess) cudaEventElapsedTime(&ms, e.begin, e.end);
+    cudaEventDestroy(e.begin);
+    cudaEventDestroy(e.end);
+    size_t i = 0;
+    for (; i < names.size(); i++) if (names[i] == e.name) break;
+    if (i == names.size()) { names.push_back(e.name); counts.push_back(0); totals.push_back(0.0); }
+    counts[i]++;
+    totals[i] += ms;
+  }
+  g_prof.clear();
+  int used = 0;
+  for (size_t i = 0; i < names.size() && buf != nullptr; i++) {
+    int n = snprintf(buf + used, buf_bytes > used ? buf_bytes - used : 0, "%s %d %.6f\n",
+                     names[i].c_str(), counts[i], totals[i]);
+    if (n < 0 || used + n >= buf_bytes) break;
+    used += n;
+  }
+  return used;
+}
 
 extern "C" const char *mn_last_error(void) { return g_error; }
 

@@ -38,6 +38,24 @@ void set_error(const char *fmt, ...);
 
 #define MN_CHECK_LAUNCH() MN_CHECK_CUDA(cudaGetLastError())
 
+// Counts the launch and, while profiling is on (mn_profile_enable), brackets it
+// with a pair of CUDA events on the launching stream.
+struct LaunchScope {
+  LaunchScope(const char *name, cudaStream_t st);
+  ~LaunchScope();
+  cudaStream_t st_;
+  int slot_;
+};
+
+#define MN_LAUNCH(name, st, ...)                  \
+  do {                                            \
+    {                                             \
+      ::mn::LaunchScope scope__(name, st);        \
+      __VA_ARGS__;                                \
+    }                                             \
+    MN_CHECK_LAUNCH();                            \
+  } while (0)
+
 #define MN_RETURN_IF(expr)              \
   do {                                  \
     mn_status s__ = (expr);             \

@@ -327,11 +327,14 @@ mn_status run_gather(const ConvLayout &L, const ConvBuffers &b, int64_t S, int64
   g.row_bytes = row_bytes;
   g.lanes_per_row = lpr;
   const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(div_up(S, 32), 8));
+  {
+  LaunchScope scope("gather_kernel", st);
   switch (vec) {
     case 16: gather_kernel<16><<<blocks, 256, 0, st>>>(g, L.plan); break;
     case 8: gather_kernel<8><<<blocks, 256, 0, st>>>(g, L.plan); break;
     case 4: gather_kernel<4><<<blocks, 256, 0, st>>>(g, L.plan); break;
     default: gather_kernel<2><<<blocks, 256, 0, st>>>(g, L.plan); break;
+  }
   }
   MN_CHECK_LAUNCH();
   return MN_OK;
@@ -378,10 +381,13 @@ mn_status run_scatter_t(const ConvLayout &L, const ConvBuffers &b, int64_t T_row
     else if (need <= 16) scatter_kernel<T, VE, 16><<<blocks, 256, 0, st>>>(a, L.plan);   \
     else scatter_kernel<T, VE, 32><<<blocks, 256, 0, st>>>(a, L.plan);                   \
   } while (0)
+  {
+  LaunchScope scope("scatter_kernel", st);
   if (vec_elems * e == 16) { MN_SCATTER(16 / e); }
   else if (vec_elems * e == 8) { MN_SCATTER(8 / e); }
   else if (vec_elems * e == 4) { MN_SCATTER(4 / e); }
   else { MN_SCATTER(1); }
+  }
 #undef MN_SCATTER
   MN_CHECK_LAUNCH();
   return MN_OK;
@@ -429,6 +435,8 @@ mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *siz
   tab.tile_prefix[0] = 0;
   for (int p = 0; p < np; p++) tab.tile_prefix[p + 1] = tab.tile_prefix[p] + (int)div_up(tab.rows[p], kGemmTM);
   const dim3 grid(tab.tile_prefix[np], (unsigned)div_up(c_out, kGemmTN));
+  {
+  LaunchScope scope("gemm_simt_kernel", st);
   switch (dtype) {
     case MN_F32:
       gemm_simt_kernel<float><<<grid, 256, 0, st>>>(tab, static_cast<const float *>(weights), order,
@@ -442,6 +450,7 @@ mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *siz
       gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
           tab, static_cast<const __nv_bfloat16 *>(weights), order, (int)c_in, (int)c_out);
       break;
+  }
   }
   MN_CHECK_LAUNCH();
   return MN_OK;

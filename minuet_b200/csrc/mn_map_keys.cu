@@ -209,11 +209,9 @@ mn_status launch_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb
   int blocks = (int)std::min<int64_t>(kBBoxMaxBlocks, std::max<int64_t>(1, div_up(elems, kBBoxThreads * 16)));
   int32_t *partial = ws.take<int32_t>((size_t)kBBoxMaxBlocks * 8);
   MN_CHECK_WS(ws);
-  bbox_partial_kernel<<<blocks, kBBoxThreads, 0, st>>>(na > 0 ? a : nullptr, na,
-                                                       nb > 0 ? b : nullptr, nb, ndim, partial);
-  MN_CHECK_LAUNCH();
-  bbox_final_kernel<<<1, 256, 0, st>>>(partial, blocks, minmax_dev);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("bbox_partial_kernel", st, bbox_partial_kernel<<<blocks, kBBoxThreads, 0, st>>>(na > 0 ? a : nullptr, na,
+                                                       nb > 0 ? b : nullptr, nb, ndim, partial));
+  MN_LAUNCH("bbox_final_kernel", st, bbox_final_kernel<<<1, 256, 0, st>>>(partial, blocks, minmax_dev));
   return MN_OK;
 }
 
@@ -235,9 +233,8 @@ mn_status launch_pack(const int32_t *coords, int64_t n, int ndim,
   }
   if (batch_dims == nullptr) num_clouds = 1;
   int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, kPackThreads * 4));
-  pack_kernel<<<blocks, kPackThreads, 0, st>>>(coords, n, ndim, batch_dims, (int)num_clouds,
-                                               p, keys_out, status_dev);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("pack_kernel", st, pack_kernel<<<blocks, kPackThreads, 0, st>>>(coords, n, ndim, batch_dims, (int)num_clouds,
+                                               p, keys_out, status_dev));
   return MN_OK;
 }
 

@@ -465,8 +465,11 @@ mn_status run_search(int mode, const uint64_t *rows, int64_t n_rows, const uint6
   a.kernel_map = kernel_map; a.hit_words = hit_words; a.tile_counts = tile_counts;
   a.n_tiles = (int)div_up(n_rows, kQTile);
   for (int k = 0; k < 4; k++) a.shift[k] = spec.shift[k];
-  if (mode == kMap) search_kernel<kMap><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
-  else search_kernel<kBits><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+  {
+    LaunchScope scope(mode == kMap ? "search_kernel<map>" : "search_kernel<bits>", st);
+    if (mode == kMap) search_kernel<kMap><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+    else search_kernel<kBits><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+  }
   MN_CHECK_LAUNCH();
   return MN_OK;
 }
@@ -552,9 +555,8 @@ extern "C" mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int6
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(kernel_map != nullptr, "sizes: null kernel map");
   const int n_tiles = (int)div_up(T, kQTile);
-  map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, nullptr,
-                                                                     sizes_out);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("map_count_kernel", st, map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, nullptr,
+                                                                     sizes_out));
   return MN_OK;
 }
 
@@ -578,18 +580,15 @@ extern "C" mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int6
   int32_t *counts = ws.take<int32_t>((size_t)O * n_tiles);
   int32_t *scratch = ws.take<int32_t>(4 * MN_MAX_OFFSETS);
   MN_CHECK_WS(ws);
-  map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, counts,
-                                                                     nullptr);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("map_count_kernel", st, map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, counts,
+                                                                     nullptr));
   PlanArgs p{};
   p.counts_a = counts; p.tiles_a = n_tiles; p.num_offsets = (int)O; p.reorder = 0;
   p.sizes_raw = nullptr; p.pos_of = scratch; p.order_out = scratch + MN_MAX_OFFSETS;
   p.sizes_out = scratch + 2 * MN_MAX_OFFSETS;
-  plan_kernel<<<1, 1024, 0, st>>>(p);
-  MN_CHECK_LAUNCH();
-  map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
-      kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
+  MN_LAUNCH("map_masks_kernel", st, map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
+      kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out));
   return MN_OK;
 }
 
@@ -652,8 +651,7 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
     PlanArgs p{};
     p.counts_a = counts_t; p.tiles_a = 0; p.num_offsets = (int)O; p.reorder = 0;
     p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
-    plan_kernel<<<1, 1024, 0, st>>>(p);
-    MN_CHECK_LAUNCH();
+    MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
     return MN_OK;
   }
   MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
@@ -672,15 +670,13 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   p.counts_b = mirrored ? nullptr : counts_s; p.tiles_b = tiles_s;
   p.num_offsets = (int)O; p.reorder = reorder ? 1 : 0;
   p.sizes_raw = nullptr; p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
-  plan_kernel<<<1, 1024, 0, st>>>(p);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
 
   EmitArgs e{};
   e.words_t = words_t; e.words_s = words_s; e.prefix_t = counts_t; e.prefix_s = counts_s;
   e.pos_of = pos_of; e.target_masks = target_masks_out; e.source_masks = source_masks_out;
   e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s; e.num_offsets = (int)O;
   for (int64_t o = 0; o < O; o++) e.mirror[o] = mirrored ? neg[o] : (uint8_t)o;
-  emit_masks_kernel<<<tiles_t + tiles_s, kQThreads, 0, st>>>(e);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("emit_masks_kernel", st, emit_masks_kernel<<<tiles_t + tiles_s, kQThreads, 0, st>>>(e));
   return MN_OK;
 }

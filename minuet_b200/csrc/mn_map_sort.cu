@@ -375,10 +375,10 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
   int32_t *vin = vals, *vout = vals_tmp;
   bool first = true;
   for (int shift = begin_bit; shift < end_bit; shift += 8) {
-    radix_hist_kernel<<<nblocks, kRsThreads, 0, st>>>(kin, n, shift, block_hist, nblocks);
-    MN_CHECK_LAUNCH();
-    radix_scan_kernel<<<kRadix / kRsWarps, kRsThreads, 0, st>>>(block_hist, nblocks, digit_total);
-    MN_CHECK_LAUNCH();
+    MN_LAUNCH("radix_hist_kernel", st, radix_hist_kernel<<<nblocks, kRsThreads, 0, st>>>(kin, n, shift, block_hist, nblocks));
+    MN_LAUNCH("radix_scan_kernel", st, radix_scan_kernel<<<kRadix / kRsWarps, kRsThreads, 0, st>>>(block_hist, nblocks, digit_total));
+    {
+    LaunchScope scope("radix_scatter_kernel", st);
     if (has_vals) {
       radix_scatter_kernel<true><<<nblocks, kRsThreads, 0, st>>>(
           kin, (first && iota_vals) ? nullptr : vin, n, shift, block_hist, nblocks,
@@ -386,6 +386,7 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
     } else {
       radix_scatter_kernel<false><<<nblocks, kRsThreads, 0, st>>>(
           kin, nullptr, n, shift, block_hist, nblocks, digit_total, kout, nullptr);
+    }
     }
     MN_CHECK_LAUNCH();
     std::swap(kin, kout);
@@ -424,8 +425,7 @@ extern "C" mn_status mn_arg_sort_coordinates(const int32_t *coords, int64_t n, i
   MN_RETURN_IF(launch_radix_sort(keys, keys_tmp, vals, vals_tmp, true, n, 0, spec->total_bits,
                                  ws, &in_tmp, st));
   const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, 256));
-  widen_index_kernel<<<blocks, 256, 0, st>>>(in_tmp ? vals_tmp : vals, n, index_out);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("widen_index_kernel", st, widen_index_kernel<<<blocks, 256, 0, st>>>(in_tmp ? vals_tmp : vals, n, index_out));
   return MN_OK;
 }
 
@@ -436,8 +436,7 @@ extern "C" mn_status mn_unique_coordinates(const int32_t *coords, int64_t n, int
   MN_CHECK_ARG(n >= 0 && ndim >= 1 && ndim <= MN_MAX_NDIM, "unique: bad n/ndim");
   MN_CHECK_ARG(indices_out != nullptr, "unique: null indices");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  zero_index0_kernel<<<1, 1, 0, st>>>(indices_out);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("zero_index0_kernel", st, zero_index0_kernel<<<1, 1, 0, st>>>(indices_out));
   if (n == 0) return MN_OK;
   MN_CHECK_ARG(coords != nullptr && unique_out != nullptr, "unique: null pointer");
   MN_CHECK_ARG(n < (1ll << 31), "unique: n exceeds 2^31-1");
@@ -448,12 +447,9 @@ extern "C" mn_status mn_unique_coordinates(const int32_t *coords, int64_t n, int
   MN_CHECK_WS(ws);
   RowsView view{coords, batch_dims, batch_dims ? (int)num_clouds : 1, ndim, n};
   CoordSink sink{coords, ndim, unique_out, indices_out};
-  unique_count_kernel<RowsView><<<nblocks, kUqThreads, 0, st>>>(view, counts);
-  MN_CHECK_LAUNCH();
-  scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, nullptr);
-  MN_CHECK_LAUNCH();
-  unique_compact_kernel<RowsView, CoordSink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("unique_count_kernel", st, unique_count_kernel<RowsView><<<nblocks, kUqThreads, 0, st>>>(view, counts));
+  MN_LAUNCH("scan_blocks_kernel", st, scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, nullptr));
+  MN_LAUNCH("unique_compact_kernel", st, unique_compact_kernel<RowsView, CoordSink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts));
   return MN_OK;
 }
 
@@ -494,17 +490,13 @@ extern "C" mn_status mn_downsample_coordinates(
   const uint64_t *sorted = in_tmp ? keys_tmp : keys;
   KeysView view{sorted, n};
   KeySink sink{sorted, *spec, keys_out, unique_out};
-  unique_count_kernel<KeysView><<<nblocks, kUqThreads, 0, st>>>(view, counts);
-  MN_CHECK_LAUNCH();
-  scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, count_dev);
-  MN_CHECK_LAUNCH();
-  unique_compact_kernel<KeysView, KeySink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts);
-  MN_CHECK_LAUNCH();
+  MN_LAUNCH("unique_count_kernel", st, unique_count_kernel<KeysView><<<nblocks, kUqThreads, 0, st>>>(view, counts));
+  MN_LAUNCH("scan_blocks_kernel", st, scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, count_dev));
+  MN_LAUNCH("unique_compact_kernel", st, unique_compact_kernel<KeysView, KeySink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts));
   if (batch_dims != nullptr && out_batch_dims != nullptr) {
     const int nb = (int)num_clouds + 1;
-    cloud_starts_kernel<<<(nb + 127) / 128, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
-                                                           (int)num_clouds, out_batch_dims);
-    MN_CHECK_LAUNCH();
+    MN_LAUNCH("cloud_starts_kernel", st, cloud_starts_kernel<<<(nb + 127) / 128, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
+                                                           (int)num_clouds, out_batch_dims));
   }
   return MN_OK;
 }
