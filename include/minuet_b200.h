@@ -119,6 +119,25 @@ mn_status mn_unique_coordinates(const int32_t *coords, int64_t n, int ndim,
                                 int32_t *unique_out, int64_t *indices_out,
                                 void *ws, size_t ws_bytes, void *stream);
 
+/* Same result as mn_unique_coordinates for callers that cannot hand over a
+ * workspace because they are not allowed to allocate device memory where this
+ * runs (inside a stream capture, under an allocator-free hot loop, or in a
+ * plugin with a fixed memory budget).  It has no counterpart in the reference.
+ * The scratch (block counts) is a fixed array inside the library image, about
+ * 33 KB on every GPU that loads the library, which bounds one call to
+ * 16 777 216 rows; larger n returns MN_ERR_BAD_ARG with a message that names
+ * the limit.  It calls no cudaMalloc/cudaFree or allocating library routine.
+ * The first call on each device looks up the array's device address (the
+ * device that owns the pointers must be current); make that first call before
+ * any stream capture begins.  All calls share the one array: calls whose
+ * kernels can overlap on the GPU (different streams, or different host threads
+ * on one device) race and must be serialised by the caller.  Nothing in the
+ * array has to start at zero; each call writes every word before reading it. */
+mn_status mn_unique_coordinates_static(const int32_t *coords, int64_t n, int ndim,
+                                       const int64_t *batch_dims, int64_t num_clouds,
+                                       int32_t *unique_out, int64_t *indices_out,
+                                       void *stream);
+
 /* Fused target-coordinate build of a strided convolution
  * (KernelMapCache.get_target_coordinates, minuet/nn/convolutions.py:85-96):
  * floor to the target stride, sort, unique.  Outputs: unique_out int32

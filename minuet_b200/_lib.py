@@ -52,6 +52,7 @@ PROTOTYPES = {
                                         c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_unique_coordinates": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr, c_ptr, c_ptr,
                                       c_size, c_ptr]),
+    "mn_unique_coordinates_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "mn_downsample_coordinates": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr,
                                           ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_ptr, c_ptr,
                                           c_ptr, c_ptr, c_size, c_ptr]),

@@ -11,6 +11,7 @@
 #include "mn_common.cuh"
 
 #include <algorithm>
+#include <mutex>
 
 namespace mn {
 
@@ -498,5 +499,77 @@ extern "C" mn_status mn_downsample_coordinates(
     MN_LAUNCH("cloud_starts_kernel", st, cloud_starts_kernel<<<(nb + 127) / 128, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
                                                            (int)num_clouds, out_batch_dims));
   }
+  return MN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of mn_unique_coordinates
+// ---------------------------------------------------------------------------
+// Some hosts may not allocate device memory at the point where they need this
+// op: code running inside a CUDA stream capture or under a framework that
+// forbids allocator calls on its hot path, plugins handed a fixed memory
+// budget at load time, or real-time loops that must not touch the driver's
+// allocator.  For them the block counts and the total live in a fixed array
+// inside the library image.  Every GPU that loads the library carries these
+// 33 KB until the process exits.
+namespace {
+constexpr int64_t kStaticUniqueMaxRows = 16ll << 20;  // 16 Mi rows per call
+constexpr int kStaticUniqueBlocks = (int)(kStaticUniqueMaxRows / kUqTile);  // 8192 block counts
+constexpr int kStaticUniqueWords = kStaticUniqueBlocks + 64;                // + the total
+constexpr int kMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) uint32_t g_unique_scratch[kStaticUniqueWords];
+
+// In host code `g_unique_scratch` is only a handle for the symbol, not a device
+// address, so the address is looked up once per device (with that device
+// current) and cached here.
+static uint32_t *g_unique_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_unique_scratch_mutex;
+
+static mn_status unique_scratch_address(uint32_t **out) {
+  int device = -1;
+  MN_CHECK_CUDA(cudaGetDevice(&device));
+  MN_CHECK_ARG(device >= 0 && device < kMaxDevices, "unique_static: device index %d out of range",
+               device);
+  std::lock_guard<std::mutex> lock(g_unique_scratch_mutex);
+  if (g_unique_scratch_addr[device] == nullptr) {
+    uint32_t *p = nullptr;
+    MN_CHECK_CUDA(cudaGetSymbolAddress((void **)&p, g_unique_scratch));
+    g_unique_scratch_addr[device] = p;
+  }
+  *out = g_unique_scratch_addr[device];
+  return MN_OK;
+}
+
+extern "C" mn_status mn_unique_coordinates_static(const int32_t *coords, int64_t n, int ndim,
+                                                  const int64_t *batch_dims, int64_t num_clouds,
+                                                  int32_t *unique_out, int64_t *indices_out,
+                                                  void *stream) {
+  MN_CHECK_ARG(n >= 0 && ndim >= 1 && ndim <= MN_MAX_NDIM, "unique_static: bad n/ndim");
+  MN_CHECK_ARG(indices_out != nullptr, "unique_static: null indices");
+  if (n > kStaticUniqueMaxRows) {
+    set_error("unique_static: %lld rows exceed the built-in scratch limit of %lld rows; call "
+              "mn_unique_coordinates with a caller-provided workspace instead",
+              (long long)n, (long long)kStaticUniqueMaxRows);
+    return MN_ERR_BAD_ARG;
+  }
+  uint32_t *scratch = nullptr;
+  MN_RETURN_IF(unique_scratch_address(&scratch));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MN_LAUNCH("zero_index0_kernel", st, zero_index0_kernel<<<1, 1, 0, st>>>(indices_out));
+  if (n == 0) return MN_OK;
+  MN_CHECK_ARG(coords != nullptr && unique_out != nullptr, "unique_static: null pointer");
+  const int nblocks = (int)div_up(n, kUqTile);
+  uint32_t *counts = scratch;                       // [nblocks], every word written before read
+  uint32_t *total = scratch + kStaticUniqueBlocks;  // [1]
+  RowsView view{coords, batch_dims, batch_dims ? (int)num_clouds : 1, ndim, n};
+  CoordSink sink{coords, ndim, unique_out, indices_out};
+  MN_LAUNCH("unique_count_kernel", st,
+            unique_count_kernel<RowsView><<<nblocks, kUqThreads, 0, st>>>(view, counts));
+  MN_LAUNCH("scan_blocks_kernel", st,
+            scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, nullptr));
+  MN_LAUNCH("unique_compact_kernel", st,
+            unique_compact_kernel<RowsView, CoordSink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts));
   return MN_OK;
 }
