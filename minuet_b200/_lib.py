@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libminuet_b200.so")
+# MINUET_B200_LIB points at another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("MINUET_B200_LIB") or os.path.join(_HERE, "libminuet_b200.so")
 
 MN_OK, MN_ERR_BAD_ARG, MN_ERR_UNSUPPORTED, MN_ERR_WORKSPACE, MN_ERR_CUDA, MN_ERR_DEVICE = range(6)
 MN_F32, MN_F16, MN_BF16 = 0, 1, 2

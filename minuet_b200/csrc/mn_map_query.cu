@@ -31,11 +31,17 @@ namespace mn {
 
 namespace {
 
-constexpr int kQThreads = 256;
+#ifndef MN_QTHREADS
+#define MN_QTHREADS 128
+#endif
+constexpr int kQThreads = MN_QTHREADS;
 constexpr int kQWarps = kQThreads / 32;
 constexpr int kQRows = 4;                    // rows per thread
-constexpr int kQTile = kQThreads * kQRows;   // 1024 rows per block
-constexpr int kQWindow = 3072;               // table keys staged per pass (24 KB)
+constexpr int kQTile = kQThreads * kQRows;   // 512 rows per block
+constexpr int kQWindow = 2048;               // table keys staged per pass
+constexpr int kQHash = 2048;                 // slots of the shared-memory hash of cells
+constexpr uint32_t kHashEmpty = 0xffffffffu;
+constexpr uint32_t kQPad = 4096;             // slack below/above the window in relative keys
 constexpr uint64_t kKeyInf = ~0ull;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
@@ -80,12 +86,14 @@ struct SearchArgs {
   int32_t *tile_counts;  // kBits: [O, n_tiles]
   int32_t n_tiles;
   int32_t shift[4];
+  int32_t fast_ok;       // every last-dimension offset is within +-kQPad
 };
 
 enum SearchMode { kMap = 0, kBits = 1 };
 
 // lower bound of q in win[a, b); trip count depends only on b - a (uniform)
-__device__ __forceinline__ int lower_bound_win(const uint64_t *win, int a, int b, uint64_t q) {
+template <typename K>
+__device__ __forceinline__ int lower_bound_win(const K *win, int a, int b, K q) {
   int base = a, len = b - a;
   while (len > 1) {
     const int half = len >> 1;
@@ -95,20 +103,61 @@ __device__ __forceinline__ int lower_bound_win(const uint64_t *win, int a, int b
   return (len == 1 && win[base] < q) ? base + 1 : base;
 }
 
+// One result of one (row, offset): either a kernel-map entry or a hit bit.
 template <int kMode>
-__global__ void __launch_bounds__(kQThreads)
-search_kernel(const SearchArgs a, const __grid_constant__ OffsetTable tab) {
-  __shared__ uint64_t s_win[kQWindow];
+__device__ __forceinline__ void emit(const SearchArgs &a, int o, int64_t row, bool vec_ok,
+                                     const bool (&live)[kQRows], const int32_t (&idx)[kQRows],
+                                     uint32_t (&bits)[kQRows]) {
+  if (kMode == kMap) {
+    int32_t *dst = a.kernel_map + (int64_t)o * a.n_rows + row;
+    if (vec_ok && live[kQRows - 1]) {
+      *reinterpret_cast<int4 *>(dst) = make_int4(idx[0], idx[1], idx[2], idx[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kQRows; j++) if (live[j]) dst[j] = idx[j];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kQRows; j++) bits[j] |= (idx[j] >= 0 ? 1u : 0u) << o;
+  }
+}
+
+__device__ __forceinline__ uint32_t hash_slot(uint32_t k) {
+  return (k * 0x9E3779B1u) >> 21;  // top 11 bits: kQHash = 2048 slots
+}
+
+// A block owns 512 consecutive rows, a thread 4 consecutive rows.
+//
+// Fast path (the table window that can match the tile, over ALL offsets, holds
+// at most kQWindow keys spanning less than 2^32 - 4*kQPad, and no offset moves
+// the last dimension by more than kQPad): two warp-cooperative 32-ary searches
+// find the window of the sorted table.  The block stages that sorted block in
+// shared memory as a hash set of CELLS: 32 consecutive values of the last
+// dimension share one slot {cell id, 32-bit occupancy mask} (plus the position
+// of the cell's first key when kernel-map entries are wanted; the rest follows
+// by popcount because the table is sorted).  The offsets of a group differ only
+// in the last dimension, so one probe usually answers the whole group, and the
+// probes of a thread do not depend on each other.
+// General path (huge or wide windows): per-group windows, 64-bit keys, staged
+// when they fit, binary-searched in global memory otherwise.
+template <int kMode>
+__global__ void __launch_bounds__(kQThreads, 8)
+search_kernel(const __grid_constant__ SearchArgs a, const __grid_constant__ OffsetTable tab) {
+  __shared__ __align__(16) uint64_t s_win[kQWindow + 2];          // hash slots / general path
+  __shared__ uint16_t s_hpos[kMode == kMap ? kQHash : 1];         // first position of a cell
   __shared__ int64_t s_delta[MN_MAX_OFFSETS];
   __shared__ int64_t s_glo[MN_MAX_OFFSETS], s_ghi[MN_MAX_OFFSETS];
   __shared__ int32_t s_stage_gbeg[MN_MAX_OFFSETS + 1];
   __shared__ int32_t s_counts[MN_MAX_OFFSETS];
   __shared__ int32_t s_num_stages;
+  static_assert(kQHash <= kQWindow + 2, "the hash slots live in s_win");
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int O = tab.num_offsets, G = tab.num_groups;
+  const int last = tab.ndim - 1;
   const int64_t tile0 = (int64_t)blockIdx.x * kQTile;
   const int tile_rows = (int)min((int64_t)kQTile, a.n_rows - tile0);
+  const int64_t row0 = tile0 + tid * kQRows;
 
   for (int o = tid; o < O; o += kQThreads) {
     int64_t d = 0;
@@ -119,110 +168,254 @@ search_kernel(const SearchArgs a, const __grid_constant__ OffsetTable tab) {
 
   uint64_t key[kQRows];
   bool live[kQRows];
+  if (tid * kQRows + kQRows <= tile_rows && (reinterpret_cast<uintptr_t>(a.rows) & 15) == 0) {
+    const ulonglong2 v0 = __ldg(reinterpret_cast<const ulonglong2 *>(a.rows + row0));
+    const ulonglong2 v1 = __ldg(reinterpret_cast<const ulonglong2 *>(a.rows + row0) + 1);
+    key[0] = v0.x; key[1] = v0.y; key[2] = v1.x; key[3] = v1.y;
 #pragma unroll
-  for (int j = 0; j < kQRows; j++) {
-    const int r = j * kQThreads + tid;
-    live[j] = r < tile_rows;
-    key[j] = live[j] ? __ldg(a.rows + tile0 + r) : 0ull;
+    for (int j = 0; j < kQRows; j++) live[j] = true;
+  } else {
+#pragma unroll
+    for (int j = 0; j < kQRows; j++) {
+      live[j] = tid * kQRows + j < tile_rows;
+      key[j] = live[j] ? __ldg(a.rows + row0 + j) : 0ull;
+    }
   }
   const uint64_t kfirst = __ldg(a.rows + tile0);
   const uint64_t klast = __ldg(a.rows + tile0 + tile_rows - 1);
+  const bool vec_ok = kMode == kMap && (a.n_rows & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(a.kernel_map) & 15) == 0;
   __syncthreads();
 
-  // (1) table window of every group
-  for (int g = warp; g < G; g += kQWarps) {
-    const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
-    const uint64_t qlo = kfirst + (uint64_t)s_delta[tab.member[mb]];
-    const uint64_t qhi = klast + (uint64_t)s_delta[tab.member[me - 1]];
-    const int64_t lo = warp_bound(a.table, a.n_table, qlo, false, lane);
-    const int64_t hi = warp_bound(a.table, a.n_table, qhi, true, lane);
-    if (lane == 0) { s_glo[g] = lo; s_ghi[g] = max(lo, hi); }
+  // window of the table over all offsets: groups are ordered by delta
+  __shared__ int64_t s_union[2];
+  if (warp < 2) {
+    const uint64_t q = warp == 0 ? kfirst + (uint64_t)s_delta[tab.member[0]]
+                                 : klast + (uint64_t)s_delta[tab.member[O - 1]];
+    const int64_t r = warp_bound(a.table, a.n_table, q, warp == 1, lane);
+    if (lane == 0) s_union[warp] = r;
   }
+  uint2 *slots = reinterpret_cast<uint2 *>(s_win);
+  for (int i = tid; i < kQHash; i += kQThreads) slots[i] = make_uint2(kHashEmpty, 0u);
   __syncthreads();
-  // (2) merge adjacent groups into staging passes
-  if (tid == 0) {
-    int ns = 0, g = 0;
-    while (g < G) {
-      s_stage_gbeg[ns++] = g;
-      int64_t lo = s_glo[g], hi = s_ghi[g];
-      g++;
-      if (hi - lo <= kQWindow) {
-        while (g < G) {
-          const int64_t nlo = min(lo, s_glo[g]), nhi = max(hi, s_ghi[g]);
-          if (nhi - nlo > kQWindow) break;
-          lo = nlo; hi = nhi; g++;
-        }
-      }
-    }
-    s_stage_gbeg[ns] = G;
-    s_num_stages = ns;
+  const int64_t ulo = s_union[0], uhi = max(s_union[0], s_union[1]);
+  const int wn = (int)min(uhi - ulo, (int64_t)kQWindow + 1);
+  bool fast = a.fast_ok && uhi - ulo <= kQWindow;
+  uint64_t base = 0;
+  if (fast && wn > 0) {
+    base = __ldg(a.table + ulo);
+    fast = __ldg(a.table + uhi - 1) - base < 0xffffffffull - 4ull * kQPad;
   }
-  __syncthreads();
 
   uint32_t bits[kQRows] = {0u, 0u, 0u, 0u};
-  const int num_stages = s_num_stages;
-  for (int st = 0; st < num_stages; st++) {
-    const int gb = s_stage_gbeg[st], ge = s_stage_gbeg[st + 1];
-    int64_t lo = s_glo[gb], hi = s_ghi[gb];
-    for (int g = gb + 1; g < ge; g++) { lo = min(lo, s_glo[g]); hi = max(hi, s_ghi[g]); }
-    const int64_t wn = hi - lo;
-    const bool staged = wn <= kQWindow;
-    if (staged) {
-      for (int i = tid; i < (int)wn; i += kQThreads) s_win[i] = __ldg(a.table + lo + i);
+  if (fast) {
+    // keys relative to base - kQPad, so that "query below the window" needs no test
+    for (int w = tid; w < wn; w += kQThreads) {
+      const uint64_t tk = __ldg(a.table + ulo + w);
+      const uint32_t k = (uint32_t)(tk - base) + kQPad;
+      const uint32_t cell = k >> 5;
+      uint32_t h = hash_slot(cell);
+      for (int probe = 0; probe < kQHash; probe++) {
+        const uint32_t old = atomicCAS(&slots[h].x, kHashEmpty, cell);
+        if (old == kHashEmpty || old == cell) break;
+        h = (h + 1) & (kQHash - 1);
+      }
+      atomicOr(&slots[h].y, 1u << (k & 31));
+      if (kMode == kMap) {
+        // the table is sorted: exactly one key of a cell has a predecessor in another cell
+        const bool first = w == 0 ||
+            (((uint32_t)(__ldg(a.table + ulo + w - 1) - base) + kQPad) >> 5) != cell;
+        if (first) s_hpos[h] = (uint16_t)w;
+      }
     }
     __syncthreads();
-    for (int g = gb; g < ge; g++) {
+    int64_t rel[kQRows];
+#pragma unroll
+    for (int j = 0; j < kQRows; j++) rel[j] = (int64_t)(key[j] - base) + kQPad;
+    for (int g = 0; g < G; g++) {
       const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
-      const int64_t glo = s_glo[g], ghi = s_ghi[g];
+      const int o_first = tab.member[mb];
+      const int e_first = tab.off[o_first][last];
+      const int e_span = tab.off[tab.member[me - 1]][last] - e_first;  // >= 0, members ascend
+      const int64_t dg = s_delta[o_first] - e_first;  // the last dimension sits at bit 0
+      // Per row: the 64 consecutive last-dimension values starting at the cell of
+      // the group's first query, as one 64-bit occupancy mask (low cell | high cell).
+      uint32_t sh[kQRows], mlo[kQRows], mhi[kQRows], slo[kQRows], shi[kQRows];
+      uint2 v[kQRows];
+      uint32_t c0[kQRows];
+      bool ok[kQRows];
 #pragma unroll
       for (int j = 0; j < kQRows; j++) {
-        if (live[j]) {
-        const uint64_t q0 = key[j] + (uint64_t)s_delta[tab.member[mb]];
-        int64_t pos;  // absolute index into the table
-        if (staged) {
-          pos = lo + lower_bound_win(s_win, (int)(glo - lo), (int)(ghi - lo), q0);
-        } else {
-          int64_t l = glo, h = ghi;
-          while (l < h) {
-            const int64_t mid = (l + h) >> 1;
-            if (__ldg(a.table + mid) < q0) l = mid + 1; else h = mid;
+        const uint64_t t = (uint64_t)(rel[j] + dg);
+        ok[j] = live[j] && t < 0xffffffffull - 2ull * kQPad;  // t +- kQPad stays inside 32 bits
+        const uint32_t q0 = (uint32_t)t + (uint32_t)e_first;
+        c0[j] = q0 >> 5;
+        sh[j] = q0 & 31;
+        slo[j] = hash_slot(c0[j]);
+        v[j] = slots[slo[j]];   // the four first probes are issued together
+      }
+#pragma unroll
+      for (int j = 0; j < kQRows; j++) {
+        for (int probe = 0; probe < kQHash && v[j].x != c0[j] && v[j].x != kHashEmpty; probe++) {
+          slo[j] = (slo[j] + 1) & (kQHash - 1);
+          v[j] = slots[slo[j]];
+        }
+        mlo[j] = (ok[j] && v[j].x == c0[j]) ? v[j].y : 0u;
+        mhi[j] = 0u;
+        shi[j] = 0u;
+        if (ok[j] && (int)sh[j] + e_span > 31) {  // the group reaches into the next cell(s)
+          const uint32_t c1 = c0[j] + 1;
+          uint32_t h = hash_slot(c1);
+          uint2 u = slots[h];
+          for (int probe = 0; probe < kQHash && u.x != c1 && u.x != kHashEmpty; probe++) {
+            h = (h + 1) & (kQHash - 1);
+            u = slots[h];
           }
-          pos = l;
+          mhi[j] = u.x == c1 ? u.y : 0u;
+          shi[j] = h;
+        }
+      }
+      if (kMode == kBits && e_span <= 32) {
+        bool any = false;
+#pragma unroll
+        for (int j = 0; j < kQRows; j++) any |= (mlo[j] | mhi[j]) != 0u;
+        if (!any) continue;  // no table key near any of the four rows for this group
+      }
+      for (int m = mb; m < me; m++) {
+        const int o = tab.member[m];
+        const int de = tab.off[o][last] - e_first;
+        int32_t idx[kQRows];
+#pragma unroll
+        for (int j = 0; j < kQRows; j++) {
+          const int b = (int)sh[j] + de;   // bit index into the 64-value strip (or beyond)
+          idx[j] = -1;
+          if (b < 32) {
+            if ((mlo[j] >> b) & 1u)
+              idx[j] = kMode == kMap
+                  ? (int32_t)(ulo + s_hpos[slo[j]] + __popc(mlo[j] & ((1u << b) - 1u))) : 0;
+          } else if (b < 64) {
+            if ((mhi[j] >> (b - 32)) & 1u)
+              idx[j] = kMode == kMap
+                  ? (int32_t)(ulo + s_hpos[shi[j]] + __popc(mhi[j] & ((1u << (b - 32)) - 1u))) : 0;
+          } else if (ok[j]) {   // offsets more than 63 apart inside one group: probe per member
+            const uint32_t q = (c0[j] << 5) + (uint32_t)b;
+            const uint32_t c = q >> 5;
+            uint32_t h = hash_slot(c);
+            uint2 u = slots[h];
+            for (int probe = 0; probe < kQHash && u.x != c && u.x != kHashEmpty; probe++) {
+              h = (h + 1) & (kQHash - 1);
+              u = slots[h];
+            }
+            if (u.x == c && ((u.y >> (q & 31)) & 1u))
+              idx[j] = kMode == kMap
+                  ? (int32_t)(ulo + s_hpos[h] + __popc(u.y & ((1u << (q & 31)) - 1u))) : 0;
+          }
+        }
+        emit<kMode>(a, o, row0, vec_ok, live, idx, bits);
+      }
+    }
+  } else {
+    // ---- general path -----------------------------------------------------
+    for (int g = warp; g < G; g += kQWarps) {
+      const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+      const uint64_t qlo = kfirst + (uint64_t)s_delta[tab.member[mb]];
+      const uint64_t qhi = klast + (uint64_t)s_delta[tab.member[me - 1]];
+      const int64_t lo = warp_bound(a.table, a.n_table, qlo, false, lane);
+      const int64_t hi = warp_bound(a.table, a.n_table, qhi, true, lane);
+      if (lane == 0) { s_glo[g] = lo; s_ghi[g] = max(lo, hi); }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int ns = 0, g = 0;
+      while (g < G) {
+        s_stage_gbeg[ns++] = g;
+        int64_t lo = s_glo[g], hi = s_ghi[g];
+        g++;
+        if (hi - lo <= kQWindow) {
+          while (g < G) {
+            const int64_t nlo = min(lo, s_glo[g]), nhi = max(hi, s_ghi[g]);
+            if (nhi - nlo > kQWindow) break;
+            lo = nlo; hi = nhi; g++;
+          }
+        }
+      }
+      s_stage_gbeg[ns] = G;
+      s_num_stages = ns;
+    }
+    __syncthreads();
+    const int num_stages = s_num_stages;
+    for (int st = 0; st < num_stages; st++) {
+      const int gb = s_stage_gbeg[st], ge = s_stage_gbeg[st + 1];
+      int64_t lo = s_glo[gb], hi = s_ghi[gb];
+      for (int g = gb + 1; g < ge; g++) { lo = min(lo, s_glo[g]); hi = max(hi, s_ghi[g]); }
+      const int64_t n = hi - lo;
+      const bool staged = n <= kQWindow;
+      if (staged) {
+        for (int i = tid; i < (int)n; i += kQThreads) s_win[i] = __ldg(a.table + lo + i);
+      }
+      __syncthreads();
+      for (int g = gb; g < ge; g++) {
+        const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+        const int64_t glo = s_glo[g], ghi = s_ghi[g];
+        int64_t pos[kQRows];
+#pragma unroll
+        for (int j = 0; j < kQRows; j++) {
+          const uint64_t q0 = key[j] + (uint64_t)s_delta[tab.member[mb]];
+          if (staged) {
+            pos[j] = lo + lower_bound_win<uint64_t>(s_win, (int)(glo - lo), (int)(ghi - lo), q0);
+          } else {
+            int64_t l = glo, h = ghi;
+            while (l < h) {
+              const int64_t mid = (l + h) >> 1;
+              if (__ldg(a.table + mid) < q0) l = mid + 1; else h = mid;
+            }
+            pos[j] = l;
+          }
         }
         for (int m = mb; m < me; m++) {
           const int o = tab.member[m];
-          const uint64_t q = key[j] + (uint64_t)s_delta[o];
-          uint64_t v = kKeyInf;
-          while (pos < ghi) {
-            v = staged ? s_win[pos - lo] : __ldg(a.table + pos);
-            if (v >= q) break;
-            pos++;
-            v = kKeyInf;
+          int32_t idx[kQRows];
+#pragma unroll
+          for (int j = 0; j < kQRows; j++) {
+            const uint64_t q = key[j] + (uint64_t)s_delta[o];
+            int64_t p = pos[j];
+            uint64_t v = kKeyInf;
+            while (p < ghi) {
+              v = staged ? s_win[p - lo] : __ldg(a.table + p);
+              if (v >= q) break;
+              p++;
+              v = kKeyInf;
+            }
+            pos[j] = p;
+            idx[j] = (live[j] && v == q) ? (int32_t)p : -1;
           }
-          const bool hit = (v == q);
-          if (kMode == kMap) {
-            a.kernel_map[(int64_t)o * a.n_rows + tile0 + j * kQThreads + tid] =
-                hit ? (int32_t)pos : -1;
-          } else {
-            bits[j] |= (hit ? 1u : 0u) << o;
-          }
-        }
+          emit<kMode>(a, o, row0, vec_ok, live, idx, bits);
         }
       }
+      __syncthreads();
     }
-    __syncthreads();
   }
 
   if (kMode == kBits) {
+    if (live[kQRows - 1] && (reinterpret_cast<uintptr_t>(a.hit_words) & 15) == 0) {
+      *reinterpret_cast<uint4 *>(a.hit_words + row0) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+    } else {
 #pragma unroll
-    for (int j = 0; j < kQRows; j++)
-      if (live[j]) a.hit_words[tile0 + j * kQThreads + tid] = bits[j];
-    for (int o = 0; o < O; o++) {
-      int c = 0;
+      for (int j = 0; j < kQRows; j++) if (live[j]) a.hit_words[row0 + j] = bits[j];
+    }
+    // per-offset hit counts of the warp, four offsets at a time: the four bits of
+    // a word are spread into four byte lanes by a multiply, summed over the rows
+    // and reduced over the warp with one redux
+    for (int o0 = 0; o0 < O; o0 += 4) {
+      uint32_t packed = 0;
 #pragma unroll
-      for (int j = 0; j < kQRows; j++) c += (bits[j] >> o) & 1u;
-      c = __reduce_add_sync(0xffffffffu, c);
-      if (lane == 0 && c != 0) atomicAdd(&s_counts[o], c);
+      for (int j = 0; j < kQRows; j++)
+        packed += (((bits[j] >> o0) & 0xfu) * 0x00204081u) & 0x01010101u;
+      packed = __reduce_add_sync(0xffffffffu, packed);  // each byte <= 128
+      if (lane < 4 && o0 + lane < O) {
+        const int c = (packed >> (8 * lane)) & 0xff;
+        if (c != 0) atomicAdd(&s_counts[o0 + lane], c);
+      }
     }
     __syncthreads();
     for (int o = tid; o < O; o += kQThreads)
@@ -231,24 +424,28 @@ search_kernel(const SearchArgs a, const __grid_constant__ OffsetTable tab) {
 }
 
 // ---------------------------------------------------------------------------
-// plan: scan tile counts -> sizes -> stable ascending order
+// plan: per-offset exclusive scan of the tile counts, sizes
 // ---------------------------------------------------------------------------
-struct PlanArgs {
-  int32_t *counts_a;  // [O, tiles_a] hit counts -> exclusive prefix, in place
-  int32_t *counts_b;  // optional second direction, [O, tiles_b]
-  int32_t tiles_a, tiles_b;
+// Block (o, dir) turns row o of counts[dir] ([O, tiles]) into its exclusive
+// prefix, in place, and writes the row total to sizes[dir * O + o].
+struct ScanArgs {
+  int32_t *counts[2];
+  int32_t tiles[2];
   int32_t num_offsets;
-  int32_t reorder;
-  int32_t *sizes_raw;     // [O] unsorted (workspace)
-  int32_t *pos_of;        // [O] mask row of offset o (workspace)
-  int32_t *order_out;     // [O] offset at mask row p
-  int32_t *sizes_out;     // [O] size of mask row p
+  int32_t *sizes;  // [2, O]
 };
 
-__device__ __forceinline__ int32_t warp_scan_row(int32_t *row, int n, int lane) {
-  int32_t carry = 0;
-  for (int b0 = 0; b0 < n; b0 += 32) {
-    const int b = b0 + lane;
+__global__ void __launch_bounds__(256) scan_tiles_kernel(const ScanArgs p) {
+  __shared__ int32_t s_warp[8];
+  __shared__ int32_t s_carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int o = blockIdx.x, dir = blockIdx.y;
+  const int n = p.tiles[dir];
+  int32_t *row = p.counts[dir] + (int64_t)o * n;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < n; b0 += 256) {
+    const int b = b0 + threadIdx.x;
     const int32_t v = b < n ? row[b] : 0;
     int32_t inc = v;
 #pragma unroll
@@ -256,37 +453,38 @@ __device__ __forceinline__ int32_t warp_scan_row(int32_t *row, int n, int lane) 
       const int32_t t = __shfl_up_sync(0xffffffffu, inc, s);
       if (lane >= s) inc += t;
     }
-    if (b < n) row[b] = carry + inc - v;
-    carry += __shfl_sync(0xffffffffu, inc, 31);
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    int32_t before = s_carry;
+    for (int w = 0; w < warp; w++) before += s_warp[w];
+    if (b < n) row[b] = before + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 255) s_carry = before + inc;
+    __syncthreads();
   }
-  return carry;
+  if (threadIdx.x == 0) p.sizes[dir * p.num_offsets + o] = s_carry;
 }
 
-__global__ void __launch_bounds__(1024) plan_kernel(const PlanArgs p) {
-  __shared__ int32_t s_size[MN_MAX_OFFSETS];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int O = p.num_offsets;
-  for (int o = warp; o < O; o += 32) {
-    const int32_t total = warp_scan_row(p.counts_a + (int64_t)o * p.tiles_a, p.tiles_a, lane);
-    if (p.counts_b != nullptr) warp_scan_row(p.counts_b + (int64_t)o * p.tiles_b, p.tiles_b, lane);
-    if (lane == 0) s_size[o] = total;
-  }
-  __syncthreads();
+// order[p] = offset at mask row p (stable ascending sizes), sizes_out[p] its size
+__device__ __forceinline__ void rank_offsets(const int32_t *sizes_raw, int O, int reorder,
+                                             int32_t *s_pos /* shared [O] */) {
   for (int o = threadIdx.x; o < O; o += blockDim.x) {
-    const int32_t mine = s_size[o];
     int pos = o;
-    if (p.reorder) {
+    if (reorder) {
+      const int32_t mine = sizes_raw[o];
       pos = 0;
       for (int j = 0; j < O; j++) {
-        const int32_t other = s_size[j];
+        const int32_t other = sizes_raw[j];
         pos += (other < mine) || (other == mine && j < o);
       }
     }
-    if (p.sizes_raw != nullptr) p.sizes_raw[o] = mine;
-    p.pos_of[o] = pos;
-    p.order_out[pos] = o;
-    p.sizes_out[pos] = mine;
+    s_pos[o] = pos;
   }
+}
+
+__global__ void identity_order_kernel(int O, int32_t *order_out, int32_t *sizes_out) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o < O) { order_out[o] = o; sizes_out[o] = 0; }
 }
 
 // ---------------------------------------------------------------------------
@@ -297,7 +495,10 @@ struct EmitArgs {
   const uint32_t *words_s;   // [S] hit bits of source rows (== words_t when mirrored)
   const int32_t *prefix_t;   // [O, tiles_t] exclusive tile prefix, target direction
   const int32_t *prefix_s;   // [O, tiles_s] source direction (== prefix_t when mirrored)
-  const int32_t *pos_of;     // [O]
+  const int32_t *sizes_raw;  // [O] hits per offset (offset order)
+  int32_t *order_out;        // [O] offset at mask row p
+  int32_t *sizes_out;        // [O] size of mask row p
+  int32_t reorder;
   int32_t *target_masks;     // [O, T]
   int32_t *source_masks;     // [O, S]
   int64_t T, S;
@@ -313,7 +514,16 @@ struct EmitArgs {
 __global__ void __launch_bounds__(kQThreads)
 emit_masks_kernel(const __grid_constant__ EmitArgs e) {
   __shared__ int32_t s_wtot[32][kQWarps + 1];  // offsets handled 32 at a time
+  __shared__ int32_t s_pos[MN_MAX_OFFSETS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  rank_offsets(e.sizes_raw, e.num_offsets, e.reorder, s_pos);
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int o = tid; o < e.num_offsets; o += kQThreads) {
+      e.order_out[s_pos[o]] = o;
+      e.sizes_out[s_pos[o]] = e.sizes_raw[o];
+    }
+  }
   const bool src_dir = blockIdx.x >= (unsigned)e.tiles_t;
   const int tile = src_dir ? blockIdx.x - e.tiles_t : blockIdx.x;
   const uint32_t *words = src_dir ? e.words_s : e.words_t;
@@ -375,7 +585,7 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
       res.y = v1 ? r : -1; r += v1;
       res.z = v2 ? r : -1; r += v2;
       res.w = v3 ? r : -1;
-      int32_t *dst = out + (int64_t)__ldg(e.pos_of + o) * n + row0;
+      int32_t *dst = out + (int64_t)s_pos[o] * n + row0;
       if (vec_out) {
         if (row0 < n) *reinterpret_cast<int4 *>(dst) = res;
       } else {
@@ -465,6 +675,11 @@ mn_status run_search(int mode, const uint64_t *rows, int64_t n_rows, const uint6
   a.kernel_map = kernel_map; a.hit_words = hit_words; a.tile_counts = tile_counts;
   a.n_tiles = (int)div_up(n_rows, kQTile);
   for (int k = 0; k < 4; k++) a.shift[k] = spec.shift[k];
+  a.fast_ok = spec.shift[spec.ndim - 1] == 0;
+  for (int o = 0; o < tab.num_offsets; o++) {
+    const int e = tab.off[o][tab.ndim - 1];
+    if (e > (int)kQPad || e < -(int)kQPad) a.fast_ok = 0;
+  }
   {
     LaunchScope scope(mode == kMap ? "search_kernel<map>" : "search_kernel<bits>", st);
     if (mode == kMap) search_kernel<kMap><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
@@ -582,11 +797,9 @@ extern "C" mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int6
   MN_CHECK_WS(ws);
   MN_LAUNCH("map_count_kernel", st, map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, counts,
                                                                      nullptr));
-  PlanArgs p{};
-  p.counts_a = counts; p.tiles_a = n_tiles; p.num_offsets = (int)O; p.reorder = 0;
-  p.sizes_raw = nullptr; p.pos_of = scratch; p.order_out = scratch + MN_MAX_OFFSETS;
-  p.sizes_out = scratch + 2 * MN_MAX_OFFSETS;
-  MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
+  ScanArgs p{};
+  p.counts[0] = counts; p.tiles[0] = n_tiles; p.num_offsets = (int)O; p.sizes = scratch;
+  MN_LAUNCH("scan_tiles_kernel", st, scan_tiles_kernel<<<dim3((unsigned)O, 1), 256, 0, st>>>(p));
   MN_LAUNCH("map_masks_kernel", st, map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
       kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out));
   return MN_OK;
@@ -637,21 +850,15 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
     words_s = ws.take<uint32_t>(std::max<int64_t>(S, 1));
     counts_s = ws.take<int32_t>((size_t)O * std::max(tiles_s, 1));
   }
-  int32_t *pos_of = ws.take<int32_t>(MN_MAX_OFFSETS);
+  int32_t *sizes_raw = ws.take<int32_t>(2 * MN_MAX_OFFSETS);
   MN_CHECK_WS(ws);
 
   if (T == 0 || S == 0) {
     // nothing can match: every mask entry is -1, every size 0
     if (S > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
     if (T > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(target_masks_out, 0xff, sizeof(int32_t) * O * T, st));
-    std::vector<int32_t> iota(O);
-    for (int64_t o = 0; o < O; o++) iota[o] = (int32_t)o;
-    MN_CHECK_CUDA(cudaMemsetAsync(sizes_out, 0, sizeof(int32_t) * O, st));
-    // order = identity; written by a plan launch over zero tiles
-    PlanArgs p{};
-    p.counts_a = counts_t; p.tiles_a = 0; p.num_offsets = (int)O; p.reorder = 0;
-    p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
-    MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
+    MN_LAUNCH("identity_order_kernel", st,
+              identity_order_kernel<<<1, MN_MAX_OFFSETS, 0, st>>>((int)O, order_out, sizes_out));
     return MN_OK;
   }
   MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
@@ -665,16 +872,17 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
     MN_RETURN_IF(run_search(kBits, source_keys, S, target_keys, T, bwd, *spec, nullptr, words_s,
                             counts_s, st));
   }
-  PlanArgs p{};
-  p.counts_a = counts_t; p.tiles_a = tiles_t;
-  p.counts_b = mirrored ? nullptr : counts_s; p.tiles_b = tiles_s;
-  p.num_offsets = (int)O; p.reorder = reorder ? 1 : 0;
-  p.sizes_raw = nullptr; p.pos_of = pos_of; p.order_out = order_out; p.sizes_out = sizes_out;
-  MN_LAUNCH("plan_kernel", st, plan_kernel<<<1, 1024, 0, st>>>(p));
+  ScanArgs p{};
+  p.counts[0] = counts_t; p.tiles[0] = tiles_t;
+  p.counts[1] = counts_s; p.tiles[1] = tiles_s;
+  p.num_offsets = (int)O; p.sizes = sizes_raw;
+  MN_LAUNCH("scan_tiles_kernel", st,
+            scan_tiles_kernel<<<dim3((unsigned)O, mirrored ? 1 : 2), 256, 0, st>>>(p));
 
   EmitArgs e{};
   e.words_t = words_t; e.words_s = words_s; e.prefix_t = counts_t; e.prefix_s = counts_s;
-  e.pos_of = pos_of; e.target_masks = target_masks_out; e.source_masks = source_masks_out;
+  e.sizes_raw = sizes_raw; e.order_out = order_out; e.sizes_out = sizes_out;
+  e.reorder = reorder ? 1 : 0; e.target_masks = target_masks_out; e.source_masks = source_masks_out;
   e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s; e.num_offsets = (int)O;
   for (int64_t o = 0; o < O; o++) e.mirror[o] = mirrored ? neg[o] : (uint8_t)o;
   MN_LAUNCH("emit_masks_kernel", st, emit_masks_kernel<<<tiles_t + tiles_s, kQThreads, 0, st>>>(e));

@@ -140,10 +140,34 @@ def pack_keys(coords: torch.Tensor, batch_dims: Optional[torch.Tensor], spec: Ke
 _host_copies = {}
 
 
-def remember_host(t: torch.Tensor, values: np.ndarray):
+class PendingHostCopy:
+    """Asynchronous device-to-host copy of ``[values..., status word]`` into
+    pinned memory; the wait happens when (and if) the host needs the values."""
+
+    def __init__(self, values: torch.Tensor):
+        device = values.device
+        packed = torch.cat([values, status_word(device)])
+        self.device = device
+        self.pinned = torch.empty(packed.shape, dtype=packed.dtype, pin_memory=True)
+        self.pinned.copy_(packed, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record(torch.cuda.current_stream(device))
+        self.values = None
+
+    def get(self) -> np.ndarray:
+        if self.values is None:
+            self.event.synchronize()
+            host = self.pinned.numpy().copy()
+            raise_on_status(int(host[-1]), self.device)
+            self.values = np.ascontiguousarray(host[:-1])
+            self.pinned = None
+        return self.values
+
+
+def remember_host(t: torch.Tensor, values):
+    """``values``: a numpy array or a PendingHostCopy of the tensor's contents."""
     key = id(t)
-    _host_copies[key] = (weakref.ref(t, lambda _r, k=key: _host_copies.pop(k, None)),
-                         np.ascontiguousarray(values))
+    _host_copies[key] = (weakref.ref(t, lambda _r, k=key: _host_copies.pop(k, None)), values)
 
 
 def host_copy(t: torch.Tensor, dtype=np.int32) -> np.ndarray:
@@ -151,5 +175,6 @@ def host_copy(t: torch.Tensor, dtype=np.int32) -> np.ndarray:
     engine, otherwise a blocking device-to-host read."""
     hit = _host_copies.get(id(t))
     if hit is not None and hit[0]() is t:
-        return hit[1].astype(dtype, copy=False)
+        values = hit[1].get() if isinstance(hit[1], PendingHostCopy) else hit[1]
+        return np.ascontiguousarray(values.astype(dtype, copy=False))
     return np.ascontiguousarray(t.detach().cpu().numpy().astype(dtype, copy=False))

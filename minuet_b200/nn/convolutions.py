@@ -220,10 +220,9 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
         _lib.check(lib.mn_compute_kernel_map_masks(
             engine.ptr(kernel_map), O, S, T, engine.ptr(source_masks), engine.ptr(target_masks),
             engine.ptr(ws), ws.numel(), stream), "compute_kernel_map_masks")
-    # one blocking read per map: sizes for the GEMM plan + the status word
-    host = torch.cat([sizes, engine.status_word(device)]).cpu().numpy()
-    engine.raise_on_status(int(host[-1]), device)
-    engine.remember_host(sizes, host[:-1].astype(np.int32))
+    # the GEMM plan needs the sizes on the host: start the copy (sizes + status
+    # word) now, wait for it only when a convolution asks
+    engine.remember_host(sizes, engine.PendingHostCopy(sizes))
     return source_masks, target_masks, (order if reorder else None), sizes
 
 

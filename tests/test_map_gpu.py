@@ -220,10 +220,15 @@ def test_cache_rejects_foreign_coordinates():
     a = dev(synth.sort_unique(np.random.default_rng(0).integers(0, 50, size=(500, 3))))
     cache.get_kernel_map(a, 1, None, a, 1, None, 3, 1)
     far = dev(np.array([[10_000, 0, 0]], np.int32))
+    # the out-of-box flag travels with the (lazy) host copy of the sizes, which
+    # is what a convolution waits for before it plans its GEMMs
+    from minuet_b200 import engine
+    sizes = cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)[3]
     with pytest.raises(RuntimeError):
-        cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)
+        engine.host_copy(sizes)
     cache.reset()
-    cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)
+    sizes = cache.get_kernel_map(far, 2, None, far, 2, None, 3, 1)[3]
+    assert engine.host_copy(sizes).sum() == 1
 
 
 @pytest.mark.parametrize("kind", ["uniform50k", "outdoor4"])
