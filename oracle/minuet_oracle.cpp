@@ -9,11 +9,15 @@
 // The reference ships no CPU implementation of this path (every functional
 // wrapper raises NotImplementedError off-GPU: minuet/nn/functional/indexing.py:56,127,
 // hash.py:25,50, scan.py:24,48, convolution.py:155), and no tests or golden
-// vectors.  Parity status: the integer stages are pinned only where
-// tests/test_reference_pin.py could run the reference's own CUDA sources
-// (built into oracle/_ref) against this file on a GPU; everything else is
-// "parity unpinned" by the reference and rests on the reference formulas cited
-// beside each function.
+// vectors of its own.  Parity status: PINNED against outputs of the reference
+// itself.  The reference's unmodified CUDA sources are compiled into
+// oracle/_ref/libminuet_ref.so (oracle/build_ref.py); tests/test_reference_pin.py
+// runs them on a GPU against this file (arg-sort, unique, kernel map, sizes,
+// masks bit-exact, fp32 forward within 1e-5), and tests/test_golden.py checks
+// this file against tests/golden/reference_golden.npz, which
+// tests/golden/make_reference_golden.py recorded from the same library.  The
+// size order is the one stage the reference leaves undefined (torch.sort ties);
+// see orc_order.
 //
 // All coordinates are int32 [n, D] row-major (D <= 4), clouds are delimited by
 // int64 prefix offsets batch_dims[B+1] (NULL = one cloud).
