@@ -206,13 +206,17 @@ size_t mn_conv_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t S,
 
 /* _C.cuda_sparse_convolution_forward
  * (csrc/minuet/torch/cuda_sparse_convolution_forward.cu:136-213).
- * sizes_host: HOST copy of the mask-row sizes; order: DEVICE int32 [O] or NULL. */
+ * sizes_host: HOST copy of the mask-row sizes; order: DEVICE int32 [O] or NULL.
+ * status_dev: DEVICE int32 word (may be NULL, which keeps fp16/bf16 on the SIMT
+ * GEMM); the tensor-core GEMM sets bit 2 there if one of its bounded barrier
+ * waits expires instead of hanging. */
 mn_status mn_sparse_convolution_forward(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
     const void *sources, const void *weights, const int32_t *source_masks,
     const int32_t *target_masks, const int32_t *order, const int32_t *sizes_host,
     int gather_tile, int scatter_tile, int allow_shortcut, int has_threshold,
-    double threshold, void *targets_out, void *ws, size_t ws_bytes, void *stream);
+    double threshold, void *targets_out, int32_t *status_dev, void *ws, size_t ws_bytes,
+    void *stream);
 
 /* _C.cuda_time_gather / cuda_time_scatter / cuda_time_gemm
  * (cuda_sparse_convolution_forward.cu:8-134): enqueue only the named stage of
@@ -224,7 +228,7 @@ mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, int64_t c_in
                         const int32_t *target_masks, const int32_t *order,
                         const int32_t *sizes_host, int tile, int allow_shortcut,
                         int has_threshold, double threshold, void *targets_out,
-                        void *ws, size_t ws_bytes, void *stream);
+                        int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -71,9 +71,10 @@ PROTOTYPES = {
                                          c_int, c_dbl]),
     "mn_sparse_convolution_forward": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_ptr,
                                               c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int,
-                                              c_int, c_int, c_dbl, c_ptr, c_ptr, c_size, c_ptr]),
+                                              c_int, c_int, c_dbl, c_ptr, c_ptr, c_ptr, c_size,
+                                              c_ptr]),
     "mn_conv_stage": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr,
-                              c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_dbl, c_ptr, c_ptr,
+                              c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_dbl, c_ptr, c_ptr, c_ptr,
                               c_size, c_ptr]),
 }
 

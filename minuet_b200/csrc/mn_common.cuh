@@ -120,13 +120,28 @@ struct GemmTable {
   int32_t weight_row[MN_MAX_OFFSETS + 1];     // mask row whose weight matrix to use
   const void *a[MN_MAX_OFFSETS + 1];          // first A row of the problem
   void *c[MN_MAX_OFFSETS + 1];                // first C row of the problem
+  int64_t a_row[MN_MAX_OFFSETS + 1];          // that row's index inside its operand array
+  uint8_t direct[MN_MAX_OFFSETS + 1];         // 1: A is the input feature matrix, 0: gather buffer
+};
+
+// Operand arrays of the tensor-core GEMM (TMA addresses whole arrays, not rows).
+struct TcOperands {
+  const void *gathered = nullptr;   // [gathered_rows, c_in]
+  int64_t gathered_rows = 0;
+  const void *sources = nullptr;    // [source_rows, c_in]
+  int64_t source_rows = 0;
+  void *weights_t = nullptr;        // scratch for the transposed weights [O, c_out, c_in]
+  int num_weights = 0;              // O
+  int32_t *status = nullptr;        // device status word
 };
 
 // Tensor-core grouped GEMM (mn_gemm_tc.cu); *handled = false when the shape or
 // dtype is outside what it covers and the caller must use the SIMT kernel.
-mn_status launch_gemm_tc(const GemmTable &tab, int c_in, int c_out, mn_dtype dtype,
-                         const void *weights, const int32_t *order, cudaStream_t st,
-                         bool *handled);
+mn_status launch_gemm_tc(const GemmTable &tab, const TcOperands &ops, int c_in, int c_out,
+                         mn_dtype dtype, const void *weights, const int32_t *order,
+                         cudaStream_t st, bool *handled);
+bool gemm_tc_supported(int c_in, int c_out, mn_dtype dtype);
+size_t gemm_tc_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out);
 
 // ---- launchers (defined in the .cu files) ---------------------------------
 mn_status launch_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,

@@ -1,13 +1,481 @@
-// Tensor-core grouped GEMM over kernel offsets (tcgen05 + TMEM + TMA).
+// Tensor-core grouped GEMM over kernel offsets: tcgen05.mma with TMEM
+// accumulators, operands staged in shared memory by TMA, fp16/bf16 in, fp32
+// accumulate.  One persistent launch covers every offset of a convolution (and
+// its centre offset), where the reference issues one cuBLAS call per padding
+// bucket on up to four streams
+// (csrc/minuet/cuda/functions/sparse_convolution.cu:586-641, 647-660).
+//
+// Layout of one CTA (192 threads, one CTA per SM, no clusters, no multicast):
+//   warp 0      TMA producer: A tile [128 rows x 64 k] and B tile [N x 64 k] per
+//               k-block into a ring of shared-memory stages (128-byte swizzle)
+//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits
+//               stage-free and accumulator-ready barriers
+//   warps 2..5  epilogue: tcgen05.ld the 128 x N fp32 accumulator (each warp its
+//               own 32-lane quarter), convert, store the rows that exist
+// Two accumulators (2 x N columns of TMEM) let the epilogue of tile i overlap
+// the MMAs of tile i+1.  Every barrier wait is bounded: on expiry the kernel
+// raises bit 2 of *status, all roles leave their loops, TMEM is freed and the
+// kernel returns.
+//
+// B is the weight matrix of one offset TRANSPOSED to [N, K] (K contiguous), so
+// that both operands are K-major; a small kernel transposes the layer's weights
+// into the workspace first.
 #include "mn_common.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
 
 namespace mn {
 
-mn_status launch_gemm_tc(const GemmTable &tab, int c_in, int c_out, mn_dtype dtype,
-                         const void *weights, const int32_t *order, cudaStream_t st,
-                         bool *handled) {
-  (void)tab; (void)c_in; (void)c_out; (void)dtype; (void)weights; (void)order; (void)st;
+namespace {
+
+constexpr int kTcThreads = 192;
+constexpr int kBM = 128;            // rows per tile = UMMA M
+constexpr int kBK = 64;             // k elements per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;          // k elements per tcgen05.mma (16-bit inputs)
+constexpr int kMaxStages = 6;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct TcArgs {
+  int32_t k_blocks;      // ceil(c_in / 64)
+  int32_t n_pad;         // c_out rounded up to 16 (UMMA N)
+  int32_t c_out;
+  int32_t stages;
+  int32_t a_bytes;       // bytes of one A stage (16 KB)
+  int32_t stage_bytes;   // A + B bytes of one stage
+  int32_t elem_is_bf16;
+  int32_t total_tiles;
+  const int32_t *order;  // device, may be NULL
+  int32_t *status;       // device status word (bit 2: bounded wait expired)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: false when the limit expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int32_t *status) {
+  for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(status, 4);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y,
+                                            uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z,
+                                            uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle:
+// rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);   // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                         // layout: 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+struct TilePos {
+  int problem;
+  int m0;      // first row of the tile inside the problem
+};
+
+__device__ __forceinline__ TilePos locate_tile(const GemmTable &tab, int tile) {
+  int lo = 0, hi = tab.num_problems;  // last p with tile_prefix[p] <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tab.tile_prefix[mid] <= tile) lo = mid; else hi = mid;
+  }
+  return TilePos{lo, (tile - tab.tile_prefix[lo]) * kBM};
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ TcArgs args,
+               const __grid_constant__ CUtensorMap map_a,       // gather buffer  [rows, K]
+               const __grid_constant__ CUtensorMap map_direct,  // input features [S, K]
+               const __grid_constant__ CUtensorMap map_b) {     // weights^T      [O, N, K]
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[kMaxStages], bar_empty[kMaxStages];
+  __shared__ uint64_t bar_acc_full[2], bar_acc_empty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to 1024
+  uint8_t *stage_base = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = args.stages;
+  const uint32_t tmem_cols = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; s++) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&bar_acc_full[a], 1); mbar_init(&bar_acc_empty[a], 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)), "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int *abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (uint32_t)args.stage_bytes;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < args.total_tiles; tile += gridDim.x) {
+        const TilePos pos = locate_tile(tab, tile);
+        const int p = pos.problem;
+        const bool direct = tab.direct[p] != 0;
+        const int row0 = (int)tab.a_row[p] + pos.m0;
+        const int wrow = tab.weight_row[p];
+        const int widx = args.order != nullptr ? __ldg(args.order + wrow) : wrow;
+        for (int kb = 0; kb < args.k_blocks; kb++) {
+          if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag, args.status)) { alive = false; break; }
+          uint8_t *sa = stage_base + (size_t)stage * args.stage_bytes;
+          uint8_t *sb = sa + args.a_bytes;
+          mbar_expect_tx(&bar_full[stage], tx_bytes);
+          tma_load_2d(sa, direct ? &map_direct : &map_a, kb * kBK, row0, &bar_full[stage]);
+          tma_load_3d(sb, &map_b, kb * kBK, 0, widx, &bar_full[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A/B format, both K-major, N, M
+      const uint32_t fmt = args.elem_is_bf16 ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) |
+                             ((uint32_t)(args.n_pad >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < args.total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_flag, args.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * args.n_pad);
+        for (int kb = 0; kb < args.k_blocks; kb++) {
+          if (!mbar_wait(&bar_full[stage], phase, abort_flag, args.status)) { alive = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(stage_base + (size_t)stage * args.stage_bytes);
+          const uint32_t sb = sa + (uint32_t)args.a_bytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; k++) {
+            const uint64_t da = umma_desc(sa + k * kUmmaK * 2);
+            const uint64_t db = umma_desc(sb + k * kUmmaK * 2);
+            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&bar_empty[stage]);   // the stage is free once these MMAs have read it
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit(&bar_acc_full[acc]);    // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;           // TMEM lanes a warp may read: 32 * (warp id % 4)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const int n = args.c_out;
+    for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
+      const TilePos pos = locate_tile(tab, tile);
+      const int p = pos.problem;
+      if (!mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = pos.m0 + quarter * 32 + lane;
+      const bool live = row < tab.rows[p];
+      T *crow = static_cast<T *>(tab.c[p]) + (int64_t)row * n;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_pad);
+      for (int c0 = 0; c0 < args.n_pad; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
+#pragma unroll
+          for (int v = 0; v < 4; v++) {       // 8 outputs = 16 bytes per store
+            const int c = c0 + v * 8;
+            if (c + 8 <= n) {
+              uint4 out;
+              uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+              for (int h = 0; h < 4; h++) {
+                const float lo = __uint_as_float(r[v * 8 + 2 * h]);
+                const float hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
+                if (sizeof(T) == 2 && args.elem_is_bf16) {
+                  __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+                  o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+                } else {
+                  __half2 pk = __floats2half2_rn(lo, hi);
+                  o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+                }
+              }
+              *reinterpret_cast<uint4 *>(crow + c) = out;
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s_abort) {
+    // a role gave up: give copies and MMAs still in flight time to land before
+    // shared memory and TMEM go away
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+// wt[o][n][k] = w[o][k][n]
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose_weights_kernel(const T *__restrict__ w, T *__restrict__ wt, int K, int N) {
+  __shared__ T tile[32][33];
+  const int o = blockIdx.z;
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const T *src = w + (int64_t)o * K * N;
+  T *dst = wt + (int64_t)o * K * N;
+  for (int i = ty; i < 32; i += 8)
+    if (k0 + i < K && n0 + tx < N) tile[i][tx] = src[(int64_t)(k0 + i) * N + n0 + tx];
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8)
+    if (n0 + i < N && k0 + tx < K) dst[(int64_t)(n0 + i) * K + k0 + tx] = tile[tx][i];
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// K-major operand map: dims (K, rows[, batch]), box (64, box_rows[, 1]), 128-byte swizzle
+mn_status make_map(CUtensorMap *map, const void *base, bool bf16, int64_t K, int64_t rows,
+                   int64_t batch, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return MN_ERR_CUDA;
+  }
+  const cuuint32_t rank = batch > 0 ? 3 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(batch, 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)K * 2 * (cuuint64_t)rows};
+  cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        rank, const_cast<void *>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (K=%lld rows=%lld batch=%lld)", (int)r,
+              (long long)K, (long long)rows, (long long)batch);
+    return MN_ERR_CUDA;
+  }
+  return MN_OK;
+}
+
+}  // namespace
+
+size_t gemm_tc_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out) {
+  return align_up((size_t)O * c_in * c_out * 2, 1024);
+}
+
+bool gemm_tc_supported(int c_in, int c_out, mn_dtype dtype) {
+  return (dtype == MN_F16 || dtype == MN_BF16) && c_in >= 8 && c_in % 8 == 0 && c_out >= 8 &&
+         c_out % 8 == 0 && c_out <= 256;
+}
+
+mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_in, int c_out,
+                         mn_dtype dtype, const void *weights, const int32_t *order,
+                         cudaStream_t st, bool *handled) {
   *handled = false;
+  if (!gemm_tc_supported(c_in, c_out, dtype) || ops.weights_t == nullptr || ops.status == nullptr)
+    return MN_OK;
+  const bool bf16 = dtype == MN_BF16;
+  const int O = ops.num_weights;
+
+  // weights [O, K, N] -> [O, N, K]
+  {
+    const dim3 grid((unsigned)div_up(c_out, 32), (unsigned)div_up(c_in, 32), (unsigned)O);
+    if (bf16) {
+      MN_LAUNCH("transpose_weights_kernel", st,
+                transpose_weights_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+                    static_cast<const __nv_bfloat16 *>(weights),
+                    static_cast<__nv_bfloat16 *>(ops.weights_t), c_in, c_out));
+    } else {
+      MN_LAUNCH("transpose_weights_kernel", st,
+                transpose_weights_kernel<__half><<<grid, 256, 0, st>>>(
+                    static_cast<const __half *>(weights), static_cast<__half *>(ops.weights_t),
+                    c_in, c_out));
+    }
+  }
+
+  GemmTable tab = tab_in;
+  tab.tile_rows = kBM;
+  tab.tile_prefix[0] = 0;
+  for (int p = 0; p < tab.num_problems; p++)
+    tab.tile_prefix[p + 1] = tab.tile_prefix[p] + (int)div_up(tab.rows[p], kBM);
+  const int total_tiles = tab.tile_prefix[tab.num_problems];
+  if (total_tiles == 0) { *handled = true; return MN_OK; }
+
+  TcArgs args{};
+  args.k_blocks = (int)div_up(c_in, kBK);
+  args.n_pad = (int)align_up((size_t)c_out, 16);
+  args.c_out = c_out;
+  args.a_bytes = kBM * kBK * 2;
+  args.stage_bytes = args.a_bytes + args.n_pad * kBK * 2;
+  args.stages = std::min(kMaxStages, std::max(2, (200 * 1024) / args.stage_bytes));
+  args.elem_is_bf16 = bf16 ? 1 : 0;
+  args.total_tiles = total_tiles;
+  args.order = order;
+  args.status = ops.status;
+
+  CUtensorMap map_a, map_direct, map_b;
+  // an operand that no problem uses still needs a valid map: point it at the other one
+  const void *gather_base = ops.gathered != nullptr ? ops.gathered : ops.sources;
+  const int64_t gather_rows = ops.gathered != nullptr ? ops.gathered_rows : ops.source_rows;
+  const void *direct_base = ops.sources != nullptr ? ops.sources : ops.gathered;
+  const int64_t direct_rows = ops.sources != nullptr ? ops.source_rows : ops.gathered_rows;
+  MN_CHECK_ARG(gather_base != nullptr && gather_rows > 0, "gemm_tc: no A operand");
+  MN_CHECK_ARG((reinterpret_cast<uintptr_t>(gather_base) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(direct_base) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(ops.weights_t) & 15) == 0,
+               "gemm_tc: operands must be 16-byte aligned");
+  MN_RETURN_IF(make_map(&map_a, gather_base, bf16, c_in, gather_rows, 0, kBM));
+  MN_RETURN_IF(make_map(&map_direct, direct_base, bf16, c_in, direct_rows, 0, kBM));
+  MN_RETURN_IF(make_map(&map_b, ops.weights_t, bf16, c_in, c_out, O, args.n_pad));
+
+  // at least 120 KB so that two CTAs (each allocating all 512 TMEM columns) can
+  // never share an SM
+  const size_t smem = std::max<size_t>((size_t)args.stages * args.stage_bytes + 1024, 120 * 1024);
+  const int grid = std::min(total_tiles, kNumSMs);
+  if (bf16) {
+    MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MN_LAUNCH("gemm_tc_kernel", st,
+              gemm_tc_kernel<__nv_bfloat16><<<grid, kTcThreads, smem, st>>>(tab, args, map_a,
+                                                                            map_direct, map_b));
+  } else {
+    MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__half>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MN_LAUNCH("gemm_tc_kernel", st,
+              gemm_tc_kernel<__half><<<grid, kTcThreads, smem, st>>>(tab, args, map_a, map_direct,
+                                                                    map_b));
+  }
+  *handled = true;
   return MN_OK;
 }
 

@@ -285,14 +285,18 @@ ConvLayout make_layout(const int32_t *sizes, int64_t O, int64_t S, int64_t T, in
 struct ConvBuffers {
   char *gathered;   // [total_rows, c_in]
   char *products;   // [total_rows, c_out]
+  char *weights_t;  // [O, c_out, c_in], tensor-core path only
 };
 
-mn_status carve(const ConvLayout &L, int64_t c_in, int64_t c_out, mn_dtype dtype, void *ws_ptr,
-                size_t ws_bytes, ConvBuffers *b) {
+mn_status carve(const ConvLayout &L, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
+                void *ws_ptr, size_t ws_bytes, ConvBuffers *b) {
   Workspace ws(ws_ptr, ws_bytes);
   const size_t e = dtype_size(dtype);
   b->gathered = ws.take<char>((size_t)std::max<int64_t>(L.total_rows, 1) * c_in * e);
   b->products = ws.take<char>((size_t)std::max<int64_t>(L.total_rows, 1) * c_out * e);
+  b->weights_t = nullptr;
+  if (gemm_tc_supported((int)c_in, (int)c_out, dtype))
+    b->weights_t = ws.take<char>(gemm_tc_workspace_bytes(O, c_in, c_out));
   MN_CHECK_WS(ws);
   return MN_OK;
 }
@@ -403,9 +407,10 @@ mn_status run_scatter(const ConvLayout &L, const ConvBuffers &b, int64_t T_rows,
   }
 }
 
-mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *sizes, int64_t S,
-                   int64_t c_in, int64_t c_out, mn_dtype dtype, const void *sources,
-                   const void *weights, const int32_t *order, void *out, cudaStream_t st) {
+mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *sizes, int64_t O,
+                   int64_t S, int64_t c_in, int64_t c_out, mn_dtype dtype, const void *sources,
+                   const void *weights, const int32_t *order, void *out, int32_t *status_dev,
+                   cudaStream_t st) {
   const size_t e = dtype_size(dtype);
   GemmTable tab{};
   int np = 0;
@@ -415,6 +420,8 @@ mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *siz
     tab.weight_row[np] = o;
     tab.a[np] = b.gathered + (size_t)L.plan.row_begin[o] * c_in * e;
     tab.c[np] = b.products + (size_t)L.plan.row_begin[o] * c_out * e;
+    tab.a_row[np] = L.plan.row_begin[o];
+    tab.direct[np] = 0;
     np++;
   }
   if (L.shortcut && S > 0) {
@@ -422,13 +429,23 @@ mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *siz
     tab.weight_row[np] = L.n_buf;
     tab.a[np] = sources;
     tab.c[np] = out;
+    tab.a_row[np] = 0;
+    tab.direct[np] = 1;
     np++;
   }
   tab.num_problems = np;
   if (np == 0) return MN_OK;
 
   bool handled = false;
-  MN_RETURN_IF(launch_gemm_tc(tab, (int)c_in, (int)c_out, dtype, weights, order, st, &handled));
+  TcOperands ops;
+  ops.gathered = L.total_rows > 0 ? b.gathered : nullptr;
+  ops.gathered_rows = L.total_rows;
+  ops.sources = S > 0 ? sources : nullptr;
+  ops.source_rows = S;
+  ops.weights_t = b.weights_t;
+  ops.num_weights = (int)O;
+  ops.status = status_dev;
+  MN_RETURN_IF(launch_gemm_tc(tab, ops, (int)c_in, (int)c_out, dtype, weights, order, st, &handled));
   if (handled) return MN_OK;
 
   tab.tile_rows = kGemmTM;
@@ -514,7 +531,9 @@ extern "C" size_t mn_conv_workspace_bytes(const int32_t *sizes_host, int64_t O, 
   const ConvLayout L = make_layout(sizes_host, O, S, T, allow_shortcut);
   const size_t e = dtype_size(dtype);
   const size_t rows = (size_t)std::max<int64_t>(L.total_rows, 1);
-  return align_up(rows * c_in * e, 256) + align_up(rows * c_out * e, 256) + 1024;
+  size_t total = align_up(rows * c_in * e, 256) + align_up(rows * c_out * e, 256) + 1024;
+  if (gemm_tc_supported((int)c_in, (int)c_out, dtype)) total += gemm_tc_workspace_bytes(O, c_in, c_out) + 256;
+  return total;
 }
 
 extern "C" mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, int64_t c_in,
@@ -523,20 +542,22 @@ extern "C" mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, i
                                    const int32_t *target_masks, const int32_t *order,
                                    const int32_t *sizes_host, int tile, int allow_shortcut,
                                    int has_threshold, double threshold, void *targets_out,
-                                   void *ws_ptr, size_t ws_bytes, void *stream) {
+                                   int32_t *status_dev, void *ws_ptr, size_t ws_bytes,
+                                   void *stream) {
   (void)has_threshold; (void)threshold;
   MN_RETURN_IF(check_conv_args(S, T, O, c_in, c_out, dtype, sizes_host));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const ConvLayout L = make_layout(sizes_host, O, S, T, allow_shortcut);
   ConvBuffers b{};
-  MN_RETURN_IF(carve(L, c_in, c_out, dtype, ws_ptr, ws_bytes, &b));
+  MN_RETURN_IF(carve(L, O, c_in, c_out, dtype, ws_ptr, ws_bytes, &b));
   switch (stage) {
     case 0:
       MN_CHECK_ARG(sources != nullptr && source_masks != nullptr, "conv_stage: null pointer");
       return run_gather(L, b, S, c_in, dtype, sources, source_masks, tile, st);
     case 1:
       MN_CHECK_ARG(sources != nullptr && weights != nullptr && targets_out != nullptr, "conv_stage: null pointer");
-      return run_gemm(L, b, sizes_host, S, c_in, c_out, dtype, sources, weights, order, targets_out, st);
+      return run_gemm(L, b, sizes_host, O, S, c_in, c_out, dtype, sources, weights, order,
+                      targets_out, status_dev, st);
     case 2:
       MN_CHECK_ARG(target_masks != nullptr && targets_out != nullptr, "conv_stage: null pointer");
       return run_scatter(L, b, T, c_out, dtype, target_masks, tile, targets_out, st);
@@ -551,7 +572,7 @@ extern "C" mn_status mn_sparse_convolution_forward(
     const void *sources, const void *weights, const int32_t *source_masks,
     const int32_t *target_masks, const int32_t *order, const int32_t *sizes_host, int gather_tile,
     int scatter_tile, int allow_shortcut, int has_threshold, double threshold, void *targets_out,
-    void *ws_ptr, size_t ws_bytes, void *stream) {
+    int32_t *status_dev, void *ws_ptr, size_t ws_bytes, void *stream) {
   (void)has_threshold; (void)threshold;
   MN_RETURN_IF(check_conv_args(S, T, O, c_in, c_out, dtype, sizes_host));
   if (T == 0) return MN_OK;
@@ -561,10 +582,10 @@ extern "C" mn_status mn_sparse_convolution_forward(
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const ConvLayout L = make_layout(sizes_host, O, S, T, allow_shortcut);
   ConvBuffers b{};
-  MN_RETURN_IF(carve(L, c_in, c_out, dtype, ws_ptr, ws_bytes, &b));
+  MN_RETURN_IF(carve(L, O, c_in, c_out, dtype, ws_ptr, ws_bytes, &b));
   MN_RETURN_IF(run_gather(L, b, S, c_in, dtype, sources, source_masks, gather_tile, st));
-  MN_RETURN_IF(run_gemm(L, b, sizes_host, S, c_in, c_out, dtype, sources, weights, order,
-                        targets_out, st));
+  MN_RETURN_IF(run_gemm(L, b, sizes_host, O, S, c_in, c_out, dtype, sources, weights, order,
+                        targets_out, status_dev, st));
   MN_RETURN_IF(run_scatter(L, b, T, c_out, dtype, target_masks, scatter_tile, targets_out, st));
   return MN_OK;
 }

@@ -92,8 +92,9 @@ def sparse_convolution_forward(sources: torch.Tensor,
         S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights), engine.ptr(sm),
         engine.ptr(tm), engine.ptr(order), engine.np_ptr(sizes_host), int(gather_tile_size),
         int(scatter_tile_size), int(bool(allow_shortcut_matmul)), 0 if threshold is None else 1,
-        0.0 if threshold is None else float(threshold), engine.ptr(out), engine.ptr(ws),
-        ws.numel(), engine.stream_ptr(device)), "sparse_convolution_forward")
+        0.0 if threshold is None else float(threshold), engine.ptr(out),
+        engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
+        engine.stream_ptr(device)), "sparse_convolution_forward")
     return out
 
 
@@ -117,8 +118,9 @@ def _time_stage(stage, weights, source_masks, target_masks, kernel_map_sizes, ti
         stage, S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights),
         engine.ptr(sm), engine.ptr(tm), None, engine.np_ptr(sizes_host), int(tile_size),
         int(bool(allow_shortcut_matmul)), 0 if threshold is None else 1,
-        0.0 if threshold is None else float(threshold), engine.ptr(out), engine.ptr(ws),
-        ws.numel(), engine.stream_ptr(device)), "conv_stage")
+        0.0 if threshold is None else float(threshold), engine.ptr(out),
+        engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
+        engine.stream_ptr(device)), "conv_stage")
     end.record(stream)
     end.synchronize()
     return begin.elapsed_time(end)

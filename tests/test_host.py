@@ -98,7 +98,7 @@ def test_bad_arguments_are_reported_without_a_gpu(mn_lib):
     sizes = np.array([5, 9], np.int32)
     st = mn_lib.mn_sparse_convolution_forward(4, 4, 2, 8, 8, 0, None, None, None, None, None,
                                               sizes.ctypes.data_as(ctypes.c_void_p), 1, 1, 1, 1,
-                                              0.0, None, None, 0, None)
+                                              0.0, None, None, None, 0, None)
     assert st == _lib.MN_ERR_BAD_ARG          # sizes exceed min(S, T)
     with pytest.raises(RuntimeError):
         _lib.check(st, "conv")
