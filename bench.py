@@ -339,6 +339,10 @@ def gpu_arm(args):
         cpu = {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{done} full steps of the same 4-cloud batch ({ms:.1f} ms/step)"}
 
+    sweep = None
+    if world == 1 and args.gms_sweep:
+        sweep = gms_sweep(torch, minuet, cache, d_coords, d_bd)
+
     h2d = h_coords.numel() * 4 + h_bd.numel() * 8
     d2h = sum((k ** 3 + 1) * 4 + k ** 3 * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8 + 32
     line = {
@@ -353,11 +357,53 @@ def gpu_arm(args):
         "gpu_launches": int(launches),
         "roofline": roofline,
         "cpu_baseline": cpu,
+        "gms_sweep": sweep,
         "wall_s": round(t_wall, 3),
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=(16, 32, 64, 128, 256), rounds=5):
+    """Gather / grouped GEMM / scatter stage times on the 3^3 stride-1 map of the
+    benchmark batch, fp16 features and weights (fp32 accumulate)."""
+    from minuet_b200 import engine
+    from minuet_b200.nn import functional as F
+    peaks, _ = measured_peaks()
+    tc = cache.get_target_coordinates(d_coords, d_bd, 1, 1)
+    sm, tm, order, sizes = cache.get_kernel_map(d_coords, 1, d_bd, tc[0], tc[1], tc[2], 3, 1)
+    h_sizes = engine.host_copy(sizes)
+    S = T = d_coords.shape[0]
+    O = len(h_sizes)
+    E = int(h_sizes.sum())
+    E1, O1 = E - int(h_sizes[-1]), O - 1            # centre offset takes the shortcut
+    out = {}
+    for c in channels:
+        w = torch.randn(O, c, c, device=d_coords.device).half()
+        kw = dict(weights=w, source_masks=sm, target_masks=tm, kernel_map_sizes=sizes,
+                  allow_shortcut_matmul=True)
+        for fn in (F.cuda_time_gather, F.cuda_time_scatter):
+            fn(tile_size=1, **kw)
+        F.cuda_time_gemm(**kw)
+        tg = min(F.cuda_time_gather(tile_size=1, **kw) for _ in range(rounds))
+        tm_ = min(F.cuda_time_gemm(**kw) for _ in range(rounds))
+        ts = min(F.cuda_time_scatter(tile_size=1, **kw) for _ in range(rounds))
+        gather_bytes = S * c * 2 + 4 * O1 * S + E1 * c * 2
+        scatter_bytes = E1 * c * 2 + 4 * O1 * T + 2 * T * c * 2
+        flops = 2.0 * E * c * c
+        gemm_bytes = E * 2 * c * 2 + O * c * c * 2
+        out[str(c)] = {
+            "gather_ms": round(tg, 4), "gather_gbs": round(gather_bytes / tg / 1e6, 1),
+            "gather_frac_hbm": round(gather_bytes / tg / 1e6 / peaks["hbm_gbs"], 3),
+            "gemm_ms": round(tm_, 4), "gemm_tflops": round(flops / tm_ / 1e9, 2),
+            "gemm_frac_tensor": round(flops / tm_ / 1e9 / peaks["bf16_tflops"], 4),
+            "gemm_gbs": round(gemm_bytes / tm_ / 1e6, 1),
+            "scatter_ms": round(ts, 4), "scatter_gbs": round(scatter_bytes / ts / 1e6, 1),
+            "scatter_frac_hbm": round(scatter_bytes / ts / 1e6 / peaks["hbm_gbs"], 3),
+        }
+    return {"map": "3^3 stride 1 on the benchmark batch", "S": int(S), "pairs": E,
+            "pairs_without_centre": E1, "dtype": "f16", "channels": out}
 
 
 def main():
@@ -367,6 +413,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gms-sweep", action="store_true",
+                    help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

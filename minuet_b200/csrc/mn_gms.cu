@@ -63,14 +63,16 @@ struct GatherArgs {
   int32_t lanes_per_row;       // power of two <= 32
 };
 
-// A warp owns 32 consecutive source rows.  For every offset it reads the 32
-// mask words with one coalesced load, compacts the hits through shared memory
-// and copies 32/lanes_per_row rows per step; the input rows stay in L1 across
-// the offsets that reuse them.
+// A warp owns 32 consecutive source rows.  It reads the mask words of eight
+// offsets at a time (eight independent coalesced 128-byte loads in flight),
+// then, per offset, compacts the hit rows through shared memory and copies
+// 32/lanes_per_row rows per step with 16-byte accesses; the input rows stay in
+// L1 across the offsets that reuse them.
 template <int kVec>
 __global__ void __launch_bounds__(256)
 gather_kernel(const GatherArgs g, const __grid_constant__ RowPlan plan) {
   using V = typename Chunk<kVec>::type;
+  constexpr int kBatch = 8;
   __shared__ int2 s_list[8][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int lpr = g.lanes_per_row, rpi = 32 / lpr;
@@ -79,26 +81,33 @@ gather_kernel(const GatherArgs g, const __grid_constant__ RowPlan plan) {
   const int64_t n_chunks32 = (g.S + 31) >> 5;
   for (int64_t blk = (int64_t)blockIdx.x * 8 + warp; blk < n_chunks32; blk += (int64_t)gridDim.x * 8) {
     const int64_t s = (blk << 5) + lane;
-    for (int o = 0; o < g.num_offsets; o++) {
-      const int m = s < g.S ? __ldg(g.source_masks + (int64_t)o * g.S + s) : -1;
-      const unsigned hits = __ballot_sync(0xffffffffu, m >= 0);
-      if (hits == 0) continue;
-      const int cnt = __popc(hits);
-      if (m >= 0) {
-        const int r = __popc(hits & ((1u << lane) - 1u));
-        s_list[warp][r] = make_int2(lane, m);
-      }
-      __syncwarp();
-      for (int e0 = 0; e0 < cnt; e0 += rpi) {
-        const int e = e0 + sub;
-        if (e < cnt) {
-          const int2 it = s_list[warp][e];
-          const V *src = reinterpret_cast<const V *>(g.in + ((blk << 5) + it.x) * g.row_bytes);
-          V *dst = reinterpret_cast<V *>(g.buf + (plan.row_begin[o] + it.y) * g.row_bytes);
-          for (int c = part; c < chunks; c += lpr) dst[c] = __ldg(src + c);
+    for (int o0 = 0; o0 < g.num_offsets; o0 += kBatch) {
+      int m[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; i++)
+        m[i] = (s < g.S && o0 + i < g.num_offsets)
+                   ? __ldg(g.source_masks + (int64_t)(o0 + i) * g.S + s) : -1;
+#pragma unroll
+      for (int i = 0; i < kBatch; i++) {
+        const unsigned hits = __ballot_sync(0xffffffffu, m[i] >= 0);
+        if (hits == 0) continue;
+        const int cnt = __popc(hits);
+        if (m[i] >= 0) {
+          const int r = __popc(hits & ((1u << lane) - 1u));
+          s_list[warp][r] = make_int2(lane, m[i]);
         }
+        __syncwarp();
+        for (int e0 = 0; e0 < cnt; e0 += rpi) {
+          const int e = e0 + sub;
+          if (e < cnt) {
+            const int2 it = s_list[warp][e];
+            const V *src = reinterpret_cast<const V *>(g.in + ((blk << 5) + it.x) * g.row_bytes);
+            V *dst = reinterpret_cast<V *>(g.buf + (plan.row_begin[o0 + i] + it.y) * g.row_bytes);
+            for (int c = part; c < chunks; c += lpr) dst[c] = __ldg(src + c);
+          }
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   }
 }
@@ -118,65 +127,105 @@ struct ScatterArgs {
   int32_t add_existing;        // out already holds the centre product: add it last
 };
 
-// lanes_per_row lanes share one target row and keep kAcc fp32 accumulators each
-// (channel c of the row belongs to lane c / kVecElems % lanes_per_row); offsets
-// are visited in mask-row order and the row is written once.
+// A warp owns 32 consecutive target rows.  Phase 1: lane r reads the mask words
+// of row r for every offset (coalesced, many loads in flight), keeps a bit per
+// hit and parks the words in shared memory.  Phase 2: lanes_per_row lanes share
+// one row, walk only that row's hits in mask-row order, accumulate the product
+// rows in fp32 registers and write the row once (adding the centre product that
+// the GEMM already left in `out` last, when there is one).
 template <typename T, int kVecElems, int kAcc>
 __global__ void __launch_bounds__(256)
 scatter_kernel(const ScatterArgs<T> a, const __grid_constant__ RowPlan plan) {
   using V = typename Chunk<kVecElems * sizeof(T)>::type;
-  const int lane = threadIdx.x & 31;
+  extern __shared__ int32_t s_masks[];   // [warps][num_offsets][32]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int O = a.num_offsets;
+  int32_t *my = s_masks + (size_t)warp * O * 32;
   const int lpr = a.lanes_per_row, rpi = 32 / lpr;
   const int sub = lane / lpr, part = lane % lpr;
   const int chunks = a.channels / kVecElems;
-  const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nw = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  const int64_t n_groups = (a.T_rows + rpi - 1) / rpi;
-  for (int64_t grp = gw; grp < n_groups; grp += nw) {
-    const int64_t t = grp * rpi + sub;
-    const bool live = t < a.T_rows;
-    float acc[kAcc];
+  const int64_t n_blocks32 = (a.T_rows + 31) >> 5;
+  for (int64_t blk = (int64_t)blockIdx.x * nwarps + warp; blk < n_blocks32;
+       blk += (int64_t)gridDim.x * nwarps) {
+    const int64_t t_lane = (blk << 5) + lane;
+    uint32_t hits[4] = {0u, 0u, 0u, 0u};   // bit o of word o/32: offset o feeds row `lane`
 #pragma unroll
-    for (int i = 0; i < kAcc; i++) acc[i] = 0.f;
-    for (int o = 0; o < a.num_offsets; o++) {
-      const int m = live ? __ldg(a.target_masks + (int64_t)o * a.T_rows + t) : -1;
-      if (m < 0) continue;
-      const V *src = reinterpret_cast<const V *>(a.buf + (plan.row_begin[o] + m) * a.channels);
+    for (int w = 0; w < 4; w++) {
+      if (w * 32 < O) {
+        for (int o0 = w * 32; o0 < min(O, w * 32 + 32); o0 += 8) {
+          int m[8];
 #pragma unroll
-      for (int i = 0; i < kAcc / kVecElems; i++) {
-        const int c = part + i * lpr;
-        if (c < chunks) {
-          const V v = __ldg(src + c);
-          const T *e = reinterpret_cast<const T *>(&v);
+          for (int i = 0; i < 8; i++)
+            m[i] = (t_lane < a.T_rows && o0 + i < O)
+                       ? __ldg(a.target_masks + (int64_t)(o0 + i) * a.T_rows + t_lane) : -1;
 #pragma unroll
-          for (int k = 0; k < kVecElems; k++) acc[i * kVecElems + k] += to_f32(e[k]);
-        }
-      }
-    }
-    if (live) {
-      V *dst = reinterpret_cast<V *>(a.out + t * a.channels);
-#pragma unroll
-      for (int i = 0; i < kAcc / kVecElems; i++) {
-        const int c = part + i * lpr;
-        if (c < chunks) {
-          V v;
-          T *e = reinterpret_cast<T *>(&v);
-          if (a.add_existing) {
-            const V old = dst[c];
-            const T *oe = reinterpret_cast<const T *>(&old);
-#pragma unroll
-            for (int k = 0; k < kVecElems; k++)
-              e[k] = from_f32<T>(acc[i * kVecElems + k] + to_f32(oe[k]));
-          } else {
-#pragma unroll
-            for (int k = 0; k < kVecElems; k++) e[k] = from_f32<T>(acc[i * kVecElems + k]);
+          for (int i = 0; i < 8; i++) {
+            if (o0 + i < O) my[(o0 + i) * 32 + lane] = m[i];
+            hits[w] |= (m[i] >= 0 ? 1u : 0u) << ((o0 + i) & 31);
           }
-          dst[c] = v;
         }
       }
     }
+    __syncwarp();
+    for (int r0 = 0; r0 < 32; r0 += rpi) {
+      const int r = r0 + sub;
+      const int64_t t = (blk << 5) + r;
+      float acc[kAcc];
+#pragma unroll
+      for (int i = 0; i < kAcc; i++) acc[i] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; w++) {
+        if (w * 32 < O) {
+          uint32_t h = __shfl_sync(0xffffffffu, hits[w], r);
+          while (h != 0u) {
+            const int o = w * 32 + __ffs(h) - 1;
+            h &= h - 1u;
+            const int m = my[o * 32 + r];
+            const V *src = reinterpret_cast<const V *>(a.buf + (plan.row_begin[o] + m) * a.channels);
+#pragma unroll
+            for (int i = 0; i < kAcc / kVecElems; i++) {
+              const int c = part + i * lpr;
+              if (c < chunks) {
+                const V v = __ldg(src + c);
+                const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int k = 0; k < kVecElems; k++) acc[i * kVecElems + k] += to_f32(e[k]);
+              }
+            }
+          }
+        }
+      }
+      if (t < a.T_rows) {
+        V *dst = reinterpret_cast<V *>(a.out + t * a.channels);
+#pragma unroll
+        for (int i = 0; i < kAcc / kVecElems; i++) {
+          const int c = part + i * lpr;
+          if (c < chunks) {
+            V v;
+            T *e = reinterpret_cast<T *>(&v);
+            if (a.add_existing) {
+              const V old = dst[c];
+              const T *oe = reinterpret_cast<const T *>(&old);
+#pragma unroll
+              for (int k = 0; k < kVecElems; k++)
+                e[k] = from_f32<T>(acc[i * kVecElems + k] + to_f32(oe[k]));
+            } else {
+#pragma unroll
+              for (int k = 0; k < kVecElems; k++) e[k] = from_f32<T>(acc[i * kVecElems + k]);
+            }
+            dst[c] = v;
+          }
+        }
+      }
+    }
+    __syncwarp();
   }
 }
+
+}  // namespace
+
+namespace {
 
 constexpr int kGemmTM = 64, kGemmTN = 64, kGemmTK = 16;
 
@@ -375,15 +424,19 @@ mn_status run_scatter_t(const ConvLayout &L, const ConvBuffers &b, int64_t T_row
   a.channels = (int)c_out;
   a.lanes_per_row = lpr;
   a.add_existing = L.shortcut ? 1 : 0;
-  const int rpi = 32 / lpr;
-  const int64_t warps = div_up(T_rows, rpi);
-  const int blocks = (int)std::min<int64_t>(kNumSMs * 16, div_up(warps, 8));
+  // shared memory: one 128-byte row of mask words per (warp, offset)
+  const int n_off = std::max(L.n_buf, 1);
+  const int warps_per_block = n_off <= 32 ? 8 : (n_off <= 64 ? 4 : 2);
+  const int threads = warps_per_block * 32;
+  const size_t smem = (size_t)warps_per_block * n_off * 32 * sizeof(int32_t);
+  const int blocks =
+      (int)std::min<int64_t>(kNumSMs * 16, div_up(div_up(T_rows, 32), warps_per_block));
   const int need = acc_needed(lpr);
-#define MN_SCATTER(VE)                                                                   \
-  do {                                                                                   \
-    if (need <= 8) scatter_kernel<T, VE, 8><<<blocks, 256, 0, st>>>(a, L.plan);          \
-    else if (need <= 16) scatter_kernel<T, VE, 16><<<blocks, 256, 0, st>>>(a, L.plan);   \
-    else scatter_kernel<T, VE, 32><<<blocks, 256, 0, st>>>(a, L.plan);                   \
+#define MN_SCATTER(VE)                                                                          \
+  do {                                                                                          \
+    if (need <= 8) scatter_kernel<T, VE, 8><<<blocks, threads, smem, st>>>(a, L.plan);          \
+    else if (need <= 16) scatter_kernel<T, VE, 16><<<blocks, threads, smem, st>>>(a, L.plan);   \
+    else scatter_kernel<T, VE, 32><<<blocks, threads, smem, st>>>(a, L.plan);                   \
   } while (0)
   {
   LaunchScope scope("scatter_kernel", st);
