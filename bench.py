@@ -281,6 +281,13 @@ def gpu_arm(args):
     value = voxels_all * args.steps / (ms_total * 1e-3) / 1e6
     e2e_value = voxels_all * args.steps / (ms_e2e * 1e-3) / 1e6
 
+    unet = None
+    if not args.no_unet:
+        del flush
+        torch.cuda.empty_cache()
+        unet = unet_section(args, torch, dist, dev, rank, world, lib)
+        flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -358,6 +365,7 @@ def gpu_arm(args):
         "roofline": roofline,
         "cpu_baseline": cpu,
         "gms_sweep": sweep,
+        "unet": unet,
         "wall_s": round(t_wall, 3),
     }
     print(json.dumps(line), flush=True)
@@ -406,6 +414,124 @@ def gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=(16, 32, 64, 128, 2
             "pairs_without_centre": E1, "dtype": "f16", "channels": out}
 
 
+UNET_CLOUDS = 64          # C4: 64 outdoor clouds in total, sharded over the ranks
+UNET_SEED0 = 3000
+
+
+def _make_cloud(seed):
+    from minuet_b200 import synth
+    return synth.outdoor_cloud(seed, VOXELS_PER_CLOUD)
+
+
+def unet_section(args, torch, dist, dev, rank, world, lib):
+    """Sparse UNet (fp16, random weights, eval-mode BatchNorm) on 64 outdoor clouds
+    sharded by cloud over the ranks; the logits are gathered with NCCL.  Strong
+    scaling: the 64 clouds are the whole job at every N."""
+    import concurrent.futures
+    import minuet_b200 as minuet
+    from minuet_b200 import sharding
+    from minuet_b200.unet import SparseUNet
+
+    shards = sharding.assign_clouds([VOXELS_PER_CLOUD] * UNET_CLOUDS, world)
+    mine = shards[rank]
+    with concurrent.futures.ProcessPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
+        clouds = list(pool.map(_make_cloud, [UNET_SEED0 + i for i in mine]))
+    coords = np.ascontiguousarray(np.concatenate(clouds).astype(np.int32))
+    bd = np.zeros(len(clouds) + 1, dtype=np.int64)
+    bd[1:] = np.cumsum([len(c) for c in clouds])
+    rng = np.random.default_rng(UNET_SEED0 + 7919 * rank)
+    feats = np.concatenate([coords.astype(np.float32) * 0.05,
+                            rng.random((len(coords), 1), dtype=np.float32)], axis=1)
+    h_coords = torch.from_numpy(coords).pin_memory()
+    h_bd = torch.from_numpy(bd).pin_memory()
+    h_feats = torch.from_numpy(feats).half().pin_memory()
+    d_coords, d_bd, d_feats = h_coords.to(dev), h_bd.to(dev), h_feats.to(dev)
+
+    torch.manual_seed(0)
+    net = SparseUNet(4, num_classes=20).to(dev).half().eval()
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
+    minuet.set_kernel_map_cache(net, cache)
+
+    def forward(c, b, f):
+        cache.reset()
+        with torch.no_grad():
+            out = net(minuet.SparseTensor(f, c, batch_dims=b))
+        if dist is not None:
+            return sharding.gather_rows(out.F, dst=0)
+        return [out.F]
+
+    def timed(fn, steps):
+        total = 0.0
+        for _ in range(steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            total += a.elapsed_time(b)
+        return total
+
+    steps, warm = args.unet_steps, 3
+    for _ in range(warm):
+        forward(d_coords, d_bd, d_feats)
+    launches0 = lib.mn_launch_count()
+    ms = timed(lambda: forward(d_coords, d_bd, d_feats), steps)
+    launches = lib.mn_launch_count() - launches0
+
+    def e2e():
+        c = h_coords.to(dev, non_blocking=True)
+        b = h_bd.to(dev, non_blocking=True)
+        f = h_feats.to(dev, non_blocking=True)
+        parts = forward(c, b, f)
+        if parts is not None:      # rank 0: per-voxel class labels go back to the host
+            return [p.argmax(dim=1).to(torch.uint8).cpu() for p in parts]
+        return None
+
+    e2e()
+    ms_e2e = timed(e2e, steps)
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = (float(v) for v in t.cpu())
+
+    kernels = None
+    if rank == 0:
+        lib.mn_profile_enable(1)
+        forward(d_coords, d_bd, d_feats)
+        torch.cuda.synchronize()
+        lib.mn_profile_enable(0)
+        buf = ctypes.create_string_buffer(1 << 16)
+        lib.mn_profile_report(buf, len(buf))
+        kernels = {}
+        for row in buf.value.decode().splitlines():
+            name, count, kms = row.rsplit(" ", 2)
+            kernels[name] = {"launches": int(count), "ms": round(float(kms), 4)}
+        kernels = dict(sorted(kernels.items(), key=lambda kv: -kv[1]["ms"]))
+    if dist is not None:
+        dist.barrier()
+    if rank != 0:
+        return None
+    return {
+        "metric": "sparse-UNet fp16 clouds/sec", "value": round(UNET_CLOUDS * steps / (ms * 1e-3), 2),
+        "unit": "clouds/s", "scaling": "strong", "ms_per_step": round(ms / steps, 3),
+        "steps": steps, "warmup": warm,
+        "config": {"workload": "C4: UNet (stem 32, encoder 32/64/128/256, decoder mirror, 20 "
+                               "classes) on 64 outdoor clouds x 120k voxels, 4-channel fp16 "
+                               "features, clouds sharded over the GPUs, NCCL gather of the logits",
+                   "clouds_total": UNET_CLOUDS, "clouds_on_rank0": len(mine),
+                   "voxels_on_rank0": int(len(coords))},
+        "e2e": {"value": round(UNET_CLOUDS * steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
+                "ms_per_step": round(ms_e2e / steps, 3),
+                "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_bd.numel() * 8 + h_feats.numel() * 2),
+                "d2h_bytes_per_step": int(UNET_CLOUDS * VOXELS_PER_CLOUD)},
+        "gpu_launches": int(launches),
+        "library_kernel_ms_rank0_one_step": kernels,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -413,6 +539,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-unet", action="store_true",
+                    help="skip the secondary end-to-end UNet measurement")
+    ap.add_argument("--unet-steps", type=int, default=5)
     ap.add_argument("--gms-sweep", action="store_true",
                     help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
     args = ap.parse_args()

@@ -5,7 +5,7 @@
 // bucket on up to four streams
 // (csrc/minuet/cuda/functions/sparse_convolution.cu:586-641, 647-660).
 //
-// Layout of one CTA (192 threads, one CTA per SM, no clusters, no multicast):
+// Layout of one CTA (192 threads, one CTA per SM, cluster size 1, every TMA load is CTA-local):
 //   warp 0      TMA producer: A tile [128 rows x 64 k] and B tile [N x 64 k] per
 //               k-block into a ring of shared-memory stages (128-byte swizzle)
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits

@@ -11,7 +11,23 @@ import numpy as np
 
 def sort_unique(coords: np.ndarray) -> np.ndarray:
     """Unique rows in lexicographic order, dimension 0 most significant."""
-    coords = np.unique(np.asarray(coords, dtype=np.int64), axis=0)
+    coords = np.asarray(coords, dtype=np.int64)
+    if coords.shape[0] == 0:
+        return np.ascontiguousarray(coords.astype(np.int32))
+    lo = coords.min(axis=0)
+    span = coords.max(axis=0) - lo + 1
+    if float(np.prod(span.astype(np.float64))) < 2.0 ** 62:
+        # one 1-D unique over packed keys is an order of magnitude faster than axis=0
+        key = np.zeros(coords.shape[0], dtype=np.int64)
+        for k in range(coords.shape[1]):
+            key = key * span[k] + (coords[:, k] - lo[k])
+        key = np.unique(key)
+        out = np.empty((key.shape[0], coords.shape[1]), dtype=np.int64)
+        for k in range(coords.shape[1] - 1, -1, -1):
+            out[:, k] = key % span[k] + lo[k]
+            key //= span[k]
+        return np.ascontiguousarray(out.astype(np.int32))
+    coords = np.unique(coords, axis=0)
     return np.ascontiguousarray(coords.astype(np.int32))
 
 

@@ -1,0 +1,82 @@
+"""Sparse UNet built from the path's own modules (SparseConv3d / SparseConv,
+BatchNorm, ReLU, cat).  The reference ships no model zoo; this is the network of
+the end-to-end benchmark configurations:
+
+  stem 3^3 conv -> 32 channels;
+  4 encoder stages (2^3 stride-2 conv + 2 residual blocks of 3^3 convs) with
+  32 / 64 / 128 / 256 channels;
+  4 decoder stages (2^3 stride-2 transposed conv, skip concatenation, 2 residual
+  blocks); 1x1x1 head to the class logits.
+"""
+from typing import Sequence
+
+import torch
+from torch import nn
+
+from minuet_b200.nn import BatchNorm, ReLU, SparseConv, SparseConv3d
+from minuet_b200.nn import functional as F
+from minuet_b200.tensors import SparseTensor
+
+
+class ConvBlock(nn.Sequential):
+    def __init__(self, c_in: int, c_out: int, kernel_size: int, stride: int = 1,
+                 transposed: bool = False):
+        if transposed:
+            conv = SparseConv(3, c_in, c_out, kernel_size, stride=stride, transposed=True)
+        else:
+            conv = SparseConv3d(c_in, c_out, kernel_size, stride=stride)
+        super().__init__(conv, BatchNorm(c_out), ReLU(inplace=True))
+
+
+class ResidualBlock(nn.Module):
+    """conv3-BN-ReLU-conv3-BN plus the (projected) input, then ReLU."""
+
+    def __init__(self, c_in: int, c_out: int):
+        super().__init__()
+        self.body = nn.Sequential(SparseConv3d(c_in, c_out, 3), BatchNorm(c_out),
+                                  ReLU(inplace=True), SparseConv3d(c_out, c_out, 3),
+                                  BatchNorm(c_out))
+        self.project = None
+        if c_in != c_out:
+            self.project = nn.Sequential(SparseConv3d(c_in, c_out, 1), BatchNorm(c_out))
+        self.relu = ReLU(inplace=True)
+
+    def forward(self, x: SparseTensor) -> SparseTensor:
+        y = self.body(x)
+        skip = x if self.project is None else self.project(x)
+        out = SparseTensor(y.F + skip.F, y.C, stride=y.stride, batch_dims=y.batch_dims)
+        return self.relu(out)
+
+
+class SparseUNet(nn.Module):
+    def __init__(self, in_channels: int, num_classes: int = 20,
+                 channels: Sequence[int] = (32, 64, 128, 256), stem_channels: int = 32):
+        super().__init__()
+        self.stem = ConvBlock(in_channels, stem_channels, 3)
+        self.down = nn.ModuleList()
+        self.enc = nn.ModuleList()
+        prev = stem_channels
+        for c in channels:
+            self.down.append(ConvBlock(prev, c, 2, stride=2))
+            self.enc.append(nn.Sequential(ResidualBlock(c, c), ResidualBlock(c, c)))
+            prev = c
+        skips = [stem_channels, *channels[:-1]]
+        self.up = nn.ModuleList()
+        self.dec = nn.ModuleList()
+        for skip_c in reversed(skips):
+            self.up.append(ConvBlock(prev, skip_c, 2, stride=2, transposed=True))
+            self.dec.append(nn.Sequential(ResidualBlock(2 * skip_c, skip_c),
+                                          ResidualBlock(skip_c, skip_c)))
+            prev = skip_c
+        self.head = SparseConv3d(prev, num_classes, 1)
+
+    def forward(self, x: SparseTensor) -> SparseTensor:
+        x = self.stem(x)
+        skips = []
+        for down, enc in zip(self.down, self.enc):
+            skips.append(x)
+            x = enc(down(x))
+        for up, dec in zip(self.up, self.dec):
+            x = up(x)
+            x = dec(F.cat([x, skips.pop()]))
+        return self.head(x)
