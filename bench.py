@@ -196,8 +196,10 @@ def gpu_arm(args):
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
+        import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that fails must not hold the others for long
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
 
     lib = _lib.load()
     coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000 + 100 * rank,
@@ -452,12 +454,15 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
     minuet.set_kernel_map_cache(net, cache)
 
-    def forward(c, b, f):
+    def local_forward(c, b, f):
         cache.reset()
         with torch.no_grad():
-            out = net(minuet.SparseTensor(f, c, batch_dims=b))
+            return net(minuet.SparseTensor(f, c, batch_dims=b))
+
+    def forward(c, b, f):
+        out = local_forward(c, b, f)
         if dist is not None:
-            return sharding.gather_rows(out.F, dst=0)
+            return sharding.gather_rows(out.F, dst=0)   # collective: every rank calls it
         return [out.F]
 
     def timed(fn, steps):
@@ -500,7 +505,7 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     kernels = None
     if rank == 0:
         lib.mn_profile_enable(1)
-        forward(d_coords, d_bd, d_feats)
+        local_forward(d_coords, d_bd, d_feats)      # rank-local: no collective in here
         torch.cuda.synchronize()
         lib.mn_profile_enable(0)
         buf = ctypes.create_string_buffer(1 << 16)
