@@ -350,7 +350,8 @@ def gpu_arm(args):
 
     sweep = None
     if world == 1 and args.gms_sweep:
-        sweep = gms_sweep(torch, minuet, cache, d_coords, d_bd)
+        chans = tuple(int(c) for c in args.gms_channels.split(","))
+        sweep = gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=chans)
 
     h2d = h_coords.numel() * 4 + h_bd.numel() * 8
     d2h = sum((k ** 3 + 1) * 4 + k ** 3 * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8 + 32
@@ -547,6 +548,7 @@ def main():
     ap.add_argument("--no-unet", action="store_true",
                     help="skip the secondary end-to-end UNet measurement")
     ap.add_argument("--unet-steps", type=int, default=5)
+    ap.add_argument("--gms-channels", default="16,32,64,128,256")
     ap.add_argument("--gms-sweep", action="store_true",
                     help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
     args = ap.parse_args()
