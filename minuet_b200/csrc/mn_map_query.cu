@@ -89,6 +89,13 @@ struct SearchArgs {
   int32_t fast_ok;       // every last-dimension offset is within +-kQPad
 };
 
+// One launch can serve two searches (e.g. targets->sources and sources->targets).
+struct SearchPair {
+  SearchArgs a[2];
+  OffsetTable tab[2];
+  int32_t tiles0;   // blocks of the first search
+};
+
 enum SearchMode { kMap = 0, kBits = 1 };
 
 // lower bound of q in win[a, b); trip count depends only on b - a (uniform)
@@ -142,7 +149,12 @@ __device__ __forceinline__ uint32_t hash_slot(uint32_t k) {
 // when they fit, binary-searched in global memory otherwise.
 template <int kMode>
 __global__ void __launch_bounds__(kQThreads, 8)
-search_kernel(const __grid_constant__ SearchArgs a, const __grid_constant__ OffsetTable tab) {
+search_kernel(const __grid_constant__ SearchPair sp) {
+  // blocks [0, tiles0) serve direction 0, the rest direction 1 (rows and table swapped)
+  const int dir = (int)blockIdx.x >= sp.tiles0 ? 1 : 0;
+  const int bid = (int)blockIdx.x - dir * sp.tiles0;
+  const SearchArgs &a = sp.a[dir];
+  const OffsetTable &tab = sp.tab[dir];
   __shared__ __align__(16) uint64_t s_win[kQWindow + 2];          // hash slots / general path
   __shared__ uint16_t s_hpos[kMode == kMap ? kQHash : 1];         // first position of a cell
   __shared__ int64_t s_delta[MN_MAX_OFFSETS];
@@ -155,7 +167,7 @@ search_kernel(const __grid_constant__ SearchArgs a, const __grid_constant__ Offs
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int O = tab.num_offsets, G = tab.num_groups;
   const int last = tab.ndim - 1;
-  const int64_t tile0 = (int64_t)blockIdx.x * kQTile;
+  const int64_t tile0 = (int64_t)bid * kQTile;
   const int tile_rows = (int)min((int64_t)kQTile, a.n_rows - tile0);
   const int64_t row0 = tile0 + tid * kQRows;
 
@@ -276,10 +288,20 @@ search_kernel(const __grid_constant__ SearchArgs a, const __grid_constant__ Offs
         }
       }
       if (kMode == kBits && e_span <= 32) {
-        bool any = false;
+        // hit bits only: every offset of the group is one bit of the row's 64-value
+        // strip, extracted without branches so that the warp stays converged
+        uint64_t strip[kQRows];
 #pragma unroll
-        for (int j = 0; j < kQRows; j++) any |= (mlo[j] | mhi[j]) != 0u;
-        if (!any) continue;  // no table key near any of the four rows for this group
+        for (int j = 0; j < kQRows; j++)
+          strip[j] = (((uint64_t)mhi[j] << 32) | mlo[j]) >> sh[j];
+        for (int m = mb; m < me; m++) {
+          const int o = tab.member[m];
+          const int de = tab.off[o][last] - e_first;   // 0..32
+#pragma unroll
+          for (int j = 0; j < kQRows; j++)
+            bits[j] |= ((uint32_t)(strip[j] >> de) & 1u) << o;
+        }
+        continue;
       }
       for (int m = mb; m < me; m++) {
         const int o = tab.member[m];
@@ -419,7 +441,7 @@ search_kernel(const __grid_constant__ SearchArgs a, const __grid_constant__ Offs
     }
     __syncthreads();
     for (int o = tid; o < O; o += kQThreads)
-      a.tile_counts[(int64_t)o * a.n_tiles + blockIdx.x] = s_counts[o];
+      a.tile_counts[(int64_t)o * a.n_tiles + bid] = s_counts[o];
   }
 }
 
@@ -665,25 +687,39 @@ map_masks_kernel(const int32_t *__restrict__ kernel_map, int64_t S, int64_t T, i
   }
 }
 
-mn_status run_search(int mode, const uint64_t *rows, int64_t n_rows, const uint64_t *table,
-                     int64_t n_table, const OffsetTable &tab, const mn_keyspec &spec,
-                     int32_t *kernel_map, uint32_t *hit_words, int32_t *tile_counts,
-                     cudaStream_t st) {
-  if (n_rows == 0) return MN_OK;
-  SearchArgs a{};
-  a.rows = rows; a.table = table; a.n_rows = n_rows; a.n_table = n_table;
-  a.kernel_map = kernel_map; a.hit_words = hit_words; a.tile_counts = tile_counts;
-  a.n_tiles = (int)div_up(n_rows, kQTile);
-  for (int k = 0; k < 4; k++) a.shift[k] = spec.shift[k];
-  a.fast_ok = spec.shift[spec.ndim - 1] == 0;
+void fill_search_args(SearchArgs *a, const uint64_t *rows, int64_t n_rows, const uint64_t *table,
+                      int64_t n_table, const OffsetTable &tab, const mn_keyspec &spec,
+                      int32_t *kernel_map, uint32_t *hit_words, int32_t *tile_counts) {
+  *a = SearchArgs{};
+  a->rows = rows; a->table = table; a->n_rows = n_rows; a->n_table = n_table;
+  a->kernel_map = kernel_map; a->hit_words = hit_words; a->tile_counts = tile_counts;
+  a->n_tiles = (int)div_up(n_rows, kQTile);
+  for (int k = 0; k < 4; k++) a->shift[k] = spec.shift[k];
+  a->fast_ok = spec.shift[spec.ndim - 1] == 0;
   for (int o = 0; o < tab.num_offsets; o++) {
     const int e = tab.off[o][tab.ndim - 1];
-    if (e > (int)kQPad || e < -(int)kQPad) a.fast_ok = 0;
+    if (e > (int)kQPad || e < -(int)kQPad) a->fast_ok = 0;
   }
+}
+
+// Launches one search, or two in the same grid when `second` is given.
+mn_status run_search(int mode, const SearchArgs &first, const OffsetTable &tab_first,
+                     const SearchArgs *second, const OffsetTable *tab_second, cudaStream_t st) {
+  thread_local static SearchPair sp;   // ~5 KB: kept off the stack; passed by value per launch
+  sp.a[0] = first;
+  sp.tab[0] = tab_first;
+  sp.tiles0 = first.n_tiles;
+  int blocks = first.n_tiles;
+  if (second != nullptr) {
+    sp.a[1] = *second;
+    sp.tab[1] = *tab_second;
+    blocks += second->n_tiles;
+  }
+  if (blocks == 0) return MN_OK;
   {
     LaunchScope scope(mode == kMap ? "search_kernel<map>" : "search_kernel<bits>", st);
-    if (mode == kMap) search_kernel<kMap><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
-    else search_kernel<kBits><<<a.n_tiles, kQThreads, 0, st>>>(a, tab);
+    if (mode == kMap) search_kernel<kMap><<<blocks, kQThreads, 0, st>>>(sp);
+    else search_kernel<kBits><<<blocks, kQThreads, 0, st>>>(sp);
   }
   MN_CHECK_LAUNCH();
   return MN_OK;
@@ -756,8 +792,9 @@ extern "C" mn_status mn_query_sorted_index_with_offsets(
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(target_keys != nullptr && kernel_map_out != nullptr && (S == 0 || source_keys != nullptr),
                "query: null pointer");
-  return run_search(kMap, target_keys, T, source_keys, S, tab, *spec, kernel_map_out, nullptr,
-                    nullptr, static_cast<cudaStream_t>(stream));
+  SearchArgs a;
+  fill_search_args(&a, target_keys, T, source_keys, S, tab, *spec, kernel_map_out, nullptr, nullptr);
+  return run_search(kMap, a, tab, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int64_t O, int64_t T,
@@ -864,13 +901,16 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
                    target_masks_out != nullptr, "build_kernel_map: null pointer");
 
-  MN_RETURN_IF(run_search(kBits, target_keys, T, source_keys, S, fwd, *spec, nullptr, words_t,
-                          counts_t, st));
-  if (!mirrored) {
+  SearchArgs fwd_args, bwd_args;
+  fill_search_args(&fwd_args, target_keys, T, source_keys, S, fwd, *spec, nullptr, words_t, counts_t);
+  if (mirrored) {
+    MN_RETURN_IF(run_search(kBits, fwd_args, fwd, nullptr, nullptr, st));
+  } else {
+    // second direction in the same launch: sources as rows, targets as table, -offsets
     OffsetTable bwd;
     MN_RETURN_IF(make_offset_table(offsets, O, ndim, -1, spec, &bwd));
-    MN_RETURN_IF(run_search(kBits, source_keys, S, target_keys, T, bwd, *spec, nullptr, words_s,
-                            counts_s, st));
+    fill_search_args(&bwd_args, source_keys, S, target_keys, T, bwd, *spec, nullptr, words_s, counts_s);
+    MN_RETURN_IF(run_search(kBits, fwd_args, fwd, &bwd_args, &bwd, st));
   }
   ScanArgs p{};
   p.counts[0] = counts_t; p.tiles[0] = tiles_t;

@@ -22,8 +22,8 @@ namespace {
 // ---------------------------------------------------------------------------
 constexpr int kRsThreads = 256;
 constexpr int kRsWarps = kRsThreads / 32;
-constexpr int kRsItems = 16;                      // keys per thread
-constexpr int kRsTile = kRsThreads * kRsItems;    // 4096 keys per block
+constexpr int kRsItems = 4;                       // keys per thread
+constexpr int kRsTile = kRsThreads * kRsItems;    // 1024 keys per block
 constexpr int kRadix = 256;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
@@ -73,8 +73,8 @@ radix_scan_kernel(uint32_t *__restrict__ block_hist, int nblocks,
   if (lane == 0) digit_total[d] = carry;
 }
 
-// Stable scatter.  Warp w owns keys [w*512, w*512+512) of the tile and walks
-// them in 16 chunks of 32 consecutive keys; inside a chunk lanes with equal
+// Stable scatter.  Warp w owns kRsItems*32 consecutive keys of the tile and walks
+// them in chunks of 32 consecutive keys; inside a chunk lanes with equal
 // digits find each other with match.any, the lowest lane bumps the warp's digit
 // counter, and every lane's rank is counter + number of equal lanes below it.
 template <bool kHasVals>
