@@ -130,6 +130,9 @@ struct TcOperands {
   int64_t gathered_rows = 0;
   const void *sources = nullptr;    // [source_rows, c_in]
   int64_t source_rows = 0;
+  void *products = nullptr;         // [gathered_rows, c_out]: outputs of the buffered problems
+  void *out = nullptr;              // [out_rows, c_out]: output of the direct problem
+  int64_t out_rows = 0;
   void *weights_t = nullptr;        // scratch for the transposed weights [O, c_out, c_in]
   int num_weights = 0;              // O
   int32_t *status = nullptr;        // device status word

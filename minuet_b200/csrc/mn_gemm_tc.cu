@@ -108,6 +108,12 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+               "r"(x), "r"(y), "r"(smem_u32(src))
+               : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle:
 // rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -168,7 +174,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ TcArgs args,
                const __grid_constant__ CUtensorMap map_a,       // gather buffer  [rows, K]
                const __grid_constant__ CUtensorMap map_direct,  // input features [S, K]
-               const __grid_constant__ CUtensorMap map_b) {     // weights^T      [O, N, K]
+               const __grid_constant__ CUtensorMap map_b,       // weights^T      [O, N, K]
+               const __grid_constant__ CUtensorMap map_c,       // product buffer [rows, N]
+               const __grid_constant__ CUtensorMap map_c_direct) {  // output features [T, N]
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kMaxStages], bar_empty[kMaxStages];
   __shared__ uint64_t bar_acc_full[2], bar_acc_empty[2];
@@ -261,45 +269,61 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
+    // Each warp turns its 32 accumulator rows into 16-bit, 64 columns at a time,
+    // parks them in a 128-byte-swizzled shared tile and lets TMA store the tile:
+    // full 128-byte lines reach memory, rows past the end of the output array
+    // are clipped by the tensor map, rows past the end of a problem land in the
+    // padding of the product buffer.
     const int quarter = warp & 3;           // TMEM lanes a warp may read: 32 * (warp id % 4)
-    int acc = 0;
+    uint8_t *cbuf = stage_base + (size_t)stages * args.stage_bytes + (size_t)(warp - 2) * 8192;
+    int acc = 0, chunk = 0;
     uint32_t acc_phase = 0;
-    const int n = args.c_out;
     for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
       const TilePos pos = locate_tile(tab, tile);
       const int p = pos.problem;
       if (!mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = pos.m0 + quarter * 32 + lane;
-      const bool live = row < tab.rows[p];
-      T *crow = static_cast<T *>(tab.c[p]) + (int64_t)row * n;
+      const bool direct = tab.direct[p] != 0;
+      const int out_row = (direct ? 0 : (int)tab.a_row[p]) + pos.m0 + quarter * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_pad);
-      for (int c0 = 0; c0 < args.n_pad; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+      for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
+        uint8_t *buf = cbuf + (chunk & 1) * 4096;
+        uint32_t r[64];
+        tmem_ld_32x32(taddr + (uint32_t)c0, *reinterpret_cast<uint32_t (*)[32]>(&r[0]));
+        if (c0 + 32 < args.n_pad) {
+          tmem_ld_32x32(taddr + (uint32_t)c0 + 32u, *reinterpret_cast<uint32_t (*)[32]>(&r[32]));
+        } else {
+#pragma unroll
+          for (int i = 32; i < 64; i++) r[i] = 0u;
+        }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (live) {
+        // the store that last read this buffer (two chunks ago) must be done with it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
 #pragma unroll
-          for (int v = 0; v < 4; v++) {       // 8 outputs = 16 bytes per store
-            const int c = c0 + v * 8;
-            if (c + 8 <= n) {
-              uint4 out;
-              uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
+        for (int v = 0; v < 8; v++) {         // 8 outputs = one 16-byte piece of the row
+          uint4 out;
+          uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
 #pragma unroll
-              for (int h = 0; h < 4; h++) {
-                const float lo = __uint_as_float(r[v * 8 + 2 * h]);
-                const float hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
-                if (sizeof(T) == 2 && args.elem_is_bf16) {
-                  __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
-                  o32[h] = *reinterpret_cast<uint32_t *>(&pk);
-                } else {
-                  __half2 pk = __floats2half2_rn(lo, hi);
-                  o32[h] = *reinterpret_cast<uint32_t *>(&pk);
-                }
-              }
-              *reinterpret_cast<uint4 *>(crow + c) = out;
+          for (int h = 0; h < 4; h++) {
+            const float lo = __uint_as_float(r[v * 8 + 2 * h]);
+            const float hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
+            if (args.elem_is_bf16) {
+              __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+            } else {
+              __half2 pk = __floats2half2_rn(lo, hi);
+              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
             }
           }
+          // 128-byte swizzle: 16-byte piece v of row `lane` lives at piece v ^ (lane % 8)
+          *reinterpret_cast<uint4 *>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = out;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(direct ? &map_c_direct : &map_c, c0, out_row, buf);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -307,6 +331,8 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
       if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -437,13 +463,14 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
   args.c_out = c_out;
   args.a_bytes = kBM * kBK * 2;
   args.stage_bytes = args.a_bytes + args.n_pad * kBK * 2;
-  args.stages = std::min(kMaxStages, std::max(2, (200 * 1024) / args.stage_bytes));
+  // 227 KB per CTA: 1 KB alignment slack + 32 KB of epilogue tiles + the operand ring
+  args.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / args.stage_bytes));
   args.elem_is_bf16 = bf16 ? 1 : 0;
   args.total_tiles = total_tiles;
   args.order = order;
   args.status = ops.status;
 
-  CUtensorMap map_a, map_direct, map_b;
+  CUtensorMap map_a, map_direct, map_b, map_c, map_c_direct;
   // an operand that no problem uses still needs a valid map: point it at the other one
   const void *gather_base = ops.gathered != nullptr ? ops.gathered : ops.sources;
   const int64_t gather_rows = ops.gathered != nullptr ? ops.gathered_rows : ops.source_rows;
@@ -457,23 +484,35 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
   MN_RETURN_IF(make_map(&map_a, gather_base, bf16, c_in, gather_rows, 0, kBM));
   MN_RETURN_IF(make_map(&map_direct, direct_base, bf16, c_in, direct_rows, 0, kBM));
   MN_RETURN_IF(make_map(&map_b, ops.weights_t, bf16, c_in, c_out, O, args.n_pad));
+  // outputs: [rows, N], box 64 columns x 32 rows (one epilogue warp), 128-byte swizzle
+  const void *prod_base = ops.products != nullptr ? ops.products : ops.out;
+  const int64_t prod_rows = ops.products != nullptr ? ops.gathered_rows : ops.out_rows;
+  const void *out_base = ops.out != nullptr ? ops.out : ops.products;
+  const int64_t out_rows = ops.out != nullptr ? ops.out_rows : ops.gathered_rows;
+  MN_CHECK_ARG(prod_base != nullptr && prod_rows > 0 &&
+                   (reinterpret_cast<uintptr_t>(prod_base) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out_base) & 15) == 0,
+               "gemm_tc: outputs must exist and be 16-byte aligned");
+  MN_RETURN_IF(make_map(&map_c, prod_base, bf16, c_out, prod_rows, 0, 32));
+  MN_RETURN_IF(make_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
 
   // at least 120 KB so that two CTAs (each allocating all 512 TMEM columns) can
   // never share an SM
-  const size_t smem = std::max<size_t>((size_t)args.stages * args.stage_bytes + 1024, 120 * 1024);
+  const size_t smem =
+      std::max<size_t>((size_t)args.stages * args.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
   const int grid = std::min(total_tiles, kNumSMs);
   if (bf16) {
     MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MN_LAUNCH("gemm_tc_kernel", st,
-              gemm_tc_kernel<__nv_bfloat16><<<grid, kTcThreads, smem, st>>>(tab, args, map_a,
-                                                                            map_direct, map_b));
+              gemm_tc_kernel<__nv_bfloat16><<<grid, kTcThreads, smem, st>>>(
+                  tab, args, map_a, map_direct, map_b, map_c, map_c_direct));
   } else {
     MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__half>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MN_LAUNCH("gemm_tc_kernel", st,
               gemm_tc_kernel<__half><<<grid, kTcThreads, smem, st>>>(tab, args, map_a, map_direct,
-                                                                    map_b));
+                                                                    map_b, map_c, map_c_direct));
   }
   *handled = true;
   return MN_OK;

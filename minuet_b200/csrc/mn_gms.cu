@@ -462,8 +462,8 @@ mn_status run_scatter(const ConvLayout &L, const ConvBuffers &b, int64_t T_rows,
 
 mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *sizes, int64_t O,
                    int64_t S, int64_t c_in, int64_t c_out, mn_dtype dtype, const void *sources,
-                   const void *weights, const int32_t *order, void *out, int32_t *status_dev,
-                   cudaStream_t st) {
+                   const void *weights, const int32_t *order, void *out, int64_t out_rows,
+                   int32_t *status_dev, cudaStream_t st) {
   const size_t e = dtype_size(dtype);
   GemmTable tab{};
   int np = 0;
@@ -495,6 +495,9 @@ mn_status run_gemm(const ConvLayout &L, const ConvBuffers &b, const int32_t *siz
   ops.gathered_rows = L.total_rows;
   ops.sources = S > 0 ? sources : nullptr;
   ops.source_rows = S;
+  ops.products = L.total_rows > 0 ? b.products : nullptr;
+  ops.out = out;
+  ops.out_rows = out_rows;
   ops.weights_t = b.weights_t;
   ops.num_weights = (int)O;
   ops.status = status_dev;
@@ -610,7 +613,7 @@ extern "C" mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, i
     case 1:
       MN_CHECK_ARG(sources != nullptr && weights != nullptr && targets_out != nullptr, "conv_stage: null pointer");
       return run_gemm(L, b, sizes_host, O, S, c_in, c_out, dtype, sources, weights, order,
-                      targets_out, status_dev, st);
+                      targets_out, T, status_dev, st);
     case 2:
       MN_CHECK_ARG(target_masks != nullptr && targets_out != nullptr, "conv_stage: null pointer");
       return run_scatter(L, b, T, c_out, dtype, target_masks, tile, targets_out, st);
@@ -638,7 +641,7 @@ extern "C" mn_status mn_sparse_convolution_forward(
   MN_RETURN_IF(carve(L, O, c_in, c_out, dtype, ws_ptr, ws_bytes, &b));
   MN_RETURN_IF(run_gather(L, b, S, c_in, dtype, sources, source_masks, gather_tile, st));
   MN_RETURN_IF(run_gemm(L, b, sizes_host, O, S, c_in, c_out, dtype, sources, weights, order,
-                        targets_out, status_dev, st));
+                        targets_out, T, status_dev, st));
   MN_RETURN_IF(run_scatter(L, b, T, c_out, dtype, target_masks, scatter_tile, targets_out, st));
   return MN_OK;
 }
