@@ -451,7 +451,7 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     d_coords, d_bd, d_feats = h_coords.to(dev), h_bd.to(dev), h_feats.to(dev)
 
     torch.manual_seed(0)
-    net = SparseUNet(4, num_classes=20).to(dev).half().eval()
+    net = SparseUNet(4, num_classes=20).to(dev).half().eval().fuse()
     cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
     minuet.set_kernel_map_cache(net, cache)
 

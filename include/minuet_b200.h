@@ -230,6 +230,43 @@ mn_status mn_conv_stage(int stage, int64_t S, int64_t T, int64_t O, int64_t c_in
                         int has_threshold, double threshold, void *targets_out,
                         int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
 
+/* ---- Fused (implicit-GEMM) forward ----------------------------------------- */
+/* No single counterpart in the reference: replaces the gather + bucket GEMMs +
+ * scatter + centre GEMM sequence of SparseConvolutionForward
+ * (csrc/minuet/cuda/functions/sparse_convolution.cu:505-661) by one kernel that
+ * keeps a 128-row target tile in TMEM and accumulates every offset into it.
+ * fp16/bf16, at most 32 offsets, channels multiple of 8, c_out <= 256. */
+int mn_implicit_supported(int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype);
+
+/* Neighbour table of a kernel map given as masks: nbr_out int32 [O, T] holds the
+ * source row feeding target t under mask row p, or -1; tile_bits_out uint32
+ * [ceil(T/128)] has bit p set when any target of that 128-row tile has a
+ * source under mask row p.  sizes_host: HOST sizes of the mask rows. */
+size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O);
+mn_status mn_build_neighbor_table(const int32_t *source_masks, const int32_t *target_masks,
+                                  const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
+                                  int32_t *nbr_out, uint32_t *tile_bits_out, void *ws,
+                                  size_t ws_bytes, void *stream);
+
+/* out[t] = epilogue(sum_p sources[nbr[p, t]] @ weights[order ? order[p] : p]) with
+ * epilogue(v) = relu?(v * scale[c] + shift[c] + residual[t, c]); scale, shift
+ * (fp32 [c_out]) and residual ([T, c_out], feature dtype) may each be NULL. */
+size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out);
+mn_status mn_sparse_convolution_forward_implicit(
+    int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
+    const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
+    const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
+    void *targets_out, int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
+
+/* In place: features[t, c] = relu?(features[t, c] * scale[c] + shift[c] + residual[t, c]);
+ * scale / shift (fp32 [channels]) and residual ([rows, channels], feature dtype)
+ * may be NULL.  The same epilogue the fused forward applies inside its kernel,
+ * for layers that go through gather - GEMM - scatter.  No reference counterpart
+ * (the reference's models run BatchNorm, add and ReLU as separate torch ops). */
+mn_status mn_apply_epilogue(void *features, int64_t rows, int64_t channels, mn_dtype dtype,
+                            const float *scale, const float *shift, const void *residual,
+                            int relu, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -76,6 +76,16 @@ PROTOTYPES = {
     "mn_conv_stage": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr,
                               c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_dbl, c_ptr, c_ptr, c_ptr,
                               c_size, c_ptr]),
+    "mn_apply_epilogue": (c_int, [c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    "mn_implicit_supported": (c_int, [c_i64, c_i64, c_i64, c_int]),
+    "mn_neighbor_table_workspace_bytes": (c_size, [c_ptr, c_i64]),
+    "mn_build_neighbor_table": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr,
+                                        c_size, c_ptr]),
+    "mn_implicit_workspace_bytes": (c_size, [c_i64, c_i64, c_i64]),
+    "mn_sparse_convolution_forward_implicit": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_int,
+                                                       c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                                                       c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr,
+                                                       c_size, c_ptr]),
 }
 
 _lib = None

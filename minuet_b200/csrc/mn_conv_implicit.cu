@@ -1,0 +1,435 @@
+// Fused (implicit-GEMM) forward pass of a sparse convolution, fp16/bf16.
+//
+// The reference gathers every (source, target) pair row into a padded buffer,
+// multiplies bucket by bucket with cuBLAS and scatters the products back
+// (csrc/minuet/cuda/functions/sparse_convolution.cu:505-661); every pair row
+// crosses HBM four times.  Here one persistent kernel owns 128 consecutive TARGET
+// rows at a time and accumulates ALL kernel offsets of that tile in one TMEM
+// accumulator:
+//   warps 0..3  producers: thread r fetches, for every active offset and k-block,
+//               the 128-byte slice of the source row that feeds target row r
+//               (cp.async straight into the 128-byte-swizzled A tile, zeros where
+//               the kernel map has no entry); thread 0 also starts the TMA load
+//               of the offset's transposed weight tile
+//   warp 4      allocates TMEM and issues tcgen05.mma over (offset, k-block)
+//   warps 5..8  epilogue: TMEM -> registers -> optional per-channel scale/shift
+//               (folded BatchNorm or bias), residual add, ReLU -> swizzled shared
+//               tile -> TMA store of the output rows
+// so that features are read once per pair (mostly from L2), outputs are written
+// once, and no pair-row buffer exists.  Offsets with no pair inside a tile are
+// skipped through a per-tile bit mask.  The neighbour table [O, T] (source row
+// of target t under mask row p, or -1) is derived once per kernel map from the
+// masks by mn_build_neighbor_table.  Every barrier wait is bounded (status bit 2).
+#include "mn_tc.cuh"
+
+#include <algorithm>
+
+namespace mn {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kImThreads = 288;
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kMaxStages = 10;
+
+struct ImArgs {
+  const uint8_t *in;          // [S, K] 16-bit
+  const int32_t *nbr;         // [O, T]
+  const uint32_t *tile_bits;  // [tiles]
+  const int32_t *order;       // [O] or NULL
+  const float *scale;         // [N] or NULL
+  const float *shift;         // [N] or NULL
+  const uint8_t *residual;    // [T, N] 16-bit or NULL
+  int32_t *status;
+  int64_t T;
+  int32_t K, N, n_pad, k_blocks, stages, a_bytes, stage_bytes, elem_is_bf16, num_tiles, relu;
+};
+
+// 16-byte asynchronous copy; src_bytes = 0 writes 16 zero bytes instead (the fill
+// travels the same path as the copies, so no proxy fence is needed for it)
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+
+template <bool kBf16>
+__device__ __forceinline__ float elem_to_f32(uint16_t v) {
+  if (kBf16) return __uint_as_float((uint32_t)v << 16);
+  return __half2float(__ushort_as_half(v));
+}
+
+__global__ void __launch_bounds__(kImThreads, 1)
+conv_implicit_kernel(const __grid_constant__ ImArgs args,
+                     const __grid_constant__ CUtensorMap map_b,     // weights^T [O, N, K]
+                     const __grid_constant__ CUtensorMap map_out) { // output    [T, N]
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[kMaxStages], bar_empty[kMaxStages];
+  __shared__ uint64_t bar_acc_full[2], bar_acc_empty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  uint8_t *stage_base = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = args.stages;
+  const uint32_t tmem_cols = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; s++) {
+      mbar_init(&bar_full[s], kBM + 1);   // 128 row producers + the weight tile's expect_tx
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int a = 0; a < 2; a++) { mbar_init(&bar_acc_full[a], 1); mbar_init(&bar_acc_empty[a], 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)), "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int *abort_flag = &s_abort;
+
+  if (warp < 4) {
+    // ------------------------------ producers ---------------------------------
+    const int r = threadIdx.x;               // A-tile row owned by this thread
+    const uint32_t b_bytes = (uint32_t)(args.stage_bytes - args.a_bytes);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
+      const int64_t t = (int64_t)tile * kBM + r;
+      const bool row_live = t < args.T;
+      const uint32_t bits = __ldg(args.tile_bits + tile);
+      // this row's source under every active offset: all loads issued together, so
+      // the tile pays one memory latency instead of one per offset
+      int nb[32];
+#pragma unroll
+      for (int p = 0; p < 32; p++)
+        nb[p] = (row_live && ((bits >> p) & 1u)) ? __ldg(args.nbr + (int64_t)p * args.T + t) : -1;
+#pragma unroll
+      for (int p = 0; p < 32; p++) {
+        if (!alive || !((bits >> p) & 1u)) continue;
+        const int src = nb[p];
+        const uint8_t *src_row = args.in + (int64_t)(src < 0 ? 0 : src) * args.K * 2;
+        for (int kb = 0; kb < args.k_blocks; kb++) {
+          if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag, args.status)) { alive = false; break; }
+          uint8_t *sa = stage_base + (size_t)stage * args.stage_bytes;
+          if (r == 0) {
+            const int widx = args.order != nullptr ? __ldg(args.order + p) : p;
+            mbar_expect_tx(&bar_full[stage], b_bytes);
+            tma_load_3d(sa + args.a_bytes, &map_b, kb * kBK, 0, widx, &bar_full[stage]);
+          }
+          const uint32_t dst_row = smem_u32(sa) + (uint32_t)r * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int kcol = kb * kBK + j * 8;
+            const uint32_t dst = dst_row + (uint32_t)((j ^ (r & 7)) << 4);
+            const bool valid = src >= 0 && kcol < args.K;
+            cp_async_16(dst, valid ? src_row + (size_t)kcol * 2 : args.in, valid ? 16u : 0u);
+          }
+          // this thread's arrival fires when its copies above have landed: no stall here
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
+                           smem_u32(&bar_full[stage]))
+                       : "memory");
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this thread is in flight at exit
+  } else if (warp == 4) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t fmt = args.elem_is_bf16 ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) |
+                             ((uint32_t)(args.n_pad >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_flag, args.status)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * args.n_pad);
+        const int n_stage = __popc(__ldg(args.tile_bits + tile)) * args.k_blocks;
+        uint32_t accumulate = 0u;
+        for (int it = 0; it < n_stage; it++) {
+          const int kb = it % args.k_blocks;
+          if (!mbar_wait(&bar_full[stage], phase, abort_flag, args.status)) { alive = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(stage_base + (size_t)stage * args.stage_bytes);
+          const uint32_t sb = sa + (uint32_t)args.a_bytes;
+          const int nk = min(kBK / kUmmaK, (args.K - kb * kBK + kUmmaK - 1) / kUmmaK);
+          for (int k = 0; k < nk; k++) {
+            umma_f16(tmem_d, umma_desc(sa + k * kUmmaK * 2), umma_desc(sb + k * kUmmaK * 2), idesc,
+                     accumulate);
+            accumulate = 1u;
+          }
+          umma_commit(&bar_empty[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!alive) break;
+        umma_commit(&bar_acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;
+    uint8_t *cbuf = stage_base + (size_t)stages * args.stage_bytes + (size_t)(warp - 5) * 8192;
+    int acc = 0, chunk = 0;
+    uint32_t acc_phase = 0;
+    const int n = args.N;
+    for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
+      if (!mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool empty_tile = __ldg(args.tile_bits + tile) == 0u;   // no pair: the rows are zero
+      const int out_row = tile * kBM + quarter * 32;
+      const int64_t row = (int64_t)out_row + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_pad);
+      for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
+        uint8_t *buf = cbuf + (chunk & 1) * 4096;
+        uint32_t rr[64];
+        tmem_ld_32x32(taddr + (uint32_t)c0, *reinterpret_cast<uint32_t (*)[32]>(&rr[0]));
+        if (c0 + 32 < args.n_pad) {
+          tmem_ld_32x32(taddr + (uint32_t)c0 + 32u, *reinterpret_cast<uint32_t (*)[32]>(&rr[32]));
+        } else {
+#pragma unroll
+          for (int i = 32; i < 64; i++) rr[i] = 0u;
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int v = 0; v < 8; v++) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) f[i] = empty_tile ? 0.f : __uint_as_float(rr[v * 8 + i]);
+          const int c = c0 + v * 8;
+          if (c < n) {
+            if (args.scale != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] *= __ldg(args.scale + c + i);
+            }
+            if (args.shift != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] += __ldg(args.shift + c + i);
+            }
+            if (args.residual != nullptr && row < args.T) {
+              const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(args.residual + (row * n + c) * 2));
+              const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
+#pragma unroll
+              for (int i = 0; i < 8; i++)
+                f[i] += args.elem_is_bf16 ? elem_to_f32<true>(r16[i]) : elem_to_f32<false>(r16[i]);
+            }
+            if (args.relu) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
+            }
+          }
+          uint4 out;
+          uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+          for (int h = 0; h < 4; h++) {
+            if (args.elem_is_bf16) {
+              __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * h], f[2 * h + 1]);
+              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+            } else {
+              __half2 pk = __floats2half2_rn(f[2 * h], f[2 * h + 1]);
+              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+            }
+          }
+          *reinterpret_cast<uint4 *>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = out;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_out, c0, out_row, buf);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s_abort) {
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---- neighbour table from masks --------------------------------------------------
+struct CumSizes {
+  int64_t cum[MN_MAX_OFFSETS + 1];
+};
+
+// src_of_rank[cum[p] + source_masks[p, s]] = s
+__global__ void __launch_bounds__(256)
+rank_to_source_kernel(const int32_t *__restrict__ source_masks, int64_t S, int O,
+                      const __grid_constant__ CumSizes cs, int32_t *__restrict__ src_of_rank) {
+  const int p = blockIdx.y;
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < S; s += gsz) {
+    const int m = __ldg(source_masks + (int64_t)p * S + s);
+    if (m >= 0) src_of_rank[cs.cum[p] + m] = (int32_t)s;
+  }
+}
+
+// nbr[p, t] = source row feeding target t under mask row p (or -1); bit p of
+// tile_bits[t / 128] is set when any row of that 128-row tile has such a source
+__global__ void __launch_bounds__(128)
+neighbor_table_kernel(const int32_t *__restrict__ target_masks, int64_t T, int O,
+                      const __grid_constant__ CumSizes cs,
+                      const int32_t *__restrict__ src_of_rank, int32_t *__restrict__ nbr,
+                      uint32_t *__restrict__ tile_bits) {
+  __shared__ uint32_t s_bits;
+  if (threadIdx.x == 0) s_bits = 0u;
+  __syncthreads();
+  const int64_t t = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  uint32_t mine = 0u;
+  for (int p = 0; p < O; p++) {
+    int v = -1;
+    if (t < T) {
+      const int m = __ldg(target_masks + (int64_t)p * T + t);
+      if (m >= 0) v = __ldg(src_of_rank + cs.cum[p] + m);
+      nbr[(int64_t)p * T + t] = v;
+    }
+    mine |= (v >= 0 ? 1u : 0u) << p;
+  }
+  mine = __reduce_or_sync(0xffffffffu, mine);
+  if ((threadIdx.x & 31) == 0 && mine != 0u) atomicOr(&s_bits, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) tile_bits[blockIdx.x] = s_bits;
+}
+
+}  // namespace
+}  // namespace mn
+
+using namespace mn;
+
+extern "C" int mn_implicit_supported(int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype) {
+  return (dtype == MN_F16 || dtype == MN_BF16) && O >= 1 && O <= 32 && c_in >= 8 && c_in % 8 == 0 &&
+         c_out >= 8 && c_out % 8 == 0 && c_out <= 256;
+}
+
+extern "C" size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O) {
+  int64_t e = 0;
+  for (int64_t p = 0; p < O; p++) e += sizes_host[p];
+  return align_up((size_t)std::max<int64_t>(e, 1) * sizeof(int32_t), 256) + 256;
+}
+
+extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
+                                             const int32_t *target_masks,
+                                             const int32_t *sizes_host, int64_t O, int64_t S,
+                                             int64_t T, int32_t *nbr_out, uint32_t *tile_bits_out,
+                                             void *ws_ptr, size_t ws_bytes, void *stream) {
+  MN_CHECK_ARG(O >= 1 && O <= 32, "neighbor table: %lld offsets (supported: 1..32)", (long long)O);
+  MN_CHECK_ARG(S >= 0 && T >= 0 && sizes_host != nullptr, "neighbor table: bad arguments");
+  if (T == 0) return MN_OK;
+  MN_CHECK_ARG(source_masks != nullptr && target_masks != nullptr && nbr_out != nullptr &&
+                   tile_bits_out != nullptr, "neighbor table: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CumSizes cs{};
+  for (int64_t p = 0; p < O; p++) {
+    MN_CHECK_ARG(sizes_host[p] >= 0 && sizes_host[p] <= std::min(S, T), "neighbor table: bad size");
+    cs.cum[p + 1] = cs.cum[p] + sizes_host[p];
+  }
+  Workspace ws(ws_ptr, ws_bytes);
+  int32_t *src_of_rank = ws.take<int32_t>((size_t)std::max<int64_t>(cs.cum[O], 1));
+  MN_CHECK_WS(ws);
+  if (S > 0) {
+    const dim3 grid((unsigned)std::min<int64_t>(kNumSMs * 4, div_up(S, 256)), (unsigned)O);
+    MN_LAUNCH("rank_to_source_kernel", st,
+              rank_to_source_kernel<<<grid, 256, 0, st>>>(source_masks, S, (int)O, cs, src_of_rank));
+  }
+  MN_LAUNCH("neighbor_table_kernel", st,
+            neighbor_table_kernel<<<(unsigned)div_up(T, 128), 128, 0, st>>>(
+                target_masks, T, (int)O, cs, src_of_rank, nbr_out, tile_bits_out));
+  return MN_OK;
+}
+
+extern "C" size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out) {
+  return align_up((size_t)O * c_in * c_out * 2, 1024) + 1024;
+}
+
+extern "C" mn_status mn_sparse_convolution_forward_implicit(
+    int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
+    const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
+    const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
+    void *targets_out, int32_t *status_dev, void *ws_ptr, size_t ws_bytes, void *stream) {
+  if (!mn_implicit_supported(O, c_in, c_out, dtype)) {
+    set_error("implicit forward: needs fp16/bf16, at most 32 offsets, channels multiple of 8, "
+              "c_out <= 256 (got O=%lld c_in=%lld c_out=%lld dtype=%d)", (long long)O,
+              (long long)c_in, (long long)c_out, (int)dtype);
+    return MN_ERR_UNSUPPORTED;
+  }
+  MN_CHECK_ARG(S >= 0 && T >= 0 && T < (1ll << 31) && S < (1ll << 31), "implicit forward: bad sizes");
+  if (T == 0) return MN_OK;
+  MN_CHECK_ARG(weights != nullptr && nbr != nullptr && tile_bits != nullptr &&
+                   targets_out != nullptr && status_dev != nullptr && (S == 0 || sources != nullptr),
+               "implicit forward: null pointer");
+  MN_CHECK_ARG(((reinterpret_cast<uintptr_t>(sources) | reinterpret_cast<uintptr_t>(targets_out) |
+                 reinterpret_cast<uintptr_t>(residual)) & 15) == 0,
+               "implicit forward: feature arrays must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool bf16 = dtype == MN_BF16;
+  Workspace ws(ws_ptr, ws_bytes);
+  char *weights_t = ws.take<char>(align_up((size_t)O * c_in * c_out * 2, 1024));
+  MN_CHECK_WS(ws);
+  MN_RETURN_IF(launch_transpose_weights(weights, weights_t, (int)O, (int)c_in, (int)c_out, bf16, st));
+
+  ImArgs a{};
+  a.in = static_cast<const uint8_t *>(sources);
+  a.nbr = nbr;
+  a.tile_bits = tile_bits;
+  a.order = order;
+  a.scale = scale;
+  a.shift = shift;
+  a.residual = static_cast<const uint8_t *>(residual);
+  a.status = status_dev;
+  a.T = T;
+  a.K = (int)c_in;
+  a.N = (int)c_out;
+  a.n_pad = (int)align_up((size_t)c_out, 16);
+  a.k_blocks = (int)div_up(c_in, kBK);
+  a.a_bytes = kBM * kBK * 2;
+  a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
+  a.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / a.stage_bytes));
+  a.elem_is_bf16 = bf16 ? 1 : 0;
+  a.num_tiles = (int)div_up(T, kBM);
+  a.relu = relu ? 1 : 0;
+
+  CUtensorMap map_b, map_out;
+  MN_RETURN_IF(make_kmajor_map(&map_b, weights_t, bf16, c_in, c_out, O, a.n_pad));
+  MN_RETURN_IF(make_kmajor_map(&map_out, targets_out, bf16, c_out, T, 0, 32));
+  const size_t smem =
+      std::max<size_t>((size_t)a.stages * a.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
+  MN_CHECK_CUDA(cudaFuncSetAttribute(conv_implicit_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = std::min(a.num_tiles, kNumSMs);
+  MN_LAUNCH("conv_implicit_kernel", st,
+            conv_implicit_kernel<<<grid, kImThreads, smem, st>>>(a, map_b, map_out));
+  return MN_OK;
+}

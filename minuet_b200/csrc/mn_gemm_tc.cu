@@ -20,9 +20,7 @@
 // B is the weight matrix of one offset TRANSPOSED to [N, K] (K contiguous), so
 // that both operands are K-major; a small kernel transposes the layer's weights
 // into the workspace first.
-#include "mn_common.cuh"
-
-#include <cuda.h>
+#include "mn_tc.cuh"
 
 #include <algorithm>
 
@@ -30,12 +28,13 @@ namespace mn {
 
 namespace {
 
+using namespace tc;
+
 constexpr int kTcThreads = 192;
 constexpr int kBM = 128;            // rows per tile = UMMA M
 constexpr int kBK = 64;             // k elements per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 16;          // k elements per tcgen05.mma (16-bit inputs)
-constexpr int kMaxStages = 6;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kMaxStages = 10;
 
 struct TcArgs {
   int32_t k_blocks;      // ceil(c_in / 64)
@@ -49,111 +48,6 @@ struct TcArgs {
   const int32_t *order;  // device, may be NULL
   int32_t *status;       // device status word (bit 2: bounded wait expired)
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait: false when the limit expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int32_t *status) {
-  for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicOr(status, 4);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y,
-                                            uint64_t *bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z,
-                                            uint64_t *bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
-               "r"(x), "r"(y), "r"(smem_u32(src))
-               : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle:
-// rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);   // start address, bits [0,14)
-  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                         // layout: 128-byte swizzle
-  return d;
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
 
 struct TilePos {
   int problem;
@@ -369,6 +263,8 @@ transpose_weights_kernel(const T *__restrict__ w, T *__restrict__ wt, int K, int
     if (n0 + i < N && k0 + tx < K) dst[(int64_t)(n0 + i) * K + k0 + tx] = tile[tx][i];
 }
 
+}  // namespace
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -389,7 +285,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // K-major operand map: dims (K, rows[, batch]), box (64, box_rows[, 1]), 128-byte swizzle
-mn_status make_map(CUtensorMap *map, const void *base, bool bf16, int64_t K, int64_t rows,
+mn_status make_kmajor_map(CUtensorMap *map, const void *base, bool bf16, int64_t K, int64_t rows,
                    int64_t batch, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) {
@@ -413,7 +309,23 @@ mn_status make_map(CUtensorMap *map, const void *base, bool bf16, int64_t K, int
   return MN_OK;
 }
 
-}  // namespace
+
+mn_status launch_transpose_weights(const void *weights, void *weights_t, int O, int c_in, int c_out,
+                                   bool bf16, cudaStream_t st) {
+  const dim3 grid((unsigned)div_up(c_out, 32), (unsigned)div_up(c_in, 32), (unsigned)O);
+  if (bf16) {
+    MN_LAUNCH("transpose_weights_kernel", st,
+              transpose_weights_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+                  static_cast<const __nv_bfloat16 *>(weights),
+                  static_cast<__nv_bfloat16 *>(weights_t), c_in, c_out));
+  } else {
+    MN_LAUNCH("transpose_weights_kernel", st,
+              transpose_weights_kernel<__half><<<grid, 256, 0, st>>>(
+                  static_cast<const __half *>(weights), static_cast<__half *>(weights_t), c_in,
+                  c_out));
+  }
+  return MN_OK;
+}
 
 size_t gemm_tc_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out) {
   return align_up((size_t)O * c_in * c_out * 2, 1024);
@@ -434,20 +346,7 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
   const int O = ops.num_weights;
 
   // weights [O, K, N] -> [O, N, K]
-  {
-    const dim3 grid((unsigned)div_up(c_out, 32), (unsigned)div_up(c_in, 32), (unsigned)O);
-    if (bf16) {
-      MN_LAUNCH("transpose_weights_kernel", st,
-                transpose_weights_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-                    static_cast<const __nv_bfloat16 *>(weights),
-                    static_cast<__nv_bfloat16 *>(ops.weights_t), c_in, c_out));
-    } else {
-      MN_LAUNCH("transpose_weights_kernel", st,
-                transpose_weights_kernel<__half><<<grid, 256, 0, st>>>(
-                    static_cast<const __half *>(weights), static_cast<__half *>(ops.weights_t),
-                    c_in, c_out));
-    }
-  }
+  MN_RETURN_IF(launch_transpose_weights(weights, ops.weights_t, O, c_in, c_out, bf16, st));
 
   GemmTable tab = tab_in;
   tab.tile_rows = kBM;
@@ -481,9 +380,9 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
                    (reinterpret_cast<uintptr_t>(direct_base) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(ops.weights_t) & 15) == 0,
                "gemm_tc: operands must be 16-byte aligned");
-  MN_RETURN_IF(make_map(&map_a, gather_base, bf16, c_in, gather_rows, 0, kBM));
-  MN_RETURN_IF(make_map(&map_direct, direct_base, bf16, c_in, direct_rows, 0, kBM));
-  MN_RETURN_IF(make_map(&map_b, ops.weights_t, bf16, c_in, c_out, O, args.n_pad));
+  MN_RETURN_IF(make_kmajor_map(&map_a, gather_base, bf16, c_in, gather_rows, 0, kBM));
+  MN_RETURN_IF(make_kmajor_map(&map_direct, direct_base, bf16, c_in, direct_rows, 0, kBM));
+  MN_RETURN_IF(make_kmajor_map(&map_b, ops.weights_t, bf16, c_in, c_out, O, args.n_pad));
   // outputs: [rows, N], box 64 columns x 32 rows (one epilogue warp), 128-byte swizzle
   const void *prod_base = ops.products != nullptr ? ops.products : ops.out;
   const int64_t prod_rows = ops.products != nullptr ? ops.gathered_rows : ops.out_rows;
@@ -493,8 +392,8 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
                    (reinterpret_cast<uintptr_t>(prod_base) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(out_base) & 15) == 0,
                "gemm_tc: outputs must exist and be 16-byte aligned");
-  MN_RETURN_IF(make_map(&map_c, prod_base, bf16, c_out, prod_rows, 0, 32));
-  MN_RETURN_IF(make_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
+  MN_RETURN_IF(make_kmajor_map(&map_c, prod_base, bf16, c_out, prod_rows, 0, 32));
+  MN_RETURN_IF(make_kmajor_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
 
   // at least 120 KB so that two CTAs (each allocating all 512 TMEM columns) can
   // never share an SM

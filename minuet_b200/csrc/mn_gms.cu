@@ -547,6 +547,81 @@ mn_status check_conv_args(int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t
 
 using namespace mn;
 
+namespace mn {
+namespace {
+
+// x[t, c] = relu?(x[t, c] * scale[c] + shift[c] + residual[t, c]), in place, 8 (16-bit) or 4
+// (fp32) channels per thread
+template <typename T, int kVecElems>
+__global__ void __launch_bounds__(256)
+epilogue_kernel(T *__restrict__ x, int64_t n_vec, int vec_per_row, const float *__restrict__ scale,
+                const float *__restrict__ shift, const T *__restrict__ residual, int relu) {
+  using V = typename Chunk<kVecElems * sizeof(T)>::type;
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += gsz) {
+    const int c0 = (int)(i % vec_per_row) * kVecElems;
+    V v = reinterpret_cast<V *>(x)[i];
+    T *e = reinterpret_cast<T *>(&v);
+    V rv{};
+    if (residual != nullptr) rv = __ldg(reinterpret_cast<const V *>(residual) + i);
+    const T *re = reinterpret_cast<const T *>(&rv);
+#pragma unroll
+    for (int k = 0; k < kVecElems; k++) {
+      float f = to_f32(e[k]);
+      if (scale != nullptr) f *= __ldg(scale + c0 + k);
+      if (shift != nullptr) f += __ldg(shift + c0 + k);
+      if (residual != nullptr) f += to_f32(re[k]);
+      if (relu) f = fmaxf(f, 0.f);
+      e[k] = from_f32<T>(f);
+    }
+    reinterpret_cast<V *>(x)[i] = v;
+  }
+}
+
+template <typename T>
+mn_status run_epilogue(void *x, int64_t rows, int64_t c, const float *scale, const float *shift,
+                       const void *residual, int relu, cudaStream_t st) {
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const bool vec_ok = c % kVec == 0 &&
+                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual)) & 15) == 0;
+  const int64_t n = rows * c;
+  if (vec_ok) {
+    const int64_t n_vec = n / kVec;
+    const int blocks = (int)std::min<int64_t>(kNumSMs * 16, div_up(n_vec, 256));
+    MN_LAUNCH("epilogue_kernel", st,
+              epilogue_kernel<T, kVec><<<blocks, 256, 0, st>>>(
+                  static_cast<T *>(x), n_vec, (int)(c / kVec), scale, shift,
+                  static_cast<const T *>(residual), relu));
+  } else {
+    const int blocks = (int)std::min<int64_t>(kNumSMs * 16, div_up(n, 256));
+    MN_LAUNCH("epilogue_kernel", st,
+              epilogue_kernel<T, 1><<<blocks, 256, 0, st>>>(static_cast<T *>(x), n, (int)c, scale,
+                                                            shift, static_cast<const T *>(residual),
+                                                            relu));
+  }
+  return MN_OK;
+}
+
+}  // namespace
+}  // namespace mn
+
+extern "C" mn_status mn_apply_epilogue(void *features, int64_t rows, int64_t channels,
+                                       mn_dtype dtype, const float *scale, const float *shift,
+                                       const void *residual, int relu, void *stream) {
+  MN_CHECK_ARG(rows >= 0 && channels >= 1, "apply_epilogue: bad shape");
+  if (rows == 0) return MN_OK;
+  MN_CHECK_ARG(features != nullptr, "apply_epilogue: null features");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MN_F32: return run_epilogue<float>(features, rows, channels, scale, shift, residual, relu, st);
+    case MN_F16: return run_epilogue<__half>(features, rows, channels, scale, shift, residual, relu, st);
+    case MN_BF16:
+      return run_epilogue<__nv_bfloat16>(features, rows, channels, scale, shift, residual, relu, st);
+  }
+  set_error("apply_epilogue: unknown dtype %d", (int)dtype);
+  return MN_ERR_BAD_ARG;
+}
+
 extern "C" mn_status mn_plan_buckets(const int32_t *sizes, int64_t O, int has_threshold,
                                      double threshold, int64_t *buckets_out, int64_t *cumsum_out,
                                      int64_t *num_buckets_out) {

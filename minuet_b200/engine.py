@@ -178,3 +178,38 @@ def host_copy(t: torch.Tensor, dtype=np.int32) -> np.ndarray:
         values = hit[1].get() if isinstance(hit[1], PendingHostCopy) else hit[1]
         return np.ascontiguousarray(values.astype(dtype, copy=False))
     return np.ascontiguousarray(t.detach().cpu().numpy().astype(dtype, copy=False))
+
+
+# ---------------------------------------------------------------------------
+# neighbour tables of kernel maps (fused forward), keyed by the mask tensors
+# ---------------------------------------------------------------------------
+_neighbor_tables = {}
+
+
+def neighbor_table(source_masks: torch.Tensor, target_masks: torch.Tensor,
+                   sizes_host: np.ndarray):
+    """``(nbr [O, T] int32, tile_bits [ceil(T/128)] int32)`` of the kernel map that
+    the two mask tensors describe; built on first use and kept for as long as the
+    masks live (a transposed convolution passes the same masks swapped and gets
+    its own table)."""
+    key = (id(source_masks), id(target_masks))
+    hit = _neighbor_tables.get(key)
+    if hit is not None and hit[0]() is source_masks and hit[1]() is target_masks:
+        return hit[2], hit[3]
+    O, S = source_masks.shape
+    T = target_masks.shape[1]
+    device = source_masks.device
+    nbr = torch.empty((O, T), dtype=torch.int32, device=device)
+    tile_bits = torch.empty((T + 127) // 128, dtype=torch.int32, device=device)
+    ws = workspace(lib().mn_neighbor_table_workspace_bytes(np_ptr(sizes_host), O), device)
+    _lib.check(lib().mn_build_neighbor_table(ptr(source_masks), ptr(target_masks),
+                                             np_ptr(sizes_host), O, S, T, ptr(nbr), ptr(tile_bits),
+                                             ptr(ws), ws.numel(), stream_ptr(device)),
+               "build_neighbor_table")
+
+    def drop(_ref, k=key):
+        _neighbor_tables.pop(k, None)
+
+    _neighbor_tables[key] = (weakref.ref(source_masks, drop), weakref.ref(target_masks, drop),
+                             nbr, tile_bits)
+    return nbr, tile_bits

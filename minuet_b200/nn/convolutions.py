@@ -1,6 +1,6 @@
 """``KernelMapCache`` and ``SparseConv`` / ``SparseConv3d``
 (API of minuet/nn/convolutions.py)."""
-__all__ = ['SparseConv', 'SparseConv3d', 'KernelMapCache']
+__all__ = ['SparseConv', 'SparseConv3d', 'KernelMapCache', 'fold_batchnorm']
 
 import contextlib
 import ctypes
@@ -361,27 +361,31 @@ class SparseConv(Module):
             self._tuning_data = None
 
     # -- forward ------------------------------------------------------------------
+    def _lookup(self, inputs: SparseTensor):
+        """Output coordinates and the kernel map of this layer for ``inputs``."""
+        cache = self._kernel_map_cache
+        if cache is None:
+            raise ValueError("Kernel map cache must be specified")
+        coordinates, stride, batch_dims = cache.get_target_coordinates(
+            source_coordinates=inputs.C, source_batch_dims=inputs.batch_dims,
+            source_stride=inputs.stride, kernel_stride=self.stride, transposed=self.transposed)
+        source_masks, target_masks, order, sizes = cache.get_kernel_map(
+            source_coordinates=inputs.C, source_stride=inputs.stride,
+            source_batch_dims=inputs.batch_dims, target_coordinates=coordinates,
+            target_stride=stride, target_batch_dims=batch_dims, kernel_size=self.kernel_size,
+            kernel_dilation=self.dilation, transposed=self.transposed)
+        if self._tuning_data is not None:
+            self._tuning_data.append((source_masks, target_masks, sizes))
+        return coordinates, stride, batch_dims, source_masks, target_masks, order, sizes
+
     def forward(self, inputs: SparseTensor) -> SparseTensor:
         features = inputs.F
         if self.is_trivial:
             out = torch.mm(features, self.kernel.view(self.in_channels, self.out_channels))
             coordinates, stride, batch_dims = inputs.C, inputs.stride, inputs.batch_dims
         else:
-            cache = self._kernel_map_cache
-            if cache is None:
-                raise ValueError("Kernel map cache must be specified")
-            coordinates, stride, batch_dims = cache.get_target_coordinates(
-                source_coordinates=inputs.C, source_batch_dims=inputs.batch_dims,
-                source_stride=inputs.stride, kernel_stride=self.stride,
-                transposed=self.transposed)
-            source_masks, target_masks, order, sizes = cache.get_kernel_map(
-                source_coordinates=inputs.C, source_stride=inputs.stride,
-                source_batch_dims=inputs.batch_dims, target_coordinates=coordinates,
-                target_stride=stride, target_batch_dims=batch_dims,
-                kernel_size=self.kernel_size, kernel_dilation=self.dilation,
-                transposed=self.transposed)
-            if self._tuning_data is not None:
-                self._tuning_data.append((source_masks, target_masks, sizes))
+            coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
+                self._lookup(inputs)
             out = F.sparse_convolution_forward(
                 sources=features, weights=self.kernel, source_masks=source_masks,
                 target_masks=target_masks, kernel_map_order=order, kernel_map_sizes=sizes,
@@ -392,6 +396,46 @@ class SparseConv(Module):
         if self.bias is not None:
             out += self.bias
         return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
+
+    def forward_fused(self, inputs: SparseTensor, scale: Optional[torch.Tensor] = None,
+                      shift: Optional[torch.Tensor] = None,
+                      residual: Optional[torch.Tensor] = None, relu: bool = False) -> SparseTensor:
+        """``relu?((conv(inputs) + bias) * scale + shift + residual)`` with the
+        epilogue applied inside the convolution (or in one in-place pass after it).
+        Inference only; ``scale`` / ``shift`` are ``[out_channels]`` vectors, e.g.
+        an eval-mode BatchNorm folded by :func:`fold_batchnorm`."""
+        if self.bias is not None:
+            bias = self.bias.detach().float()
+            shift = bias * (1.0 if scale is None else scale.float()) + \
+                (0.0 if shift is None else shift.float())
+        features = inputs.F
+        if self.is_trivial:
+            out = torch.mm(features, self.kernel.view(self.in_channels, self.out_channels))
+            if scale is not None or shift is not None or residual is not None or relu:
+                F.apply_epilogue(out, scale, shift, residual, relu)
+            return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
+        coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
+            self._lookup(inputs)
+        out = F.sparse_convolution_forward_fused(
+            sources=features, weights=self.kernel, source_masks=source_masks,
+            target_masks=target_masks, kernel_map_order=order, kernel_map_sizes=sizes,
+            gather_tile_size=self._tunable_config["gather_tile_size"],
+            scatter_tile_size=self._tunable_config["scatter_tile_size"],
+            allow_shortcut_matmul=self._allow_shortcut_matmul,
+            threshold=self._tunable_config["threshold"], scale=scale, shift=shift,
+            residual=residual, relu=relu)
+        return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
+
+
+def fold_batchnorm(bn: torch.nn.modules.batchnorm._BatchNorm):
+    """``(scale, shift)`` fp32 vectors equivalent to an eval-mode BatchNorm:
+    ``bn(x) == x * scale + shift``."""
+    var = bn.running_var.detach().float()
+    mean = bn.running_mean.detach().float()
+    weight = torch.ones_like(var) if bn.weight is None else bn.weight.detach().float()
+    bias = torch.zeros_like(var) if bn.bias is None else bn.bias.detach().float()
+    scale = weight / torch.sqrt(var + bn.eps)
+    return scale.contiguous(), (bias - mean * scale).contiguous()
 
 
 class SparseConv3d(SparseConv):

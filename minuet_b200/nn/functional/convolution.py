@@ -1,8 +1,10 @@
 """Gather - grouped GEMM - Scatter forward pass and its stage timers
 (mirror of minuet/nn/functional/convolution.py)."""
 __all__ = ['cuda_time_gather', 'cuda_time_scatter', 'sparse_convolution_forward',
-           'cuda_time_gemm', 'set_gemm_parallel_level']
+           'sparse_convolution_forward_fused', 'apply_epilogue', 'cuda_time_gemm',
+           'set_gemm_parallel_level']
 
+import math
 from typing import Optional
 
 import numpy as np
@@ -11,6 +13,11 @@ import torch
 from minuet_b200 import _lib, engine
 
 GEMM_PARALLEL_LEVEL = 4
+# Which forward algorithm fp16/bf16 layers use: "explicit" = gather - grouped GEMM -
+# scatter, "implicit" = the fused output-stationary kernel, "auto" = time both the
+# first time a layer shape / map density is seen and keep the faster one
+ALGORITHM = "auto"
+_algorithm_choice = {}
 
 
 def set_gemm_parallel_level(level: int):
@@ -75,6 +82,8 @@ def sparse_convolution_forward(sources: torch.Tensor,
     accepted and do not change the result: the grouped GEMM needs neither side
     streams nor equal-size buckets.  ``*_tile_size`` is the number of channels
     one thread moves per row; 1 (the untuned default) picks 16-byte accesses.
+    fp16/bf16 layers run either gather - grouped GEMM - scatter or the fused
+    implicit-GEMM kernel, whichever ``ALGORITHM`` selects.
     """
     del parallel
     engine.require_cuda(sources)
@@ -84,9 +93,72 @@ def sparse_convolution_forward(sources: torch.Tensor,
     S, T, O, c_in, c_out, sizes_host = _prepare(weights, sm, tm, kernel_map_sizes, sources)
     if sources.shape[0] != S:
         raise RuntimeError(f"sources has {sources.shape[0]} rows but the masks describe {S}")
+    return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
+                    scatter_tile_size, allow_shortcut_matmul, threshold)
+
+
+def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tensor,
+                                     source_masks: torch.Tensor, target_masks: torch.Tensor,
+                                     kernel_map_order: Optional[torch.Tensor],
+                                     kernel_map_sizes: torch.Tensor,
+                                     gather_tile_size: int = 1,
+                                     scatter_tile_size: int = 1,
+                                     allow_shortcut_matmul: bool = False,
+                                     threshold: Optional[float] = 0,
+                                     scale: Optional[torch.Tensor] = None,
+                                     shift: Optional[torch.Tensor] = None,
+                                     residual: Optional[torch.Tensor] = None,
+                                     relu: bool = False) -> torch.Tensor:
+    """Sparse convolution with a fused epilogue (no counterpart in the reference,
+    whose models apply BatchNorm, the residual add and ReLU as separate passes
+    over the feature matrix):
+
+        out = relu?( conv(sources) * scale[c] + shift[c] + residual )
+
+    ``scale`` / ``shift`` are ``[C_out]`` (an eval-mode BatchNorm or a bias folded
+    into two vectors; applied in fp32), ``residual`` is ``[N_out, C_out]`` in the
+    feature dtype.  Layers that take the fused implicit-GEMM kernel apply the
+    epilogue inside it; the others run gather - GEMM - scatter and one in-place
+    pass over the output."""
+    engine.require_cuda(sources)
+    sources = sources.contiguous()
+    weights = weights.contiguous()
+    sm, tm, order = _i32(source_masks), _i32(target_masks), _i32(kernel_map_order)
+    S, T, O, c_in, c_out, sizes_host = _prepare(weights, sm, tm, kernel_map_sizes, sources)
+    if sources.shape[0] != S:
+        raise RuntimeError(f"sources has {sources.shape[0]} rows but the masks describe {S}")
+    res = None if residual is None else residual.contiguous()
+    if res is not None and (tuple(res.shape) != (T, c_out) or res.dtype != weights.dtype):
+        raise RuntimeError("residual must be [N_out, C_out] in the feature dtype")
+    return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
+                    scatter_tile_size, allow_shortcut_matmul, threshold, _f32(scale), _f32(shift),
+                    res, relu)
+
+
+def apply_epilogue(features: torch.Tensor, scale=None, shift=None, residual=None,
+                   relu: bool = False) -> torch.Tensor:
+    """In place ``features = relu?(features * scale[c] + shift[c] + residual)``."""
+    engine.require_cuda(features)
+    rows, channels = features.shape
+    _lib.check(engine.lib().mn_apply_epilogue(
+        engine.ptr(features), rows, channels, engine.dtype_code(features.dtype),
+        engine.ptr(_f32(scale)), engine.ptr(_f32(shift)),
+        engine.ptr(None if residual is None else residual.contiguous()), int(bool(relu)),
+        engine.stream_ptr(features.device)), "apply_epilogue")
+    return features
+
+
+def _f32(v):
+    return None if v is None else v.detach().to(torch.float32).contiguous()
+
+
+def _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_tile_size,
+                      scatter_tile_size, allow_shortcut_matmul, threshold):
+    O, S = sm.shape
+    T = tm.shape[1]
+    c_in, c_out = weights.shape[1], weights.shape[2]
     code = engine.dtype_code(weights.dtype)
     device = sources.device
-    out = torch.empty((T, c_out), dtype=weights.dtype, device=device)
     ws = _workspace(sizes_host, S, T, O, c_in, c_out, code, allow_shortcut_matmul, threshold, device)
     _lib.check(engine.lib().mn_sparse_convolution_forward(
         S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights), engine.ptr(sm),
@@ -96,6 +168,85 @@ def sparse_convolution_forward(sources: torch.Tensor,
         engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
         engine.stream_ptr(device)), "sparse_convolution_forward")
     return out
+
+
+def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes_host, out,
+                      scale=None, shift=None, residual=None, relu=False):
+    O, S = source_masks.shape
+    T = target_masks.shape[1]
+    c_in, c_out = weights.shape[1], weights.shape[2]
+    device = sources.device
+    nbr, tile_bits = engine.neighbor_table(source_masks, target_masks, sizes_host)
+    lib = engine.lib()
+    ws = engine.workspace(lib.mn_implicit_workspace_bytes(O, c_in, c_out), device)
+    _lib.check(lib.mn_sparse_convolution_forward_implicit(
+        S, T, O, c_in, c_out, engine.dtype_code(weights.dtype), engine.ptr(sources),
+        engine.ptr(weights), engine.ptr(nbr), engine.ptr(tile_bits), engine.ptr(order),
+        engine.ptr(scale), engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
+        engine.ptr(out), engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
+        engine.stream_ptr(device)), "sparse_convolution_forward_implicit")
+    return out
+
+
+def _time_ms(fn, reps=3):
+    best = float("inf")
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        best = min(best, a.elapsed_time(b))
+    return best
+
+
+def _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit) -> str:
+    """'explicit' or 'implicit' for this layer shape and map density; with
+    ``ALGORITHM == "auto"`` both are timed once per (offsets, channels, dtype,
+    ~log2 targets, ~log2 pairs per target) and the faster one is kept."""
+    O, T = tm.shape
+    c_in, c_out = weights.shape[1], weights.shape[2]
+    if ALGORITHM == "explicit" or T == 0 or not engine.lib().mn_implicit_supported(
+            O, c_in, c_out, engine.dtype_code(weights.dtype)):
+        return "explicit"
+    if ALGORITHM == "implicit":
+        return "implicit"
+    pairs = float(sizes_host.sum())
+    key = (O, c_in, c_out, weights.dtype, round(math.log2(T)),
+           round(2 * math.log2(max(pairs, 1.0) / T)))
+    choice = _algorithm_choice.get(key)
+    if choice is None:
+        run_explicit()
+        run_implicit()
+        choice = "implicit" if _time_ms(run_implicit) < _time_ms(run_explicit) else "explicit"
+        _algorithm_choice[key] = choice
+    return choice
+
+
+def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scatter_tile_size,
+             allow_shortcut_matmul, threshold, scale=None, shift=None, residual=None, relu=False):
+    T = tm.shape[1]
+    c_out = weights.shape[2]
+    out = torch.empty((T, c_out), dtype=weights.dtype, device=sources.device)
+    has_epilogue = scale is not None or shift is not None or residual is not None or relu
+
+    def run_explicit():
+        _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_tile_size,
+                          scatter_tile_size, allow_shortcut_matmul, threshold)
+        if has_epilogue:
+            _lib.check(engine.lib().mn_apply_epilogue(
+                engine.ptr(out), T, c_out, engine.dtype_code(weights.dtype), engine.ptr(scale),
+                engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
+                engine.stream_ptr(out.device)), "apply_epilogue")
+        return out
+
+    def run_implicit():
+        return _implicit_forward(sources, weights, sm, tm, order, sizes_host, out, scale, shift,
+                                 residual, relu)
+
+    if _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit) == "implicit":
+        return run_implicit()
+    return run_explicit()
 
 
 def _time_stage(stage, weights, source_masks, target_masks, kernel_map_sizes, tile_size,

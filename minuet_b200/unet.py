@@ -13,12 +13,16 @@ from typing import Sequence
 import torch
 from torch import nn
 
-from minuet_b200.nn import BatchNorm, ReLU, SparseConv, SparseConv3d
+from minuet_b200.nn import BatchNorm, ReLU, SparseConv, SparseConv3d, fold_batchnorm
 from minuet_b200.nn import functional as F
 from minuet_b200.tensors import SparseTensor
 
 
 class ConvBlock(nn.Sequential):
+    """conv - BatchNorm - ReLU.  After :meth:`SparseUNet.fuse` (eval mode only) the
+    BatchNorm and ReLU run as the convolution's epilogue instead of as separate
+    passes over the feature matrix."""
+
     def __init__(self, c_in: int, c_out: int, kernel_size: int, stride: int = 1,
                  transposed: bool = False):
         if transposed:
@@ -26,6 +30,13 @@ class ConvBlock(nn.Sequential):
         else:
             conv = SparseConv3d(c_in, c_out, kernel_size, stride=stride)
         super().__init__(conv, BatchNorm(c_out), ReLU(inplace=True))
+        self.folded = None
+
+    def forward(self, x: SparseTensor) -> SparseTensor:
+        if self.folded is None or self.training:
+            return super().forward(x)
+        scale, shift = self.folded
+        return self[0].forward_fused(x, scale=scale, shift=shift, relu=True)
 
 
 class ResidualBlock(nn.Module):
@@ -40,8 +51,17 @@ class ResidualBlock(nn.Module):
         if c_in != c_out:
             self.project = nn.Sequential(SparseConv3d(c_in, c_out, 1), BatchNorm(c_out))
         self.relu = ReLU(inplace=True)
+        self.folded = None
 
     def forward(self, x: SparseTensor) -> SparseTensor:
+        if self.folded is not None and not self.training:
+            (s1, b1), (s2, b2), proj = self.folded
+            y = self.body[0].forward_fused(x, scale=s1, shift=b1, relu=True)
+            if self.project is None:
+                skip = x.F
+            else:
+                skip = self.project[0].forward_fused(x, scale=proj[0], shift=proj[1]).F
+            return self.body[3].forward_fused(y, scale=s2, shift=b2, residual=skip, relu=True)
         y = self.body(x)
         skip = x if self.project is None else self.project(x)
         out = SparseTensor(y.F + skip.F, y.C, stride=y.stride, batch_dims=y.batch_dims)
@@ -69,6 +89,19 @@ class SparseUNet(nn.Module):
                                           ResidualBlock(skip_c, skip_c)))
             prev = skip_c
         self.head = SparseConv3d(prev, num_classes, 1)
+
+    def fuse(self):
+        """Fold every eval-mode BatchNorm into a per-channel scale/shift and run it,
+        the residual add and the ReLU as convolution epilogues.  Call after
+        ``eval()`` and after the final dtype/device of the model is set; ``train()``
+        switches back to the unfused modules."""
+        for m in self.modules():
+            if isinstance(m, ConvBlock):
+                m.folded = fold_batchnorm(m[1])
+            elif isinstance(m, ResidualBlock):
+                proj = None if m.project is None else fold_batchnorm(m.project[1])
+                m.folded = (fold_batchnorm(m.body[1]), fold_batchnorm(m.body[4]), proj)
+        return self
 
     def forward(self, x: SparseTensor) -> SparseTensor:
         x = self.stem(x)

@@ -128,8 +128,50 @@ def test_small_unet_matches_oracle(oracle_lib, dtype, tol):
     got = out.F.float().cpu().numpy()
     scale = np.abs(want).max()
     assert np.abs(got - want).max() <= tol * scale, np.abs(got - want).max() / scale
-    # second pass on a reset cache gives identical bits (deterministic scatter order)
+    # second pass on a reset cache gives identical bits (deterministic summation order)
     cache.reset()
     with torch.no_grad():
         again = net(x)
     assert torch.equal(again.F, out.F)
+    # BatchNorm / ReLU / residual folded into the convolution epilogues: same function
+    net.fuse()
+    cache.reset()
+    with torch.no_grad():
+        fused = net(x)
+    got = fused.F.float().cpu().numpy()
+    assert np.abs(got - want).max() <= tol * scale, np.abs(got - want).max() / scale
+
+
+@pytest.mark.parametrize("algorithm", ["explicit", "implicit"])
+def test_fused_epilogue_both_algorithms(oracle_lib, algorithm):
+    from minuet_b200.nn import functional as F
+    from minuet_b200.nn.functional import convolution as conv_mod
+    rng = np.random.default_rng(3)
+    coords, bd = synth.random_small_batch(rng, 2, 4000, 22)
+    c_in, c_out = 32, 48
+    x = rng.standard_normal((len(coords), c_in)).astype(np.float32)
+    res = rng.standard_normal((len(coords), c_out)).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, c_out).astype(np.float32)
+    shift = rng.uniform(-0.3, 0.3, c_out).astype(np.float32)
+    conv = minuet.nn.SparseConv3d(c_in, c_out, 3, bias=True, dtype=torch.float16, device=DEV)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    minuet.set_kernel_map_cache(conv, cache)
+    xt = torch.as_tensor(x, device=DEV).half()
+    rt = torch.as_tensor(res, device=DEV).half()
+    inp = minuet.SparseTensor(xt, torch.as_tensor(coords, device=DEV),
+                              batch_dims=torch.as_tensor(bd, device=DEV))
+    old = conv_mod.ALGORITHM
+    conv_mod.ALGORITHM = algorithm
+    try:
+        out = conv.forward_fused(inp, scale=torch.as_tensor(scale, device=DEV),
+                                 shift=torch.as_tensor(shift, device=DEV), residual=rt, relu=True)
+    finally:
+        conv_mod.ALGORITHM = old
+    off = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    m = oracle_lib.build_kernel_map(coords, coords, off, bd, bd)
+    ref = oracle_lib.conv_forward(xt.float().cpu().numpy(), conv.kernel.detach().float().cpu().numpy(),
+                                  m["source_masks"], m["target_masks"], m["order"], acc64=True)
+    ref = (ref + conv.bias.detach().float().cpu().numpy()) * scale + shift + rt.float().cpu().numpy()
+    ref = np.maximum(ref, 0)
+    got = out.F.float().cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-3 * np.abs(ref).max() + 1e-3)
