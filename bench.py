@@ -435,7 +435,8 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     from minuet_b200 import sharding
     from minuet_b200.unet import SparseUNet
 
-    shards = sharding.assign_clouds([VOXELS_PER_CLOUD] * UNET_CLOUDS, world)
+    n_clouds = args.unet_clouds
+    shards = sharding.assign_clouds([VOXELS_PER_CLOUD] * n_clouds, world)
     mine = shards[rank]
     with concurrent.futures.ProcessPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
         clouds = list(pool.map(_make_cloud, [UNET_SEED0 + i for i in mine]))
@@ -521,18 +522,18 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     if rank != 0:
         return None
     return {
-        "metric": "sparse-UNet fp16 clouds/sec", "value": round(UNET_CLOUDS * steps / (ms * 1e-3), 2),
+        "metric": "sparse-UNet fp16 clouds/sec", "value": round(n_clouds * steps / (ms * 1e-3), 2),
         "unit": "clouds/s", "scaling": "strong", "ms_per_step": round(ms / steps, 3),
         "steps": steps, "warmup": warm,
         "config": {"workload": "C4: UNet (stem 32, encoder 32/64/128/256, decoder mirror, 20 "
                                "classes) on 64 outdoor clouds x 120k voxels, 4-channel fp16 "
                                "features, clouds sharded over the GPUs, NCCL gather of the logits",
-                   "clouds_total": UNET_CLOUDS, "clouds_on_rank0": len(mine),
+                   "clouds_total": n_clouds, "clouds_on_rank0": len(mine),
                    "voxels_on_rank0": int(len(coords))},
-        "e2e": {"value": round(UNET_CLOUDS * steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
+        "e2e": {"value": round(n_clouds * steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "ms_per_step": round(ms_e2e / steps, 3),
                 "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_bd.numel() * 8 + h_feats.numel() * 2),
-                "d2h_bytes_per_step": int(UNET_CLOUDS * VOXELS_PER_CLOUD)},
+                "d2h_bytes_per_step": int(n_clouds * VOXELS_PER_CLOUD)},
         "gpu_launches": int(launches),
         "library_kernel_ms_rank0_one_step": kernels,
     }
@@ -548,6 +549,8 @@ def main():
     ap.add_argument("--no-unet", action="store_true",
                     help="skip the secondary end-to-end UNet measurement")
     ap.add_argument("--unet-steps", type=int, default=5)
+    ap.add_argument("--unet-clouds", type=int, default=UNET_CLOUDS,
+                    help="clouds in the UNet job (64 = the benchmark configuration)")
     ap.add_argument("--gms-channels", default="16,32,64,128,256")
     ap.add_argument("--gms-sweep", action="store_true",
                     help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
