@@ -109,20 +109,23 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
     for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
       const int64_t t = (int64_t)tile * kBM + r;
       const bool row_live = t < args.T;
-      const uint32_t bits = __ldg(args.tile_bits + tile);
-      // this row's source under every active offset: all loads issued together, so
-      // the tile pays one memory latency instead of one per offset
-      int nb[32];
-#pragma unroll
-      for (int p = 0; p < 32; p++)
-        nb[p] = (row_live && ((bits >> p) & 1u)) ? __ldg(args.nbr + (int64_t)p * args.T + t) : -1;
-#pragma unroll
-      for (int p = 0; p < 32; p++) {
-        if (!alive || !((bits >> p) & 1u)) continue;
-        const int src = nb[p];
+      uint32_t rest = __ldg(args.tile_bits + tile);
+      // software pipeline over the active offsets: the next offset's source row is
+      // requested before the current one is copied
+      int p = rest != 0u ? __ffs(rest) - 1 : -1;
+      int src = (p >= 0 && row_live) ? __ldg(args.nbr + (int64_t)p * args.T + t) : -1;
+      while (alive && p >= 0) {
+        rest &= rest - 1u;
+        const int p_next = rest != 0u ? __ffs(rest) - 1 : -1;
+        const int src_next =
+            (p_next >= 0 && row_live) ? __ldg(args.nbr + (int64_t)p_next * args.T + t) : -1;
         const uint8_t *src_row = args.in + (int64_t)(src < 0 ? 0 : src) * args.K * 2;
         for (int kb = 0; kb < args.k_blocks; kb++) {
-          if (!mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag, args.status)) { alive = false; break; }
+          // one lane per warp polls the barrier; the others wait at the warp barrier
+          int ok = 1;
+          if (lane == 0) ok = mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag, args.status) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { alive = false; break; }
           uint8_t *sa = stage_base + (size_t)stage * args.stage_bytes;
           if (r == 0) {
             const int widx = args.order != nullptr ? __ldg(args.order + p) : p;
@@ -143,6 +146,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
                        : "memory");
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
+        p = p_next;
+        src = src_next;
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this thread is in flight at exit
@@ -189,7 +194,10 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
     uint32_t acc_phase = 0;
     const int n = args.N;
     for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
-      if (!mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status)) break;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool empty_tile = __ldg(args.tile_bits + tile) == 0u;   // no pair: the rows are zero
       const int out_row = tile * kBM + quarter * 32;

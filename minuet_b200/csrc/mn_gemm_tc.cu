@@ -175,7 +175,10 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
     for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
       const TilePos pos = locate_tile(tab, tile);
       const int p = pos.problem;
-      if (!mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status)) break;
+      int ok = 1;   // one lane polls the barrier, the warp follows
+      if (lane == 0) ok = mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool direct = tab.direct[p] != 0;
       const int out_row = (direct ? 0 : (int)tab.a_row[p]) + pos.m0 + quarter * 32;
