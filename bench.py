@@ -95,6 +95,84 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def reference_cuda_arm(args):
+    """Optional extra (not the contract's reference arm): the reference's OWN CUDA
+    kernels, recompiled for sm_100 into oracle/_ref/libminuet_ref.so, timed on the
+    same workload with CUDA events -- batched query + sizes + (stable order on the
+    host side of the shim) + masks per map, plus arg-sort + unique for the strided
+    target coordinates.  Prints one JSON line with impl = "reference-cuda"."""
+    import torch
+    from minuet_b200 import synth
+    from minuet_b200.utils.helpers import generate_kernel_offsets
+    path = os.path.join(ROOT, "oracle", "_ref", "libminuet_ref.so")
+    if not os.path.exists(path) or not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref library or GPU missing"}))
+        return
+    lib = ctypes.CDLL(path)
+    lib.ref_last_error.restype = ctypes.c_char_p
+    I64 = ctypes.c_int64
+    dev = torch.device("cuda", 0)
+    coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000, n_voxels=VOXELS_PER_CLOUD)
+    S = len(coords)
+    d_src = torch.as_tensor(coords, device=dev)
+    d_sbd = torch.as_tensor(bd, device=dev, dtype=torch.int32)
+    offs = {k: torch.as_tensor(generate_kernel_offsets(3, k, 1, 1).astype(np.int32), device=dev)
+            for k in (2, 3)}
+
+    def p(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    def ok(rc):
+        if rc != 0:
+            raise RuntimeError(lib.ref_last_error().decode())
+
+    def step():
+        # strided targets as KernelMapCache.get_target_coordinates does it
+        floored = (d_src // 2) * 2
+        index = torch.empty(S, dtype=torch.int32, device=dev)
+        ok(lib.ref_multi_arg_sort(I64(S), I64(CLOUDS_PER_GPU), p(floored), p(d_sbd), p(index), 1, None))
+        sorted_c = floored[index.long()].contiguous()
+        uidx = torch.empty(S + 1, dtype=torch.int32, device=dev)
+        uout = torch.empty((S, 3), dtype=torch.int32, device=dev)
+        count = I64(0)
+        ok(lib.ref_multi_unique(I64(S), I64(CLOUDS_PER_GPU + 1), p(sorted_c), p(d_sbd), p(uidx),
+                                p(uout), ctypes.byref(count), None))
+        tgt2 = uout[:count.value].contiguous()
+        tbd2 = uidx[d_sbd.long()].contiguous()
+        for kernel, stride in MAPS:
+            tgt, tbd = (d_src, d_sbd) if stride == 1 else (tgt2, tbd2)
+            O, T = kernel ** 3, tgt.shape[0]
+            km = torch.empty((O, T), dtype=torch.int32, device=dev)
+            ok(lib.ref_multi_query(I64(CLOUDS_PER_GPU), I64(O), p(d_sbd), p(tbd), p(d_src), p(tgt),
+                                   p(offs[kernel]), p(km), None))
+            sizes = torch.empty(O, dtype=torch.int32, device=dev)
+            ok(lib.ref_sizes(I64(O), I64(T), p(km), p(sizes), None))
+            sizes, order = torch.sort(sizes)
+            km = km[order].contiguous()
+            sm = torch.empty((O, S), dtype=torch.int32, device=dev)
+            tm = torch.empty((O, T), dtype=torch.int32, device=dev)
+            ok(lib.ref_masks(I64(O), I64(S), I64(T), p(km), p(sizes.int().contiguous()), p(sm), p(tm), None))
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(args.steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        b.synchronize()
+        total += a.elapsed_time(b)
+    value = len(MAPS) * S * args.steps / (total * 1e-3) / 1e6
+    print(json.dumps({"impl": "reference-cuda", "metric": METRIC, "value": round(value, 2),
+                      "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "ms_per_step": round(total / args.steps, 4),
+                      "note": "reference's own CUDA kernels (CUB/cuBLAS based, no sm_100-specific "
+                              "code) recompiled for sm_100a; same inputs, device-resident",
+                      "config": workload_config(S)}), flush=True)
+
+
 def workload_config(n_voxels_per_gpu):
     return {"workload": "C1 kernel-map build: 4 outdoor clouds x ~120k voxels per GPU, maps "
                         "(3^3,s1) (2^3,s1) (3^3,s2) (2^3,s2), cold cache, int32 coords",
@@ -544,7 +622,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unet", action="store_true",
                     help="skip the secondary end-to-end UNet measurement")
@@ -555,7 +633,9 @@ def main():
     ap.add_argument("--gms-sweep", action="store_true",
                     help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.impl == "reference-cuda":
+        reference_cuda_arm(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)

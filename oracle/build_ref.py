@@ -26,7 +26,10 @@ REF_SOURCES = [
 ]
 
 
-def build(reference_root="/root/reference", force=False):
+DEFAULT_REFERENCE = os.environ.get("MINUET_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+
+
+def build(reference_root=DEFAULT_REFERENCE, force=False):
     csrc = os.path.join(reference_root, "csrc")
     if not os.path.isdir(csrc):
         print(f"reference checkout not found at {reference_root}; keeping any prebuilt {OUT}")
@@ -64,5 +67,5 @@ def build(reference_root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else DEFAULT_REFERENCE
     print(build(root, force="--force" in sys.argv))

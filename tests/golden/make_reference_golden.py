@@ -2,7 +2,7 @@
 (oracle/_ref/libminuet_ref.so, built from the reference checkout by
 oracle/build_ref.py) on small seeded inputs.  Needs a GPU:
 
-    python tests/golden/make_reference_golden.py gpurun_out/reference_golden.npz
+    python tests/golden/make_reference_golden.py reference_golden.npz
 
 The committed copy lives beside this script; tests/test_golden.py checks the CPU
 oracle against it without a GPU.  Inputs are regenerated from the seeds below,

@@ -182,3 +182,54 @@ def test_stage_timers_and_autotune(oracle_lib):
     assert 16 % cfg["gather_tile_size"] == 0 and 16 % cfg["scatter_tile_size"] == 0
     cache.reset()
     assert_close(conv(inp).F, want, torch.float16)
+
+
+def test_neighbor_table_matches_kernel_map(oracle_lib):
+    """mn_build_neighbor_table turns masks back into the (mask-row ordered) kernel
+    map and marks, per 128-target tile, the offsets that have any pair."""
+    from minuet_b200 import engine
+    rng = np.random.default_rng(12)
+    src, sbd = synth.random_small_batch(rng, 2, 3000, 20)
+    tgt, tbd = oracle_lib.downsample(src, 2, sbd)
+    for kernel, s_, t_, sb, tb in ((3, src, src, sbd, sbd), (2, src, tgt, sbd, tbd)):
+        off = generate_kernel_offsets(3, kernel, 1, 1).astype(np.int32)
+        m = oracle_lib.build_kernel_map(s_, t_, off, sb, tb)
+        sm, tm = dev(m["source_masks"]), dev(m["target_masks"])
+        nbr, bits = engine.neighbor_table(sm, tm, m["sorted_sizes"])
+        want = m["kernel_map"][m["order"]]
+        assert np.array_equal(nbr.cpu().numpy(), want)
+        T = len(t_)
+        got_bits = bits.cpu().numpy().astype(np.uint32)
+        for tile in range((T + 127) // 128):
+            rows = want[:, tile * 128:(tile + 1) * 128]
+            expect = sum(1 << p for p in range(len(off)) if (rows[p] >= 0).any())
+            assert int(got_bits[tile]) == expect
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_apply_epilogue(dtype):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((1000, 24)).astype(np.float32)
+    res = rng.standard_normal((1000, 24)).astype(np.float32)
+    scale = rng.uniform(0.5, 2, 24).astype(np.float32)
+    shift = rng.uniform(-1, 1, 24).astype(np.float32)
+    xt, rt = dev(x).to(dtype), dev(res).to(dtype)
+    want = np.maximum(xt.float().cpu().numpy() * scale + shift + rt.float().cpu().numpy(), 0)
+    F.apply_epilogue(xt, dev(scale), dev(shift), rt, relu=True)
+    tol = 1e-6 if dtype == torch.float32 else (1e-2 if dtype == torch.float16 else 4e-2)
+    np.testing.assert_allclose(xt.float().cpu().numpy(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("algorithm", ["explicit", "implicit"])
+@pytest.mark.parametrize("kernel,stride,c_in,c_out", [(3, 1, 64, 64), (2, 2, 32, 64), (3, 2, 16, 8),
+                                                      (3, 1, 8, 256), (3, 1, 136, 24)])
+def test_both_algorithms(oracle_lib, algorithm, kernel, stride, c_in, c_out):
+    from minuet_b200.nn.functional import convolution as conv_mod
+    rng = np.random.default_rng(5)
+    src, sbd = synth.random_small_batch(rng, 2, 3500, 18)
+    old = conv_mod.ALGORITHM
+    conv_mod.ALGORITHM = algorithm
+    try:
+        run_layer(oracle_lib, src, sbd, c_in, c_out, kernel, stride, torch.float16)
+    finally:
+        conv_mod.ALGORITHM = old
