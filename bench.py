@@ -396,6 +396,16 @@ def gpu_arm(args):
     stage_bytes = sum(12 * (S + T_by_stride[s]) + 4 * k ** 3 * (S + T_by_stride[s]) for k, s in MAPS)
     stage_bytes_with_map = stage_bytes + sum(4 * k ** 3 * T_by_stride[s] for k, s in MAPS)
     gpu_ms = sum(v["ms_per_step"] for v in kernels.values())
+    # the kernel that moves most of the step's bytes (the mask emission) next to the
+    # kernel that takes most of its time (the search, which is instruction bound)
+    byte_dominant = None
+    if "emit_masks_kernel" in kernels:
+        eb = kernel_bytes("emit_masks_kernel", S, T_by_stride, CLOUDS_PER_GPU)
+        ems = kernels["emit_masks_kernel"]["ms_per_step"]
+        byte_dominant = {"kernel": "emit_masks_kernel", "algorithmic_bytes_per_step": eb,
+                         "kernel_ms_per_step": round(ems, 4),
+                         "achieved": round(eb / (ems * 1e-3) / 1e9, 1), "unit": "GB/s",
+                         "frac": round(eb / (ems * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
     roofline = {
         "bound": "hbm", "kernel": top,
         "achieved": None if achieved is None else round(achieved, 1),
@@ -414,6 +424,7 @@ def gpu_arm(args):
             "gbs_over_gpu_busy_time": round(stage_bytes / (gpu_ms * 1e-3) / 1e9, 1),
             "gbs_over_step_time": round(stage_bytes / (ms_total / args.steps * 1e-3) / 1e9, 1),
         },
+        "byte_dominant_kernel": byte_dominant,
         "kernels": {k: {"ms_per_step": round(v["ms_per_step"], 4),
                         "launches_per_step": v["launches_per_step"]}
                     for k, v in sorted(kernels.items(), key=lambda kv: -kv[1]["ms_per_step"])},

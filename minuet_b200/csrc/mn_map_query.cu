@@ -129,8 +129,41 @@ __device__ __forceinline__ void emit(const SearchArgs &a, int o, int64_t row, bo
   }
 }
 
-__device__ __forceinline__ uint32_t hash_slot(uint32_t k) {
-  return (k * 0x9E3779B1u) >> 21;  // top 11 bits: kQHash = 2048 slots
+// The hash set is kQHash / 2 buckets of two {cell, mask} slots (16 bytes).  Inserts
+// fill slot 0 of a bucket first, then slot 1, then move on to the next bucket, so a
+// bucket whose slot 1 is empty never overflowed.
+constexpr int kQBuckets = kQHash / 2;
+
+__device__ __forceinline__ uint32_t hash_bucket(uint32_t k) {
+  return (k * 0x9E3779B1u) >> 22;  // top 10 bits: 1024 buckets
+}
+
+// Occupancy mask of cell c (0 when the cell is absent) and the slot that holds it.
+// The home bucket and its successor are read up front with two 16-byte loads; only
+// a cell pushed further than that (rare at these load factors) takes the loop, so
+// the lanes of a warp stay converged.
+__device__ __forceinline__ uint32_t find_cell(const uint2 *slots, uint32_t c, uint32_t *slot) {
+  const uint4 *buckets = reinterpret_cast<const uint4 *>(slots);
+  uint32_t b = hash_bucket(c);
+  const uint4 a0 = buckets[b];
+  const uint32_t b1 = (b + 1) & (kQBuckets - 1);
+  const uint4 a1 = buckets[b1];
+  if (a0.x == c) { *slot = 2 * b; return a0.y; }
+  if (a0.z == c) { *slot = 2 * b + 1; return a0.w; }
+  if (a0.z == kHashEmpty) { *slot = 0; return 0u; }
+  if (a1.x == c) { *slot = 2 * b1; return a1.y; }
+  if (a1.z == c) { *slot = 2 * b1 + 1; return a1.w; }
+  if (a1.z == kHashEmpty) { *slot = 0; return 0u; }
+  b = b1;
+  for (int probe = 2; probe < kQBuckets; probe++) {
+    b = (b + 1) & (kQBuckets - 1);
+    const uint4 v = buckets[b];
+    if (v.x == c) { *slot = 2 * b; return v.y; }
+    if (v.z == c) { *slot = 2 * b + 1; return v.w; }
+    if (v.z == kHashEmpty) break;
+  }
+  *slot = 0;
+  return 0u;
 }
 
 // A block owns 512 consecutive rows, a thread 4 consecutive rows.
@@ -226,11 +259,13 @@ search_kernel(const __grid_constant__ SearchPair sp) {
       const uint64_t tk = __ldg(a.table + ulo + w);
       const uint32_t k = (uint32_t)(tk - base) + kQPad;
       const uint32_t cell = k >> 5;
-      uint32_t h = hash_slot(cell);
-      for (int probe = 0; probe < kQHash; probe++) {
-        const uint32_t old = atomicCAS(&slots[h].x, kHashEmpty, cell);
-        if (old == kHashEmpty || old == cell) break;
-        h = (h + 1) & (kQHash - 1);
+      uint32_t b = hash_bucket(cell), h = 0;
+      for (int probe = 0; probe < kQBuckets; probe++) {
+        uint32_t old = atomicCAS(&slots[2 * b].x, kHashEmpty, cell);
+        if (old == kHashEmpty || old == cell) { h = 2 * b; break; }
+        old = atomicCAS(&slots[2 * b + 1].x, kHashEmpty, cell);
+        if (old == kHashEmpty || old == cell) { h = 2 * b + 1; break; }
+        b = (b + 1) & (kQBuckets - 1);
       }
       atomicOr(&slots[h].y, 1u << (k & 31));
       if (kMode == kMap) {
@@ -253,7 +288,6 @@ search_kernel(const __grid_constant__ SearchPair sp) {
       // Per row: the 64 consecutive last-dimension values starting at the cell of
       // the group's first query, as one 64-bit occupancy mask (low cell | high cell).
       uint32_t sh[kQRows], mlo[kQRows], mhi[kQRows], slo[kQRows], shi[kQRows];
-      uint2 v[kQRows];
       uint32_t c0[kQRows];
       bool ok[kQRows];
 #pragma unroll
@@ -263,29 +297,15 @@ search_kernel(const __grid_constant__ SearchPair sp) {
         const uint32_t q0 = (uint32_t)t + (uint32_t)e_first;
         c0[j] = q0 >> 5;
         sh[j] = q0 & 31;
-        slo[j] = hash_slot(c0[j]);
-        v[j] = slots[slo[j]];   // the four first probes are issued together
       }
 #pragma unroll
       for (int j = 0; j < kQRows; j++) {
-        for (int probe = 0; probe < kQHash && v[j].x != c0[j] && v[j].x != kHashEmpty; probe++) {
-          slo[j] = (slo[j] + 1) & (kQHash - 1);
-          v[j] = slots[slo[j]];
-        }
-        mlo[j] = (ok[j] && v[j].x == c0[j]) ? v[j].y : 0u;
+        const uint32_t m0 = find_cell(slots, c0[j], &slo[j]);
+        mlo[j] = ok[j] ? m0 : 0u;
         mhi[j] = 0u;
         shi[j] = 0u;
-        if (ok[j] && (int)sh[j] + e_span > 31) {  // the group reaches into the next cell(s)
-          const uint32_t c1 = c0[j] + 1;
-          uint32_t h = hash_slot(c1);
-          uint2 u = slots[h];
-          for (int probe = 0; probe < kQHash && u.x != c1 && u.x != kHashEmpty; probe++) {
-            h = (h + 1) & (kQHash - 1);
-            u = slots[h];
-          }
-          mhi[j] = u.x == c1 ? u.y : 0u;
-          shi[j] = h;
-        }
+        if (ok[j] && (int)sh[j] + e_span > 31)   // the group reaches into the next cell
+          mhi[j] = find_cell(slots, c0[j] + 1, &shi[j]);
       }
       if (kMode == kBits && e_span <= 32) {
         // hit bits only: every offset of the group is one bit of the row's 64-value
@@ -322,15 +342,11 @@ search_kernel(const __grid_constant__ SearchPair sp) {
           } else if (ok[j]) {   // offsets more than 63 apart inside one group: probe per member
             const uint32_t q = (c0[j] << 5) + (uint32_t)b;
             const uint32_t c = q >> 5;
-            uint32_t h = hash_slot(c);
-            uint2 u = slots[h];
-            for (int probe = 0; probe < kQHash && u.x != c && u.x != kHashEmpty; probe++) {
-              h = (h + 1) & (kQHash - 1);
-              u = slots[h];
-            }
-            if (u.x == c && ((u.y >> (q & 31)) & 1u))
+            uint32_t h = 0;
+            const uint32_t um = find_cell(slots, c, &h);
+            if ((um >> (q & 31)) & 1u)
               idx[j] = kMode == kMap
-                  ? (int32_t)(ulo + s_hpos[h] + __popc(u.y & ((1u << (q & 31)) - 1u))) : 0;
+                  ? (int32_t)(ulo + s_hpos[h] + __popc(um & ((1u << (q & 31)) - 1u))) : 0;
           }
         }
         emit<kMode>(a, o, row0, vec_ok, live, idx, bits);

@@ -5,7 +5,7 @@
 // bits (csrc/minuet/cuda/functions/arg_sort_coodrinates.cu:346-357) and removes
 // duplicates with cub::DeviceScan + a compaction kernel
 // (csrc/minuet/cuda/functions/unique_coordinates.cu:16-101).  Here the sort is a
-// hand-written stable LSD radix sort (8-bit digits, warp match ranking) that
+// hand-written stable LSD radix sort (9-bit digits, warp match ranking) that
 // only visits the key bits the bounding box uses, and unique/compaction is one
 // count + scan + compact pipeline that can also unpack keys back to coordinates.
 #include "mn_common.cuh"
@@ -24,7 +24,8 @@ constexpr int kRsThreads = 256;
 constexpr int kRsWarps = kRsThreads / 32;
 constexpr int kRsItems = 4;                       // keys per thread
 constexpr int kRsTile = kRsThreads * kRsItems;    // 1024 keys per block
-constexpr int kRadix = 256;
+constexpr int kRsBits = 9;                        // digit width: 4 passes cover 36 key bits
+constexpr int kRadix = 1 << kRsBits;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
   unsigned m;
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(kRsThreads)
 radix_hist_kernel(const uint64_t *__restrict__ keys, int64_t n, int shift,
                   uint32_t *__restrict__ block_hist, int nblocks) {
   __shared__ uint32_t hist[kRadix];
-  hist[threadIdx.x] = 0;
+  for (int d = threadIdx.x; d < kRadix; d += kRsThreads) hist[d] = 0;
   __syncthreads();
   const int64_t tile0 = (int64_t)blockIdx.x * kRsTile;
 #pragma unroll 4
@@ -46,7 +47,8 @@ radix_hist_kernel(const uint64_t *__restrict__ keys, int64_t n, int shift,
     if (i < n) atomicAdd(&hist[(keys[i] >> shift) & (kRadix - 1)], 1u);
   }
   __syncthreads();
-  block_hist[(size_t)threadIdx.x * nblocks + blockIdx.x] = hist[threadIdx.x];
+  for (int d = threadIdx.x; d < kRadix; d += kRsThreads)
+    block_hist[(size_t)d * nblocks + blockIdx.x] = hist[d];
 }
 
 // One warp per digit: exclusive scan of that digit's row over the blocks, in
@@ -88,11 +90,12 @@ radix_scatter_kernel(const uint64_t *__restrict__ keys_in, const int32_t *__rest
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kRsWarps * kRadix; i += kRsThreads) (&s_cnt[0][0])[i] = 0;
   {
-    // exclusive scan of the 256 digit totals by warp 0 (8 digits per lane)
+    // exclusive scan of the digit totals by warp 0 (kRadix / 32 digits per lane)
     if (warp == 0) {
-      uint32_t v[8], sum = 0;
+      constexpr int kPerLane = kRadix / 32;
+      uint32_t v[kPerLane], sum = 0;
 #pragma unroll
-      for (int j = 0; j < 8; j++) { v[j] = digit_total[lane * 8 + j]; sum += v[j]; }
+      for (int j = 0; j < kPerLane; j++) { v[j] = digit_total[lane * kPerLane + j]; sum += v[j]; }
       uint32_t inc = sum;
 #pragma unroll
       for (int s = 1; s < 32; s <<= 1) {
@@ -101,7 +104,7 @@ radix_scatter_kernel(const uint64_t *__restrict__ keys_in, const int32_t *__rest
       }
       uint32_t run = inc - sum;
 #pragma unroll
-      for (int j = 0; j < 8; j++) { s_base[lane * 8 + j] = run; run += v[j]; }
+      for (int j = 0; j < kPerLane; j++) { s_base[lane * kPerLane + j] = run; run += v[j]; }
     }
   }
   __syncthreads();
@@ -128,8 +131,7 @@ radix_scatter_kernel(const uint64_t *__restrict__ keys_in, const int32_t *__rest
     __syncwarp();
   }
   __syncthreads();
-  {
-    const int d = threadIdx.x;
+  for (int d = threadIdx.x; d < kRadix; d += kRsThreads) {
     uint32_t run = s_base[d] + block_hist[(size_t)d * nblocks + blockIdx.x];
 #pragma unroll
     for (int w = 0; w < kRsWarps; w++) {
@@ -375,7 +377,7 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
   uint64_t *kin = keys, *kout = keys_tmp;
   int32_t *vin = vals, *vout = vals_tmp;
   bool first = true;
-  for (int shift = begin_bit; shift < end_bit; shift += 8) {
+  for (int shift = begin_bit; shift < end_bit; shift += kRsBits) {
     MN_LAUNCH("radix_hist_kernel", st, radix_hist_kernel<<<nblocks, kRsThreads, 0, st>>>(kin, n, shift, block_hist, nblocks));
     MN_LAUNCH("radix_scan_kernel", st, radix_scan_kernel<<<kRadix / kRsWarps, kRsThreads, 0, st>>>(block_hist, nblocks, digit_total));
     {
