@@ -486,9 +486,25 @@ def gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=(16, 32, 64, 128, 2
         for fn in (F.cuda_time_gather, F.cuda_time_scatter):
             fn(tile_size=1, **kw)
         F.cuda_time_gemm(**kw)
-        tg = min(F.cuda_time_gather(tile_size=1, **kw) for _ in range(rounds))
-        tm_ = min(F.cuda_time_gemm(**kw) for _ in range(rounds))
-        ts = min(F.cuda_time_scatter(tile_size=1, **kw) for _ in range(rounds))
+        # kernel times from the library's own event pairs around each launch (the
+        # stage timers above also count the host's launch latency)
+        lib = engine.lib()
+        lib.mn_profile_enable(1)
+        for _ in range(rounds):
+            F.cuda_time_gather(tile_size=1, **kw)
+            F.cuda_time_gemm(**kw)
+            F.cuda_time_scatter(tile_size=1, **kw)
+        torch.cuda.synchronize()
+        lib.mn_profile_enable(0)
+        buf = ctypes.create_string_buffer(1 << 14)
+        lib.mn_profile_report(buf, len(buf))
+        per = {}
+        for row in buf.value.decode().splitlines():
+            name, count, kms = row.rsplit(" ", 2)
+            per[name] = float(kms) / int(count)
+        tg = per.get("gather_kernel", float("nan"))
+        ts = per.get("scatter_kernel", float("nan"))
+        tm_ = per.get("gemm_tc_kernel", per.get("gemm_simt_kernel", float("nan")))
         gather_bytes = S * c * 2 + 4 * O1 * S + E1 * c * 2
         scatter_bytes = E1 * c * 2 + 4 * O1 * T + 2 * T * c * 2
         flops = 2.0 * E * c * c

@@ -379,7 +379,7 @@ mn_status run_gather(const ConvLayout &L, const ConvBuffers &b, int64_t S, int64
   g.num_offsets = L.n_buf;
   g.row_bytes = row_bytes;
   g.lanes_per_row = lpr;
-  const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(div_up(S, 32), 8));
+  const int blocks = (int)std::min<int64_t>(kNumSMs * 64, div_up(div_up(S, 32), 8));
   {
   LaunchScope scope("gather_kernel", st);
   switch (vec) {
@@ -430,7 +430,7 @@ mn_status run_scatter_t(const ConvLayout &L, const ConvBuffers &b, int64_t T_row
   const int threads = warps_per_block * 32;
   const size_t smem = (size_t)warps_per_block * n_off * 32 * sizeof(int32_t);
   const int blocks =
-      (int)std::min<int64_t>(kNumSMs * 16, div_up(div_up(T_rows, 32), warps_per_block));
+      (int)std::min<int64_t>(kNumSMs * 64, div_up(div_up(T_rows, 32), warps_per_block));
   const int need = acc_needed(lpr);
 #define MN_SCATTER(VE)                                                                          \
   do {                                                                                          \
