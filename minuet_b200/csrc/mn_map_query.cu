@@ -553,8 +553,20 @@ __global__ void __launch_bounds__(kQThreads)
 emit_masks_kernel(const __grid_constant__ EmitArgs e) {
   __shared__ int32_t s_wtot[32][kQWarps + 1];  // offsets handled 32 at a time
   __shared__ int32_t s_pos[MN_MAX_OFFSETS];
+  __shared__ int32_t s_pre[MN_MAX_OFFSETS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   rank_offsets(e.sizes_raw, e.num_offsets, e.reorder, s_pos);
+  {
+    // this tile's rank offset for every output row, fetched once per block
+    const bool src_dir0 = blockIdx.x >= (unsigned)e.tiles_t;
+    const int tile0 = src_dir0 ? blockIdx.x - e.tiles_t : blockIdx.x;
+    const int32_t *prefix0 = src_dir0 ? e.prefix_s : e.prefix_t;
+    const int n_tiles0 = src_dir0 ? e.tiles_s : e.tiles_t;
+    for (int o = tid; o < e.num_offsets; o += kQThreads) {
+      const int b = src_dir0 ? e.mirror[o] : o;
+      s_pre[o] = __ldg(prefix0 + (int64_t)b * n_tiles0 + tile0);
+    }
+  }
   __syncthreads();
   if (blockIdx.x == 0) {
     for (int o = tid; o < e.num_offsets; o += kQThreads) {
@@ -617,7 +629,7 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
         const int t = __shfl_up_sync(0xffffffffu, inc, s);
         if (lane >= s) inc += t;
       }
-      int r = __ldg(prefix + (int64_t)b * n_tiles + tile) + s_wtot[oo][warp] + inc - mine;
+      int r = s_pre[o] + s_wtot[oo][warp] + inc - mine;
       int4 res;
       res.x = v0 ? r : -1; r += v0;
       res.y = v1 ? r : -1; r += v1;
