@@ -258,3 +258,40 @@ def test_config_scale_maps(oracle_lib, kind):
             assert sizes[-1] == len(src) and order[-1] == 13
         if kernel == 2 and stride == 2:
             assert sizes.sum() == len(src)
+
+
+def test_dense_block_takes_the_general_search_path(oracle_lib):
+    """A solid 40^3 block: the table window of a 512-row tile spans three full
+    x-slabs (4800 keys), more than the shared-memory window, so the search falls
+    back to per-group windows and global binary search."""
+    g = np.stack(np.meshgrid(*[np.arange(40)] * 3, indexing="ij"), -1).reshape(-1, 3).astype(np.int32)
+    off = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    got = host(F.query_sorted_index_with_offsets(dev(g), dev(g), dev(off)))
+    assert np.array_equal(got, oracle_lib.query(g, g, off))
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    d_g = dev(g)
+    _check_map(oracle_lib, cache.get_kernel_map(d_g, 1, None, d_g, 1, None, 3, 1), g, g, off,
+               None, None)
+    tc, ts, tbd = cache.get_target_coordinates(d_g, None, 1, 2)
+    want_c, _ = oracle_lib.downsample(g, 2, None)
+    assert np.array_equal(host(tc), want_c)
+    _check_map(oracle_lib, cache.get_kernel_map(d_g, 1, None, tc, ts, tbd, 2, 1), g, want_c,
+               generate_kernel_offsets(3, 2, 1, 1).astype(np.int32), None, None)
+
+
+def test_indoor_batch_maps(oracle_lib):
+    """Indoor-scene-like batch (4 x 200 000 voxels at 2 cm): dense surfaces, many
+    pairs per voxel; 3^3 stride 1 and the 2^3 stride 2 down-sampling map."""
+    src, sbd = synth.indoor_batch(4)
+    d_src, d_sbd = dev(src), dev(sbd)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    off3 = generate_kernel_offsets(3, 3, 1, 1).astype(np.int32)
+    r = cache.get_kernel_map(d_src, 1, d_sbd, d_src, 1, d_sbd, 3, 1)
+    _check_map(oracle_lib, r, src, src, off3, sbd, sbd)
+    tc, ts, tbd = cache.get_target_coordinates(d_src, d_sbd, 1, 2)
+    want_c, want_bd = oracle_lib.downsample(src, 2, sbd)
+    assert np.array_equal(host(tc), want_c) and np.array_equal(host(tbd), want_bd)
+    off2 = generate_kernel_offsets(3, 2, 1, 1).astype(np.int32)
+    r2 = cache.get_kernel_map(d_src, 1, d_sbd, tc, ts, tbd, 2, 1)
+    _check_map(oracle_lib, r2, src, want_c, off2, sbd, want_bd)
+    assert int(host(r2[3]).sum()) == len(src)
