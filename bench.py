@@ -531,6 +531,11 @@ def _make_cloud(seed):
     return synth.outdoor_cloud(seed, VOXELS_PER_CLOUD)
 
 
+def _make_indoor_cloud(seed):
+    from minuet_b200 import synth
+    return synth.indoor_cloud(seed, 200_000)
+
+
 def unet_section(args, torch, dist, dev, rank, world, lib):
     """Sparse UNet (fp16, random weights, eval-mode BatchNorm) on 64 outdoor clouds
     sharded by cloud over the ranks; the logits are gathered with NCCL.  Strong
@@ -540,24 +545,32 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     from minuet_b200 import sharding
     from minuet_b200.unet import SparseUNet
 
-    n_clouds = args.unet_clouds
-    shards = sharding.assign_clouds([VOXELS_PER_CLOUD] * n_clouds, world)
+    indoor = args.unet_config == "c3"       # C3: 8 indoor scenes x 200k voxels, RGB features
+    n_clouds = 8 if indoor and args.unet_clouds == UNET_CLOUDS else args.unet_clouds
+    per_cloud = 200_000 if indoor else VOXELS_PER_CLOUD
+    shards = sharding.assign_clouds([per_cloud] * n_clouds, world)
     mine = shards[rank]
     with concurrent.futures.ProcessPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as pool:
-        clouds = list(pool.map(_make_cloud, [UNET_SEED0 + i for i in mine]))
+        if indoor:
+            clouds = list(pool.map(_make_indoor_cloud, [2000 + i for i in mine]))
+        else:
+            clouds = list(pool.map(_make_cloud, [UNET_SEED0 + i for i in mine]))
     coords = np.ascontiguousarray(np.concatenate(clouds).astype(np.int32))
     bd = np.zeros(len(clouds) + 1, dtype=np.int64)
     bd[1:] = np.cumsum([len(c) for c in clouds])
     rng = np.random.default_rng(UNET_SEED0 + 7919 * rank)
-    feats = np.concatenate([coords.astype(np.float32) * 0.05,
-                            rng.random((len(coords), 1), dtype=np.float32)], axis=1)
+    if indoor:
+        feats = rng.random((len(coords), 3), dtype=np.float32)
+    else:
+        feats = np.concatenate([coords.astype(np.float32) * 0.05,
+                                rng.random((len(coords), 1), dtype=np.float32)], axis=1)
     h_coords = torch.from_numpy(coords).pin_memory()
     h_bd = torch.from_numpy(bd).pin_memory()
     h_feats = torch.from_numpy(feats).half().pin_memory()
     d_coords, d_bd, d_feats = h_coords.to(dev), h_bd.to(dev), h_feats.to(dev)
 
     torch.manual_seed(0)
-    net = SparseUNet(4, num_classes=20).to(dev).half().eval().fuse()
+    net = SparseUNet(feats.shape[1], num_classes=20).to(dev).half().eval().fuse()
     cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
     minuet.set_kernel_map_cache(net, cache)
 
@@ -630,15 +643,18 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
         "metric": "sparse-UNet fp16 clouds/sec", "value": round(n_clouds * steps / (ms * 1e-3), 2),
         "unit": "clouds/s", "scaling": "strong", "ms_per_step": round(ms / steps, 3),
         "steps": steps, "warmup": warm,
-        "config": {"workload": "C4: UNet (stem 32, encoder 32/64/128/256, decoder mirror, 20 "
-                               "classes) on 64 outdoor clouds x 120k voxels, 4-channel fp16 "
-                               "features, clouds sharded over the GPUs, NCCL gather of the logits",
+        "config": {"workload": ("C3: UNet on 8 indoor scenes x 200k voxels, RGB fp16 features"
+                                if indoor else
+                                "C4: UNet (stem 32, encoder 32/64/128/256, decoder mirror, 20 "
+                                "classes) on 64 outdoor clouds x 120k voxels, 4-channel fp16 "
+                                "features") + ", clouds sharded over the GPUs, NCCL gather of "
+                               "the logits",
                    "clouds_total": n_clouds, "clouds_on_rank0": len(mine),
                    "voxels_on_rank0": int(len(coords))},
         "e2e": {"value": round(n_clouds * steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "ms_per_step": round(ms_e2e / steps, 3),
                 "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_bd.numel() * 8 + h_feats.numel() * 2),
-                "d2h_bytes_per_step": int(n_clouds * VOXELS_PER_CLOUD)},
+                "d2h_bytes_per_step": int(n_clouds * per_cloud)},
         "gpu_launches": int(launches),
         "library_kernel_ms_rank0_one_step": kernels,
     }
@@ -657,6 +673,8 @@ def main():
     ap.add_argument("--unet-clouds", type=int, default=UNET_CLOUDS,
                     help="clouds in the UNet job (64 = the benchmark configuration)")
     ap.add_argument("--gms-channels", default="16,32,64,128,256")
+    ap.add_argument("--unet-config", default="c4", choices=["c3", "c4"],
+                    help="c4: 64 outdoor clouds (default); c3: 8 indoor scenes with RGB features")
     ap.add_argument("--gms-sweep", action="store_true",
                     help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
     args = ap.parse_args()
