@@ -47,6 +47,9 @@ struct ImArgs {
   int32_t *status;
   int64_t T;
   int32_t K, N, n_pad, k_blocks, stages, a_bytes, stage_bytes, elem_is_bf16, num_tiles, relu;
+  int32_t sub;         // 128-row sub-tiles per CTA tile (1 or 2): they share every weight tile
+  int32_t acc_bufs;    // accumulator sets in TMEM (2 when 2 * sub * n_pad <= 512, else 1)
+  int32_t n_tiles128;  // entries of tile_bits
 };
 
 // 16-byte asynchronous copy; src_bytes = 0 writes 16 zero bytes instead (the fill
@@ -101,25 +104,36 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
 
   if (warp < 4) {
     // ------------------------------ producers ---------------------------------
-    const int r = threadIdx.x;               // A-tile row owned by this thread
+    const int r = threadIdx.x;               // row owned by this thread in every 128-row sub-tile
+    const int sub = args.sub;
     const uint32_t b_bytes = (uint32_t)(args.stage_bytes - args.a_bytes);
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
-      const int64_t t = (int64_t)tile * kBM + r;
-      const bool row_live = t < args.T;
-      uint32_t rest = __ldg(args.tile_bits + tile);
-      // software pipeline over the active offsets: the next offset's source row is
-      // requested before the current one is copied
+      int64_t t[2];
+      bool row_live[2];
+      uint32_t rest = 0u;
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        t[h] = ((int64_t)tile * sub + h) * kBM + r;
+        row_live[h] = h < sub && t[h] < args.T;
+        if (h < sub && tile * sub + h < args.n_tiles128) rest |= __ldg(args.tile_bits + tile * sub + h);
+      }
+      // software pipeline over the active offsets: the next offset's source rows are
+      // requested before the current ones are copied
       int p = rest != 0u ? __ffs(rest) - 1 : -1;
-      int src = (p >= 0 && row_live) ? __ldg(args.nbr + (int64_t)p * args.T + t) : -1;
+      int src[2], src_next[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++)
+        src[h] = (p >= 0 && row_live[h]) ? __ldg(args.nbr + (int64_t)p * args.T + t[h]) : -1;
       while (alive && p >= 0) {
         rest &= rest - 1u;
         const int p_next = rest != 0u ? __ffs(rest) - 1 : -1;
-        const int src_next =
-            (p_next >= 0 && row_live) ? __ldg(args.nbr + (int64_t)p_next * args.T + t) : -1;
-        const uint8_t *src_row = args.in + (int64_t)(src < 0 ? 0 : src) * args.K * 2;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+          src_next[h] = (p_next >= 0 && row_live[h])
+                            ? __ldg(args.nbr + (int64_t)p_next * args.T + t[h]) : -1;
         for (int kb = 0; kb < args.k_blocks; kb++) {
           // one lane per warp polls the barrier; the others wait at the warp barrier
           int ok = 1;
@@ -132,13 +146,19 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
             mbar_expect_tx(&bar_full[stage], b_bytes);
             tma_load_3d(sa + args.a_bytes, &map_b, kb * kBK, 0, widx, &bar_full[stage]);
           }
-          const uint32_t dst_row = smem_u32(sa) + (uint32_t)r * 128u;
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
-            const int kcol = kb * kBK + j * 8;
-            const uint32_t dst = dst_row + (uint32_t)((j ^ (r & 7)) << 4);
-            const bool valid = src >= 0 && kcol < args.K;
-            cp_async_16(dst, valid ? src_row + (size_t)kcol * 2 : args.in, valid ? 16u : 0u);
+          for (int h = 0; h < 2; h++) {
+            if (h < sub) {
+              const uint8_t *src_row = args.in + (int64_t)(src[h] < 0 ? 0 : src[h]) * args.K * 2;
+              const uint32_t dst_row = smem_u32(sa) + (uint32_t)(h * kBM + r) * 128u;
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const int kcol = kb * kBK + j * 8;
+                const uint32_t dst = dst_row + (uint32_t)((j ^ (r & 7)) << 4);
+                const bool valid = src[h] >= 0 && kcol < args.K;
+                cp_async_16(dst, valid ? src_row + (size_t)kcol * 2 : args.in, valid ? 16u : 0u);
+              }
+            }
           }
           // this thread's arrival fires when its copies above have landed: no stall here
           asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
@@ -147,7 +167,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         p = p_next;
-        src = src_next;
+        src[0] = src_next[0];
+        src[1] = src_next[1];
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this thread is in flight at exit
@@ -163,8 +184,11 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
         if (!mbar_wait(&bar_acc_empty[acc], acc_phase ^ 1u, abort_flag, args.status)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * args.n_pad);
-        const int n_stage = __popc(__ldg(args.tile_bits + tile)) * args.k_blocks;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * args.sub * args.n_pad);
+        uint32_t tb = 0u;
+        for (int h = 0; h < args.sub; h++)
+          if (tile * args.sub + h < args.n_tiles128) tb |= __ldg(args.tile_bits + tile * args.sub + h);
+        const int n_stage = __popc(tb) * args.k_blocks;
         uint32_t accumulate = 0u;
         for (int it = 0; it < n_stage; it++) {
           const int kb = it % args.k_blocks;
@@ -174,8 +198,10 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           const uint32_t sb = sa + (uint32_t)args.a_bytes;
           const int nk = min(kBK / kUmmaK, (args.K - kb * kBK + kUmmaK - 1) / kUmmaK);
           for (int k = 0; k < nk; k++) {
-            umma_f16(tmem_d, umma_desc(sa + k * kUmmaK * 2), umma_desc(sb + k * kUmmaK * 2), idesc,
-                     accumulate);
+            const uint64_t db = umma_desc(sb + k * kUmmaK * 2);   // one weight tile, all sub-tiles
+            for (int h = 0; h < args.sub; h++)
+              umma_f16(tmem_d + (uint32_t)(h * args.n_pad),
+                       umma_desc(sa + h * (kBM * kBK * 2) + k * kUmmaK * 2), db, idesc, accumulate);
             accumulate = 1u;
           }
           umma_commit(&bar_empty[stage]);
@@ -183,7 +209,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
         }
         if (!alive) break;
         umma_commit(&bar_acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == args.acc_bufs) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else {
@@ -199,10 +225,16 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool empty_tile = __ldg(args.tile_bits + tile) == 0u;   // no pair: the rows are zero
-      const int out_row = tile * kBM + quarter * 32;
+      uint32_t tb = 0u;
+      for (int h = 0; h < args.sub; h++)
+        if (tile * args.sub + h < args.n_tiles128) tb |= __ldg(args.tile_bits + tile * args.sub + h);
+      const bool empty_tile = tb == 0u;   // no pair in the whole tile: no MMA ran, the rows are zero
+      for (int h = 0; h < args.sub; h++) {
+      const int out_row = (tile * args.sub + h) * kBM + quarter * 32;
+      if ((int64_t)out_row >= args.T) break;
       const int64_t row = (int64_t)out_row + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_pad);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                             (uint32_t)((acc * args.sub + h) * args.n_pad);
       for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
         uint8_t *buf = cbuf + (chunk & 1) * 4096;
         uint32_t rr[64];
@@ -264,10 +296,11 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (++acc == args.acc_bufs) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
@@ -422,11 +455,19 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   a.N = (int)c_out;
   a.n_pad = (int)align_up((size_t)c_out, 16);
   a.k_blocks = (int)div_up(c_in, kBK);
-  a.a_bytes = kBM * kBK * 2;
+  // two 128-row sub-tiles per CTA tile halve the weight traffic per output row; keep one
+  // when the job would otherwise not fill the SMs
+  a.n_tiles128 = (int)div_up(T, kBM);
+  // (with one accumulator set the epilogue no longer overlaps the next tile's MMAs, which
+  // only pays off when a tile has many pipeline stages)
+  const bool two_sets_fit = 2 * 2 * a.n_pad <= 512;
+  a.sub = (a.n_tiles128 >= 2 * 2 * kNumSMs && (two_sets_fit || O * a.k_blocks >= 32)) ? 2 : 1;
+  a.acc_bufs = 2 * a.sub * a.n_pad <= 512 ? 2 : 1;
+  a.a_bytes = a.sub * kBM * kBK * 2;
   a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
   a.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / a.stage_bytes));
   a.elem_is_bf16 = bf16 ? 1 : 0;
-  a.num_tiles = (int)div_up(T, kBM);
+  a.num_tiles = (int)div_up(a.n_tiles128, a.sub);
   a.relu = relu ? 1 : 0;
 
   CUtensorMap map_b, map_out;
