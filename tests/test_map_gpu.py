@@ -295,3 +295,30 @@ def test_indoor_batch_maps(oracle_lib):
     r2 = cache.get_kernel_map(d_src, 1, d_sbd, tc, ts, tbd, 2, 1)
     _check_map(oracle_lib, r2, src, want_c, off2, sbd, want_bd)
     assert int(host(r2[3]).sum()) == len(src)
+
+
+def test_short_workspace_and_bad_shapes_are_errors_not_faults():
+    """Host-side fault injection: a workspace that is too small, a kernel with more
+    offsets than the library supports and a mask/weight mismatch come back as
+    status codes with a message; nothing is launched with bad pointers."""
+    import ctypes
+    from minuet_b200 import _lib, engine
+    lib = _lib.load()
+    km = torch.full((27, 5000), -1, dtype=torch.int32, device=DEV)
+    sm = torch.empty((27, 5000), dtype=torch.int32, device=DEV)
+    tm = torch.empty((27, 5000), dtype=torch.int32, device=DEV)
+    ws = torch.empty(64, dtype=torch.uint8, device=DEV)
+    st = lib.mn_compute_kernel_map_masks(engine.ptr(km), 27, 5000, 5000, engine.ptr(sm),
+                                         engine.ptr(tm), engine.ptr(ws), ws.numel(),
+                                         engine.stream_ptr(torch.device(DEV)))
+    assert st == _lib.MN_ERR_WORKSPACE and "workspace" in _lib.last_error()
+    big = torch.zeros((200, 3), dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError):
+        F.query_sorted_index_with_offsets(dev(np.zeros((4, 3), np.int32)),
+                                          dev(np.zeros((4, 3), np.int32)), big)
+    with pytest.raises(RuntimeError):
+        F.sparse_convolution_forward(torch.zeros(10, 8, device=DEV), torch.zeros(27, 8, 8, device=DEV),
+                                     torch.zeros((26, 10), dtype=torch.int32, device=DEV),
+                                     torch.zeros((27, 10), dtype=torch.int32, device=DEV), None,
+                                     torch.zeros(27, dtype=torch.int32, device=DEV), 1, 1)
+    torch.cuda.synchronize()

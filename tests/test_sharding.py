@@ -67,3 +67,41 @@ def test_gather_rows_world2(tmp_path, sizes):
     total = sum(sizes)
     assert full.shape == (total, 3)
     assert torch.equal(full[:, 0], torch.arange(total, dtype=torch.float32))
+
+
+def _dropout_worker(rank, world, port, result_path):
+    """Rank 1 leaves between steps (no collective in flight); rank 0's next gather
+    must end with an error after the short process-group timeout instead of hanging."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    local = torch.full((3 + rank, 2), float(rank))
+    sharding.gather_rows(local, dst=0)          # step 1: both ranks present
+    if rank == 1:
+        os._exit(0)                              # the rank disappears between steps
+    try:
+        sharding.gather_rows(local, dst=0)      # step 2: the peer is gone
+        outcome = "no error"
+    except Exception as exc:                     # gloo reports a timeout / connection error
+        outcome = "error: " + type(exc).__name__
+    with open(result_path, "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_lost_rank_is_reported_not_waited_for_forever(tmp_path):
+    path = str(tmp_path / "outcome.txt")
+    ctx = mp.spawn(_dropout_worker, args=(2, _free_port(), path), nprocs=2, join=False)
+    deadline = 60
+    import time
+    t0 = time.time()
+    while not os.path.exists(path) and time.time() - t0 < deadline:
+        time.sleep(0.2)
+    for p in ctx.processes:
+        p.join(timeout=5)
+        if p.is_alive():
+            p.kill()
+    assert os.path.exists(path), "rank 0 was still waiting after 60 s"
+    assert open(path).read().startswith("error")
