@@ -5,3 +5,4 @@ from .convolution import *
 from .memory import *
 from .pooling import *
 from .concat import *
+from .voxelize import *

@@ -322,3 +322,38 @@ def test_short_workspace_and_bad_shapes_are_errors_not_faults():
                                      torch.zeros((27, 10), dtype=torch.int32, device=DEV), None,
                                      torch.zeros(27, dtype=torch.int32, device=DEV), 1, 1)
     torch.cuda.synchronize()
+
+
+def test_voxelize_with_inverse():
+    rng = np.random.default_rng(21)
+    pts = rng.uniform(-3.0, 3.0, size=(20_000, 3)).astype(np.float32)
+    bd = np.array([0, 8_000, 20_000], np.int64)
+    vox, vbd, inv = F.voxelize(dev(pts), 0.25, batch_dims=dev(bd), return_inverse=True)
+    want = []
+    for a, b in zip(bd[:-1], bd[1:]):
+        want.append(synth.sort_unique(np.floor(pts[a:b] / np.float32(0.25)).astype(np.int64)))
+    assert np.array_equal(host(vox), np.concatenate(want))
+    assert host(vbd).tolist() == [0, len(want[0]), len(want[0]) + len(want[1])]
+    back = host(vox)[host(inv)]
+    assert np.array_equal(back, np.floor(pts / np.float32(0.25)).astype(np.int32))
+    # every point of cloud g lands in a voxel of cloud g
+    assert (host(inv)[:8000] < len(want[0])).all() and (host(inv)[8000:] >= len(want[0])).all()
+
+
+def test_int64_coordinates_through_a_layer(oracle_lib):
+    rng = np.random.default_rng(22)
+    src, sbd = synth.random_small_batch(rng, 2, 2500, 20, low=-7)
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int64, device=DEV)
+    conv = minuet.nn.SparseConv3d(8, 8, 2, stride=2, device=DEV)
+    minuet.set_kernel_map_cache(conv, cache)
+    x = minuet.SparseTensor(torch.randn(len(src), 8, device=DEV), dev(src, torch.int64),
+                            batch_dims=dev(sbd, torch.int32))
+    out = conv(x)
+    want_c, want_bd = oracle_lib.downsample(src, 2, sbd)
+    assert out.C.dtype == torch.int64 and np.array_equal(host(out.C), want_c)
+    assert out.batch_dims.dtype == torch.int32 and np.array_equal(host(out.batch_dims), want_bd)
+    off = generate_kernel_offsets(3, 2, 1, 1).astype(np.int32)
+    m = oracle_lib.build_kernel_map(src, want_c, off, sbd, want_bd)
+    ref = oracle_lib.conv_forward(x.F.cpu().numpy(), conv.kernel.detach().cpu().numpy(),
+                                  m["source_masks"], m["target_masks"], m["order"], acc64=True)
+    assert np.abs(host(out.F) - ref).max() <= 1e-5 * np.abs(ref).max()
