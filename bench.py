@@ -55,9 +55,13 @@ def oracle_step(oracle, coords, bd, offsets):
 
 
 def run_cpu(steps, warmup, coords, bd, min_seconds=0.0):
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     import oracle
     from minuet_b200.utils.helpers import generate_kernel_offsets
     oracle.build()
+    oracle.set_num_threads(cores)
     offsets = {k: generate_kernel_offsets(3, k, 1, 1).astype(np.int32) for k in (2, 3)}
     for _ in range(warmup):
         oracle_step(oracle, coords, bd, offsets)

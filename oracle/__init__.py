@@ -65,6 +65,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Override OMP_NUM_THREADS for the oracle (launchers such as torchrun export 1)."""
+    lib().orc_set_num_threads(ctypes.c_int(int(n)))
+
+
 def arg_sort(coords, batch_dims=None):
     coords = _i32(coords)
     n, d = coords.shape

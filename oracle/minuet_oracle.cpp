@@ -68,6 +68,14 @@ inline int64_t cloud_of(int64_t row, int64_t nb, const int64_t *bd) {
 
 extern "C" {
 
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
