@@ -171,13 +171,22 @@ scatter_kernel(const ScatterArgs<T> a, const __grid_constant__ RowPlan plan) {
     for (int r0 = 0; r0 < 32; r0 += rpi) {
       const int r = r0 + sub;
       const int64_t t = (blk << 5) + r;
+      // a row without any pair keeps the centre product the GEMM already wrote
+      // (all shuffles happen here, before the row groups of the warp diverge)
+      uint32_t hw[4] = {0u, 0u, 0u, 0u}, any_hit = 0u;
+#pragma unroll
+      for (int w = 0; w < 4; w++) {
+        if (w * 32 < O) hw[w] = __shfl_sync(0xffffffffu, hits[w], r);
+        any_hit |= hw[w];
+      }
+      if (any_hit == 0u && a.add_existing) continue;
       float acc[kAcc];
 #pragma unroll
       for (int i = 0; i < kAcc; i++) acc[i] = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; w++) {
         if (w * 32 < O) {
-          uint32_t h = __shfl_sync(0xffffffffu, hits[w], r);
+          uint32_t h = hw[w];
           while (h != 0u) {
             const int o = w * 32 + __ffs(h) - 1;
             h &= h - 1u;
