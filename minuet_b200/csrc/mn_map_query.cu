@@ -473,8 +473,8 @@ struct ScanArgs {
   int32_t *sizes;  // [2, O]
 };
 
-__global__ void __launch_bounds__(256) scan_tiles_kernel(const ScanArgs p) {
-  __shared__ int32_t s_warp[8];
+__global__ void __launch_bounds__(1024) scan_tiles_kernel(const ScanArgs p) {
+  __shared__ int32_t s_warp[32];
   __shared__ int32_t s_carry;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int o = blockIdx.x, dir = blockIdx.y;
@@ -482,7 +482,7 @@ __global__ void __launch_bounds__(256) scan_tiles_kernel(const ScanArgs p) {
   int32_t *row = p.counts[dir] + (int64_t)o * n;
   if (threadIdx.x == 0) s_carry = 0;
   __syncthreads();
-  for (int b0 = 0; b0 < n; b0 += 256) {
+  for (int b0 = 0; b0 < n; b0 += 1024) {
     const int b = b0 + threadIdx.x;
     const int32_t v = b < n ? row[b] : 0;
     int32_t inc = v;
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(256) scan_tiles_kernel(const ScanArgs p) {
     for (int w = 0; w < warp; w++) before += s_warp[w];
     if (b < n) row[b] = before + inc - v;
     __syncthreads();
-    if (threadIdx.x == 255) s_carry = before + inc;
+    if (threadIdx.x == 1023) s_carry = before + inc;
     __syncthreads();
   }
   if (threadIdx.x == 0) p.sizes[dir * p.num_offsets + o] = s_carry;
@@ -864,7 +864,7 @@ extern "C" mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int6
                                                                      nullptr));
   ScanArgs p{};
   p.counts[0] = counts; p.tiles[0] = n_tiles; p.num_offsets = (int)O; p.sizes = scratch;
-  MN_LAUNCH("scan_tiles_kernel", st, scan_tiles_kernel<<<dim3((unsigned)O, 1), 256, 0, st>>>(p));
+  MN_LAUNCH("scan_tiles_kernel", st, scan_tiles_kernel<<<dim3((unsigned)O, 1), 1024, 0, st>>>(p));
   MN_LAUNCH("map_masks_kernel", st, map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
       kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out));
   return MN_OK;
@@ -945,7 +945,7 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   p.counts[1] = counts_s; p.tiles[1] = tiles_s;
   p.num_offsets = (int)O; p.sizes = sizes_raw;
   MN_LAUNCH("scan_tiles_kernel", st,
-            scan_tiles_kernel<<<dim3((unsigned)O, mirrored ? 1 : 2), 256, 0, st>>>(p));
+            scan_tiles_kernel<<<dim3((unsigned)O, mirrored ? 1 : 2), 1024, 0, st>>>(p));
 
   EmitArgs e{};
   e.words_t = words_t; e.words_s = words_s; e.prefix_t = counts_t; e.prefix_s = counts_s;

@@ -332,20 +332,30 @@ unique_compact_kernel(const View v, const Sink sink, const uint32_t *__restrict_
   }
 }
 
-// out_bd[g] = number of unique keys whose cloud id is < g
-__global__ void cloud_starts_kernel(const uint64_t *__restrict__ keys,
-                                    const int64_t *__restrict__ count, int cloud_shift,
-                                    int num_clouds, int64_t *__restrict__ out_bd) {
-  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+// out_bd[g] = number of unique keys whose cloud id is < g.  One warp per cloud
+// boundary: a 32-ary ballot search (4 rounds of loads for half a million keys
+// instead of the 19 dependent loads of a binary search).
+__global__ void __launch_bounds__(128)
+cloud_starts_kernel(const uint64_t *__restrict__ keys, const int64_t *__restrict__ count,
+                    int cloud_shift, int num_clouds, int64_t *__restrict__ out_bd) {
+  const int lane = threadIdx.x & 31;
+  const int g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (g > num_clouds) return;
-  const int64_t n = *count;
-  int64_t lo = 0, hi = n;
   const uint64_t q = (uint64_t)g << cloud_shift;
-  while (lo < hi) {
-    int64_t mid = (lo + hi) >> 1;
-    if (keys[mid] < q) lo = mid + 1; else hi = mid;
+  int64_t lo = 0, hi = *count;
+  for (int round = 0; round < 16; round++) {
+    const int64_t len = hi - lo;
+    if (len <= 0) break;
+    const int64_t stride = (len + 31) >> 5;
+    const int64_t idx = lo + (int64_t)(lane + 1) * stride - 1;
+    const bool pred = idx < hi && keys[idx] < q;
+    const int c = __popc(__ballot_sync(0xffffffffu, pred));
+    if (stride == 1) { lo += c; break; }
+    const int64_t nlo = min(lo + (int64_t)c * stride, hi);
+    hi = min(hi, nlo + stride - 1);
+    lo = nlo;
   }
-  out_bd[g] = lo;
+  if (lane == 0) out_bd[g] = lo;
 }
 
 __global__ void zero_index0_kernel(int64_t *indices) { indices[0] = 0; }
@@ -498,7 +508,7 @@ extern "C" mn_status mn_downsample_coordinates(
   MN_LAUNCH("unique_compact_kernel", st, unique_compact_kernel<KeysView, KeySink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts));
   if (batch_dims != nullptr && out_batch_dims != nullptr) {
     const int nb = (int)num_clouds + 1;
-    MN_LAUNCH("cloud_starts_kernel", st, cloud_starts_kernel<<<(nb + 127) / 128, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
+    MN_LAUNCH("cloud_starts_kernel", st, cloud_starts_kernel<<<(nb + 3) / 4, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
                                                            (int)num_clouds, out_batch_dims));
   }
   return MN_OK;
