@@ -417,7 +417,10 @@ def gpu_arm(args):
         "frac": None if achieved is None else round(achieved / peaks["hbm_gbs"], 4),
         "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured"
         else "fallback 6650 GB/s",
-        "traffic": None,
+        # dram__bytes_read + dram__bytes_write of the search launches of one step under ncu
+        # (3.9 MB read per search direction, 7 directions; the hit words and tile counts they
+        # write were still in L2 when the kernels ended), profiles/search_and_emit_kernels_C1.md
+        "traffic": 27.3e6 if top.startswith("search_kernel") else None,
         "algorithmic_bytes_per_step": top_bytes,
         "kernel_ms_per_step": round(top_ms, 4),
         "launches_per_step": kernels[top]["launches_per_step"],
