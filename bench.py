@@ -448,6 +448,11 @@ def gpu_arm(args):
     if world == 1 and args.gms_sweep:
         chans = tuple(int(c) for c in args.gms_channels.split(","))
         sweep = gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=chans)
+        # the same sweep on the single 50 000-voxel uniform cloud of the fp32 configuration
+        u_coords = torch.from_numpy(synth.uniform_cloud()).to(dev)
+        u_cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
+        sweep["uniform50k"] = gms_sweep(torch, minuet, u_cache, u_coords, None, channels=chans)
+        sweep["uniform50k"]["map"] = "3^3 stride 1 on 50 000 uniform voxels in [0,256)^3"
 
     h2d = h_coords.numel() * 4 + h_bd.numel() * 8
     d2h = sum((k ** 3 + 1) * 4 + k ** 3 * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8 + 32
