@@ -141,15 +141,17 @@ _host_copies = {}
 
 
 class PendingHostCopy:
-    """Asynchronous device-to-host copy of ``[values..., status word]`` into
-    pinned memory; the wait happens when (and if) the host needs the values."""
+    """Asynchronous device-to-host copies of a small tensor and of the status word
+    into pinned memory (two DMA transfers, no kernel); the wait happens when (and
+    if) the host needs the values."""
 
     def __init__(self, values: torch.Tensor):
         device = values.device
-        packed = torch.cat([values, status_word(device)])
         self.device = device
-        self.pinned = torch.empty(packed.shape, dtype=packed.dtype, pin_memory=True)
-        self.pinned.copy_(packed, non_blocking=True)
+        self.pinned = torch.empty(values.shape, dtype=values.dtype, pin_memory=True)
+        self.pinned_status = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        self.pinned.copy_(values, non_blocking=True)
+        self.pinned_status.copy_(status_word(device), non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record(torch.cuda.current_stream(device))
         self.values = None
@@ -157,9 +159,8 @@ class PendingHostCopy:
     def get(self) -> np.ndarray:
         if self.values is None:
             self.event.synchronize()
-            host = self.pinned.numpy().copy()
-            raise_on_status(int(host[-1]), self.device)
-            self.values = np.ascontiguousarray(host[:-1])
+            raise_on_status(int(self.pinned_status[0]), self.device)
+            self.values = np.ascontiguousarray(self.pinned.numpy().copy())
             self.pinned = None
         return self.values
 
