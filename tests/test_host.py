@@ -158,3 +158,48 @@ def test_module_surface_and_tunable_config(tmp_path):
     with pytest.raises(RuntimeError):
         cache.get_target_coordinates(torch.zeros(2, 3, dtype=torch.int32), None, 2, 2,
                                      transposed=True)
+
+
+def _pack_numpy(coords, clouds, spec):
+    """numpy twin of the device key packing (mn_keyspec layout)."""
+    keys = clouds.astype(np.uint64) << np.uint64(spec.cloud_shift)
+    for k in range(spec.ndim):
+        field = (coords[:, k].astype(np.int64) - spec.base[k]).astype(np.uint64)
+        keys |= field << np.uint64(spec.shift[k])
+    return keys
+
+
+def test_key_layout_preserves_order_and_offset_addition(mn_lib):
+    """Properties the Map-step kernels rely on: unsigned key order equals
+    (cloud, lexicographic) order, and key(c + offset) == key(c) + delta(offset)
+    as plain 64-bit arithmetic for every offset within the margin."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.integers(1, 3), st.integers(0, 9), st.integers(1, 40), st.integers(0, 2 ** 20),
+           st.integers(0, 10 ** 6))
+    def check(ndim_minus_1, margin, n, span, seed):
+        ndim = ndim_minus_1 + 1
+        rng = np.random.default_rng(seed)
+        lo = rng.integers(-2 ** 20, 2 ** 20, size=ndim)
+        coords = (lo + rng.integers(0, span + 1, size=(n, ndim))).astype(np.int32)
+        clouds = np.sort(rng.integers(0, 5, size=n))
+        mm = np.zeros(8, np.int32)
+        mm[:ndim] = coords.min(0)
+        mm[4:4 + ndim] = coords.max(0)
+        spec = _lib.KeySpec()
+        assert mn_lib.mn_keyspec_make(mm.ctypes.data_as(ctypes.c_void_p), ndim, 5, margin,
+                                      ctypes.byref(spec)) == 0
+        keys = _pack_numpy(coords, clouds, spec)
+        # order
+        want = np.lexsort(tuple(coords[:, k] for k in range(ndim - 1, -1, -1)) + (clouds,))
+        got = np.argsort(keys, kind="stable")
+        assert np.array_equal(keys[got], keys[want])
+        # offsets within the margin never borrow across fields
+        off = rng.integers(-margin, margin + 1, size=ndim)
+        delta = sum(int(off[k]) << int(spec.shift[k]) for k in range(ndim))
+        moved = _pack_numpy(coords + off.astype(np.int32), clouds, spec)
+        assert np.array_equal(moved.astype(np.int64), keys.astype(np.int64) + delta)
+        assert spec.total_bits <= 63
+
+    check()
