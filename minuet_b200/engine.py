@@ -70,9 +70,17 @@ def as_i64(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 
 
 # ---------------------------------------------------------------------------
-# device status word (bit 1: a coordinate fell outside the key box)
+# device status word
+#   bit 1 (value 2): a coordinate fell outside the box the keys were built for
+#   bit 2 (value 4): a bounded wait inside a tensor-core kernel ran out; the
+#                    features that kernel wrote are invalid
+#   bit 3 (value 8): the bounding box needs more than 63 key bits
 # ---------------------------------------------------------------------------
+STATUS_KEY_BOX = 2
+STATUS_TC_TIMEOUT = 4
+STATUS_KEY_BITS = 8
 _status = {}
+_pending_status = {}
 
 
 def status_word(device) -> torch.Tensor:
@@ -83,17 +91,57 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+def decode_status(value: int) -> Optional[Exception]:
+    """The exception a non-zero status word stands for (None for 0)."""
+    value = int(value)
+    if value == 0:
+        return None
+    parts = []
+    if value & STATUS_TC_TIMEOUT:
+        parts.append("a tensor-core kernel gave up waiting on one of its barriers: the "
+                     "features it wrote are invalid (MN_ERR_DEVICE)")
+    if value & STATUS_KEY_BITS:
+        parts.append("the bounding box of the coordinates needs more than 63 key bits")
+    if value & STATUS_KEY_BOX:
+        parts.append("a coordinate lies outside the bounding box the sort/search keys were "
+                     "built for (call KernelMapCache.reset() before feeding unrelated "
+                     "coordinates)")
+    if value & ~(STATUS_KEY_BOX | STATUS_TC_TIMEOUT | STATUS_KEY_BITS):
+        parts.append(f"unknown device status bits 0x{value:x}")
+    if value & STATUS_KEY_BITS and not value & STATUS_TC_TIMEOUT:
+        return NotImplementedError("; ".join(parts))
+    return RuntimeError("; ".join(parts))
+
+
 def raise_on_status(value: int, device):
-    if value != 0:
+    error = decode_status(value)
+    if error is not None:
         status_word(device).zero_()
-        raise RuntimeError(
-            "a coordinate lies outside the bounding box the sort/search keys were built for "
-            "(call KernelMapCache.reset() before feeding unrelated coordinates)")
+        raise error
 
 
 def check_status(device):
     """Blocking read of the status word."""
     raise_on_status(int(status_word(device).item()), device)
+
+
+def poll_status(device):
+    """Non-blocking check for the forward path: queues an asynchronous copy of the
+    status word into pinned memory and raises for any earlier copy that has
+    landed with a non-zero value.  An error therefore surfaces at the latest one
+    call after the kernel that raised it, without a host-device synchronisation."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    queue = _pending_status.setdefault(key, [])
+    while queue and queue[0][1].query():
+        pinned, _ = queue.pop(0)
+        raise_on_status(int(pinned[0]), device)
+    if len(queue) < 8:
+        pinned = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        pinned.copy_(status_word(device), non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(device))
+        queue.append((pinned, event))
 
 
 # ---------------------------------------------------------------------------

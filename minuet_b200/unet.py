@@ -13,6 +13,7 @@ from typing import Sequence
 import torch
 from torch import nn
 
+from minuet_b200 import engine
 from minuet_b200.nn import BatchNorm, ReLU, SparseConv, SparseConv3d, fold_batchnorm
 from minuet_b200.nn import functional as F
 from minuet_b200.tensors import SparseTensor
@@ -112,4 +113,7 @@ class SparseUNet(nn.Module):
         for up, dec in zip(self.up, self.dec):
             x = up(x)
             x = dec(F.cat([x, skips.pop()]))
-        return self.head(x)
+        out = self.head(x)
+        if out.F.is_cuda:
+            engine.poll_status(out.F.device)   # device-side errors of this pass (no sync)
+        return out

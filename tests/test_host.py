@@ -188,8 +188,16 @@ def test_key_layout_preserves_order_and_offset_addition(mn_lib):
         mm[:ndim] = coords.min(0)
         mm[4:4 + ndim] = coords.max(0)
         spec = _lib.KeySpec()
-        assert mn_lib.mn_keyspec_make(mm.ctypes.data_as(ctypes.c_void_p), ndim, 5, margin,
-                                      ctypes.byref(spec)) == 0
+        status = mn_lib.mn_keyspec_make(mm.ctypes.data_as(ctypes.c_void_p), ndim, 5, margin,
+                                        ctypes.byref(spec))
+        # bits the box needs: per dimension the width of (extent + 2 * margin), plus 3 cloud bits
+        need = 3 + sum(max(1, int(int(mm[4 + k]) - int(mm[k]) + 2 * margin).bit_length())
+                       for k in range(ndim))
+        if need > 63:
+            # documented limit: one 64-bit key per voxel
+            assert status == _lib.MN_ERR_UNSUPPORTED and b"63" in mn_lib.mn_last_error()
+            return
+        assert status == 0
         keys = _pack_numpy(coords, clouds, spec)
         # order
         want = np.lexsort(tuple(coords[:, k] for k in range(ndim - 1, -1, -1)) + (clouds,))
@@ -203,3 +211,18 @@ def test_key_layout_preserves_order_and_offset_addition(mn_lib):
         assert spec.total_bits <= 63
 
     check()
+
+
+def test_status_word_decoding():
+    """Each bit of the device status word maps to its own exception and message."""
+    from minuet_b200 import engine
+    assert engine.decode_status(0) is None
+    box = engine.decode_status(engine.STATUS_KEY_BOX)
+    assert isinstance(box, RuntimeError) and "bounding box" in str(box)
+    tc = engine.decode_status(engine.STATUS_TC_TIMEOUT)
+    assert isinstance(tc, RuntimeError) and "tensor-core" in str(tc) and "invalid" in str(tc)
+    assert "bounding box" not in str(tc)
+    both = engine.decode_status(engine.STATUS_KEY_BOX | engine.STATUS_TC_TIMEOUT)
+    assert "tensor-core" in str(both) and "bounding box" in str(both)
+    wide = engine.decode_status(engine.STATUS_KEY_BITS)
+    assert isinstance(wide, NotImplementedError) and "63" in str(wide)
