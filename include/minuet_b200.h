@@ -44,9 +44,32 @@ typedef enum { MN_F32 = 0, MN_F16 = 1, MN_BF16 = 2 } mn_dtype;
 #define MN_MAX_NDIM 4
 #define MN_MAX_OFFSETS 128
 
+/* Control block: MN_CTRL_WORDS int32 words of DEVICE memory that the caller
+ * zeroes once and then keeps for as long as it uses the library on that
+ * stream.  Word MN_CTRL_STATUS collects MN_STATUS_* bits raised by kernels;
+ * the other words are the state of the grid-wide barrier that the cooperative
+ * kernels (mask emission, radix sort, unique) share, which is back to zero
+ * whenever no kernel is in flight.  Every parameter called `ctrl` or
+ * `status_dev` below points at such a block.  Calls whose kernels may overlap
+ * on the GPU (different streams) need a block each. */
+#define MN_CTRL_WORDS 64
+#define MN_CTRL_STATUS 0
+#define MN_CTRL_BARRIER_COUNT 8
+#define MN_CTRL_BARRIER_GEN 9
+#define MN_CTRL_LAST_BLOCK 10
+
+#define MN_STATUS_KEY_BOX 2       /* a coordinate fell outside the key box              */
+#define MN_STATUS_TC_TIMEOUT 4    /* a bounded barrier wait of a tensor-core kernel ran out */
+#define MN_STATUS_KEY_BITS 8      /* the bounding box needs more than 63 key bits       */
+#define MN_STATUS_GRID_TIMEOUT 16 /* a bounded grid-barrier wait ran out                 */
+
 /* How coordinates are packed into one 64-bit sort/search key:
  * key = cloud << cloud_shift | sum_k (c[k] - base[k]) << shift[k].
- * A plain host struct; pass it by pointer (host memory). */
+ * A plain struct; pass it by pointer (host memory).  Two ways to obtain one:
+ * mn_keyspec_make fills every field on the host from a bounding box that was
+ * read back; mn_keyspec_device derives the layout ON the device and leaves it
+ * there (no read-back): the host struct then only carries ndim, margin and
+ * device_copy, and every kernel reads the field layout through device_copy. */
 typedef struct {
   int32_t ndim;
   int32_t total_bits;       /* bits used by the key, <= 63                    */
@@ -57,6 +80,7 @@ typedef struct {
   int32_t bits[MN_MAX_NDIM];
   int64_t base[MN_MAX_NDIM];   /* coordinate that maps to field value 0       */
   int64_t extent[MN_MAX_NDIM]; /* largest legal field value                   */
+  const void *device_copy;     /* NULL, or a device mn_keyspec that overrides the layout above */
 } mn_keyspec;
 
 const char *mn_last_error(void);
@@ -90,6 +114,20 @@ mn_status mn_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,
  * MN_ERR_UNSUPPORTED when the box does not fit 63 bits. */
 mn_status mn_keyspec_make(const int32_t *minmax_host, int ndim,
                           int64_t num_clouds, int32_t margin, mn_keyspec *spec);
+
+/* Bounding box and key layout in one launch, entirely on the device: the layout
+ * is written to spec_dev (device memory, at least sizeof(mn_keyspec) bytes,
+ * 16-byte aligned, owned by the caller for as long as keys built from it are
+ * in use) and never read back; *spec (host) is filled with ndim, margin and
+ * device_copy = spec_dev and can be passed wherever a key spec is expected.
+ * A box that needs more than 63 key bits raises MN_STATUS_KEY_BITS in the
+ * status word.  Same role as mn_bbox + mn_keyspec_make without the
+ * device-to-host read between them (the reference blocks on that read,
+ * arg_sort_coodrinates.cu:286-287).  ctrl: the control block. */
+mn_status mn_keyspec_device(const int32_t *coords, int64_t n, int ndim,
+                            int64_t num_clouds, int32_t margin, void *spec_dev,
+                            mn_keyspec *spec, int32_t *ctrl, void *ws, size_t ws_bytes,
+                            void *stream);
 
 /* Pack coordinates into keys.  tstride (host, may be NULL) floors every
  * coordinate to a multiple of tstride[k] first, as
@@ -140,16 +178,18 @@ mn_status mn_unique_coordinates_static(const int32_t *coords, int64_t n, int ndi
 
 /* Fused target-coordinate build of a strided convolution
  * (KernelMapCache.get_target_coordinates, minuet/nn/convolutions.py:85-96):
- * floor to the target stride, sort, unique.  Outputs: unique_out int32
- * [n, ndim], keys_out uint64 [n] (sorted unique keys), out_batch_dims int64
- * [num_clouds+1] (only when batch_dims != NULL), count_dev int64 [1]. */
+ * floor to the target stride, sort, unique; two launches.  Outputs: unique_out
+ * int32 [n, ndim], keys_out uint64 [n] (sorted unique keys), and meta_out int64
+ * [num_clouds + 3] = { number of unique rows, batch_dims of the result
+ * [num_clouds + 1], copy of the status word }, so that one small read brings
+ * back everything the host needs.  batch_dims == NULL means one cloud
+ * (meta_out then has 4 entries).  ctrl: the control block. */
 mn_status mn_downsample_coordinates(const int32_t *coords, int64_t n, int ndim,
                                     const int64_t *batch_dims, int64_t num_clouds,
                                     const int32_t *tstride, const mn_keyspec *spec,
                                     int32_t *unique_out, uint64_t *keys_out,
-                                    int64_t *out_batch_dims, int64_t *count_dev,
-                                    int32_t *status_dev, void *ws, size_t ws_bytes,
-                                    void *stream);
+                                    int64_t *meta_out, int32_t *ctrl, void *ws,
+                                    size_t ws_bytes, void *stream);
 
 /* _C.cuda_query_sorted_index_with_offsets / _C.cuda_multi_query_...
  * (csrc/minuet/torch/cuda_sparse_convolution_mapping.cu:9-100) on packed keys:
@@ -176,14 +216,16 @@ mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int64_t O, int6
  * materialising the [O, T] kernel map.  target_keys == source_keys (same
  * pointer) selects the submanifold shortcut.  order_out int32 [O]
  * (order[p] = offset index at mask row p; identity when reorder == 0),
- * sizes_out int32 [O] (sizes of the mask rows, i.e. sorted). */
+ * sizes_out int32 [O + 1]: sizes of the mask rows (i.e. sorted), followed by a
+ * copy of the status word taken when the masks were written, so that one
+ * device-to-host copy brings back both.  ctrl: the control block. */
 mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
                               const uint64_t *target_keys, int64_t T,
                               const int32_t *offsets, int64_t O,
                               const mn_keyspec *spec, int reorder,
                               int32_t *source_masks_out, int32_t *target_masks_out,
-                              int32_t *order_out, int32_t *sizes_out, void *ws,
-                              size_t ws_bytes, void *stream);
+                              int32_t *order_out, int32_t *sizes_out, int32_t *ctrl,
+                              void *ws, size_t ws_bytes, void *stream);
 
 /* Upper bound of the workspace any Map-step entry point needs. */
 size_t mn_map_workspace_bytes(int64_t S, int64_t T, int64_t O);

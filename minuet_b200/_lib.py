@@ -14,6 +14,7 @@ MN_OK, MN_ERR_BAD_ARG, MN_ERR_UNSUPPORTED, MN_ERR_WORKSPACE, MN_ERR_CUDA, MN_ERR
 MN_F32, MN_F16, MN_BF16 = 0, 1, 2
 MN_MAX_NDIM = 4
 MN_MAX_OFFSETS = 128
+MN_CTRL_WORDS = 64
 
 c_i32p = ctypes.c_void_p
 c_ptr = ctypes.c_void_p
@@ -35,6 +36,7 @@ class KeySpec(ctypes.Structure):
         ("bits", ctypes.c_int32 * MN_MAX_NDIM),
         ("base", ctypes.c_int64 * MN_MAX_NDIM),
         ("extent", ctypes.c_int64 * MN_MAX_NDIM),
+        ("device_copy", ctypes.c_void_p),
     ]
 
 
@@ -56,7 +58,9 @@ PROTOTYPES = {
     "mn_unique_coordinates_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "mn_downsample_coordinates": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr,
                                           ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_ptr, c_ptr,
-                                          c_ptr, c_ptr, c_size, c_ptr]),
+                                          c_ptr, c_size, c_ptr]),
+    "mn_keyspec_device": (c_int, [c_ptr, c_i64, c_int, c_i64, ctypes.c_int32, c_ptr,
+                                  ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_size, c_ptr]),
     "mn_query_sorted_index_with_offsets": (c_int, [c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64,
                                                    ctypes.POINTER(KeySpec), c_ptr, c_ptr]),
     "mn_compute_kernel_map_sizes": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
@@ -64,7 +68,7 @@ PROTOTYPES = {
                                             c_size, c_ptr]),
     "mn_build_kernel_map": (c_int, [c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64,
                                     ctypes.POINTER(KeySpec), c_int, c_ptr, c_ptr, c_ptr, c_ptr,
-                                    c_ptr, c_size, c_ptr]),
+                                    c_ptr, c_ptr, c_size, c_ptr]),
     "mn_map_workspace_bytes": (c_size, [c_i64, c_i64, c_i64]),
     "mn_plan_buckets": (c_int, [c_ptr, c_i64, c_int, c_dbl, c_ptr, c_ptr, c_ptr]),
     "mn_conv_workspace_bytes": (c_size, [c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int,

@@ -15,6 +15,26 @@
 namespace mn {
 
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+constexpr int kMaxDevices = 64;
+constexpr int kMaxCoopBlocks = 1024;  // upper bound of a cooperative grid (workspace sizing)
+
+// Key layout as a kernel parameter: the host copy, or (when the layout was
+// derived on the device and never read back) a pointer to the device copy.
+struct SpecRef {
+  mn_keyspec host;
+  const mn_keyspec *dev;
+};
+inline SpecRef make_spec_ref(const mn_keyspec &s) {
+  SpecRef r;
+  r.host = s;
+  r.dev = static_cast<const mn_keyspec *>(s.device_copy);
+  return r;
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ const mn_keyspec &spec_of(const SpecRef &r) {
+  return r.dev != nullptr ? *r.dev : r.host;
+}
+#endif
 
 void set_error(const char *fmt, ...);
 
@@ -153,9 +173,18 @@ mn_status launch_pack(const int32_t *coords, int64_t n, int ndim,
                       const int64_t *batch_dims, int64_t num_clouds,
                       const int32_t *tstride, const mn_keyspec &spec,
                       uint64_t *keys_out, int32_t *status_dev, cudaStream_t st);
-mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
-                            int32_t *vals_tmp, bool iota_vals, int64_t n, int begin_bit,
-                            int end_bit, Workspace &ws, bool *result_in_tmp,
+// Coordinate rows a sort builds its keys from (floored to tstride when given).
+struct SortSource {
+  const int32_t *coords;
+  const int64_t *batch_dims;
+  int64_t num_clouds;
+  int ndim;
+  const int32_t *tstride;   // host, may be NULL
+};
+mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals, int32_t *vals_tmp,
+                            bool iota_vals, int64_t n, int begin_bit, int end_bit,
+                            const mn_keyspec &spec, const SortSource *source, int32_t *ctrl,
+                            int32_t *result_in_second_dev, Workspace &ws, bool *result_in_tmp,
                             cudaStream_t st);
 size_t radix_sort_workspace_bytes(int64_t n);
 

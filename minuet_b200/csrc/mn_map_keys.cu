@@ -9,7 +9,7 @@
 // This replaces the reference's per-cloud flattening
 // (csrc/minuet/cuda/kernels/flatten_coordinates.cuh:23-38) and its three-way
 // integer comparisons (csrc/minuet/common/functions.h:94-105).
-#include "mn_common.cuh"
+#include "mn_pack.cuh"
 
 #include <algorithm>
 #include <climits>
@@ -95,45 +95,6 @@ bbox_final_kernel(const int32_t *__restrict__ partial, int nblocks,
   if (lane == 0) minmax[which] = v;
 }
 
-__device__ __forceinline__ int floor_to(int c, int s) {
-  int q = c / s;
-  if ((c % s != 0) && (c < 0)) q--;
-  return q * s;
-}
-
-__device__ __forceinline__ int cloud_of(const int64_t *bd, int num_clouds, int64_t row) {
-  int lo = 0, hi = num_clouds;  // largest g with bd[g] <= row
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (bd[mid] <= row) lo = mid; else hi = mid;
-  }
-  return lo;
-}
-
-struct PackParams {
-  mn_keyspec spec;
-  int32_t tstride[4];
-  int32_t has_stride;
-};
-
-__device__ __forceinline__ uint64_t pack_one(const int (&c)[4], int ndim, uint64_t cloud,
-                                             const PackParams &p, bool &bad) {
-  uint64_t key = cloud << p.spec.cloud_shift;
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    if (k < ndim) {
-      int v = p.has_stride ? floor_to(c[k], p.tstride[k]) : c[k];
-      int64_t f = (int64_t)v - p.spec.base[k];
-      if (f < 0 || f > p.spec.extent[k]) {
-        bad = true;
-        f = f < 0 ? 0 : p.spec.extent[k];
-      }
-      key |= (uint64_t)f << p.spec.shift[k];
-    }
-  }
-  return key;
-}
-
 constexpr int kPackThreads = 256;
 constexpr int kMaxSmemClouds = 2048;
 
@@ -144,6 +105,7 @@ pack_kernel(const int32_t *__restrict__ coords, int64_t n, int ndim,
             const int64_t *__restrict__ batch_dims, int num_clouds,
             const __grid_constant__ PackParams p, uint64_t *__restrict__ keys,
             int32_t *__restrict__ status) {
+  const mn_keyspec &spec = spec_of(p.spec);
   __shared__ int64_t s_bd[kMaxSmemClouds + 1];
   const int64_t *bd = batch_dims;
   if (batch_dims != nullptr && num_clouds <= kMaxSmemClouds) {
@@ -171,10 +133,10 @@ pack_kernel(const int32_t *__restrict__ coords, int64_t n, int ndim,
         g2 = g0 == g3 ? g0 : cloud_of(bd, num_clouds, r + 2);
       }
       ulonglong2 lo, hi;
-      lo.x = pack_one(c0, 3, g0, p, bad);
-      lo.y = pack_one(c1, 3, g1, p, bad);
-      hi.x = pack_one(c2, 3, g2, p, bad);
-      hi.y = pack_one(c3, 3, g3, p, bad);
+      lo.x = pack_one(c0, 3, g0, spec, p, bad);
+      lo.y = pack_one(c1, 3, g1, spec, p, bad);
+      hi.x = pack_one(c2, 3, g2, spec, p, bad);
+      hi.y = pack_one(c3, 3, g3, spec, p, bad);
       ulonglong2 *kv = reinterpret_cast<ulonglong2 *>(keys + r);
       kv[0] = lo;
       kv[1] = hi;
@@ -182,23 +144,74 @@ pack_kernel(const int32_t *__restrict__ coords, int64_t n, int ndim,
     for (int64_t r = (nquad << 2) + gid; r < n; r += gsz) {
       int c[4] = {coords[r * 3], coords[r * 3 + 1], coords[r * 3 + 2], 0};
       uint64_t g = bd != nullptr ? cloud_of(bd, num_clouds, r) : 0;
-      keys[r] = pack_one(c, 3, g, p, bad);
+      keys[r] = pack_one(c, 3, g, spec, p, bad);
     }
   } else {
     for (int64_t r = gid; r < n; r += gsz) {
       int c[4] = {0, 0, 0, 0};
       for (int k = 0; k < ndim; k++) c[k] = coords[r * ndim + k];
       uint64_t g = bd != nullptr ? cloud_of(bd, num_clouds, r) : 0;
-      keys[r] = pack_one(c, ndim, g, p, bad);
+      keys[r] = pack_one(c, ndim, g, spec, p, bad);
     }
   }
-  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, 2);
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(status, MN_STATUS_KEY_BOX);
 }
 
-inline int bit_width_u64(uint64_t v) {
-  int b = 0;
-  while (v) { b++; v >>= 1; }
-  return b;
+// Last block to finish reduces the per-block boxes and derives the key layout
+// on the device (no read-back); the box also lands in minmax (may be NULL).
+__global__ void __launch_bounds__(kBBoxThreads)
+bbox_spec_kernel(const int32_t *__restrict__ a, int64_t na, int ndim, int64_t num_clouds,
+                 int32_t margin, int32_t *__restrict__ partial, mn_keyspec *__restrict__ spec_out,
+                 int32_t *__restrict__ ctrl) {
+  int mn_[4] = {INT_MAX, INT_MAX, INT_MAX, INT_MAX};
+  int mx_[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  scan_flat(a, na * ndim, ndim, mn_, mx_);
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    mn_[k] = __reduce_min_sync(0xffffffffu, mn_[k]);
+    mx_[k] = __reduce_max_sync(0xffffffffu, mx_[k]);
+  }
+  __shared__ int s[kBBoxThreads / 32][8];
+  __shared__ int s_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) { s[warp][k] = mn_[k]; s[warp][4 + k] = mx_[k]; }
+  }
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    int v = s[0][threadIdx.x];
+    for (int w = 1; w < kBBoxThreads / 32; w++)
+      v = threadIdx.x < 4 ? min(v, s[w][threadIdx.x]) : max(v, s[w][threadIdx.x]);
+    partial[blockIdx.x * 8 + threadIdx.x] = v;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(ctrl + MN_CTRL_LAST_BLOCK, 1);
+    s_last = ticket == (int)gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // 8 groups of 32 threads, one per output value
+  const int which = threadIdx.x >> 5;
+  int v = which < 4 ? INT_MAX : INT_MIN;
+  for (int b = lane; b < (int)gridDim.x; b += 32) {
+    const int p = __ldcg(partial + b * 8 + which);
+    v = which < 4 ? min(v, p) : max(v, p);
+  }
+  v = which < 4 ? __reduce_min_sync(0xffffffffu, v) : __reduce_max_sync(0xffffffffu, v);
+  __shared__ int32_t s_mm[8];
+  if (lane == 0) s_mm[which] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mn_keyspec spec;
+    if (!compute_keyspec(s_mm, ndim, num_clouds, margin, &spec))
+      atomicOr(ctrl + MN_CTRL_STATUS, MN_STATUS_KEY_BITS);
+    *spec_out = spec;
+    ctrl[MN_CTRL_LAST_BLOCK] = 0;   // ready for the next launch
+  }
 }
 
 }  // namespace
@@ -221,7 +234,7 @@ mn_status launch_pack(const int32_t *coords, int64_t n, int ndim,
                       uint64_t *keys_out, int32_t *status_dev, cudaStream_t st) {
   if (n == 0) return MN_OK;
   PackParams p;
-  p.spec = spec;
+  p.spec = make_spec_ref(spec);
   p.has_stride = 0;
   for (int k = 0; k < 4; k++) p.tstride[k] = 1;
   if (tstride != nullptr) {
@@ -249,25 +262,37 @@ extern "C" mn_status mn_keyspec_make(const int32_t *minmax_host, int ndim,
   MN_CHECK_ARG(margin >= 0, "keyspec_make: negative margin");
   MN_CHECK_ARG(num_clouds >= 1, "keyspec_make: num_clouds must be >= 1");
   *spec = mn_keyspec{};
-  spec->ndim = ndim;
-  spec->margin = margin;
-  int shift = 0;
-  for (int k = ndim - 1; k >= 0; k--) {
-    int64_t lo = minmax_host[k], hi = minmax_host[4 + k];
-    if (lo > hi) { lo = 0; hi = 0; }  // empty input
-    spec->base[k] = lo - margin;
-    spec->extent[k] = (hi + margin) - spec->base[k];
-    spec->bits[k] = std::max(1, bit_width_u64((uint64_t)spec->extent[k]));
-    spec->shift[k] = shift;
-    shift += spec->bits[k];
-  }
-  spec->cloud_shift = shift;
-  spec->cloud_bits = bit_width_u64((uint64_t)(num_clouds - 1));
-  spec->total_bits = shift + spec->cloud_bits;
-  if (spec->total_bits > 63) {
+  if (!compute_keyspec(minmax_host, ndim, num_clouds, margin, spec)) {
     set_error("keyspec_make: bounding box needs %d key bits (> 63); coordinate "
               "ranges this large are not supported", spec->total_bits);
     return MN_ERR_UNSUPPORTED;
   }
+  return MN_OK;
+}
+
+extern "C" mn_status mn_keyspec_device(const int32_t *coords, int64_t n, int ndim,
+                                       int64_t num_clouds, int32_t margin, void *spec_dev,
+                                       mn_keyspec *spec, int32_t *ctrl, void *ws_ptr,
+                                       size_t ws_bytes, void *stream) {
+  using namespace mn;
+  MN_CHECK_ARG(ndim >= 1 && ndim <= MN_MAX_NDIM, "keyspec_device: ndim %d not in 1..4", ndim);
+  MN_CHECK_ARG(n >= 0 && margin >= 0 && num_clouds >= 1, "keyspec_device: bad arguments");
+  MN_CHECK_ARG(spec_dev != nullptr && spec != nullptr && ctrl != nullptr && (n == 0 || coords != nullptr),
+               "keyspec_device: null pointer");
+  MN_CHECK_ARG((reinterpret_cast<uintptr_t>(spec_dev) & 15) == 0, "keyspec_device: spec_dev must be 16-byte aligned");
+  Workspace ws(ws_ptr, ws_bytes);
+  int32_t *partial = ws.take<int32_t>((size_t)kBBoxMaxBlocks * 8);
+  MN_CHECK_WS(ws);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t elems = n * ndim;
+  const int blocks = (int)std::min<int64_t>(kBBoxMaxBlocks, std::max<int64_t>(1, div_up(elems, kBBoxThreads * 16)));
+  MN_LAUNCH("bbox_spec_kernel", st,
+            bbox_spec_kernel<<<blocks, kBBoxThreads, 0, st>>>(
+                coords, n, ndim, num_clouds, margin, partial, static_cast<mn_keyspec *>(spec_dev), ctrl));
+  *spec = mn_keyspec{};
+  spec->ndim = ndim;
+  spec->margin = margin;
+  spec->total_bits = -1;   // only known on the device
+  spec->device_copy = spec_dev;
   return MN_OK;
 }

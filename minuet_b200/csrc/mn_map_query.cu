@@ -8,21 +8,35 @@
 // follow as a reduce-by-key, a torch.sort, a DeviceSelect, two memsets and a
 // scatter kernel (functions/scan.cu:221-365, minuet/nn/convolutions.py:156-170).
 //
-// Here both traversals live in one row-tile-stationary kernel over packed
-// 64-bit keys.  A block owns 1024 consecutive rows (targets) and, for every
-// group of offsets that differ only in the last dimension, (1) finds the window
-// of the sorted table (sources) that can match the tile with a warp-cooperative
-// 32-ary ballot search, (2) stages that window in shared memory (adjacent groups
-// share one staging pass when their union fits) and (3) lets every row do ONE
-// binary search per group followed by a short forward walk for the group's
-// other offsets, because inside a group the queries of a row are ascending.
-// The kernel either writes kernel-map rows or, for the fused build, a 32-bit
-// word of per-offset hit bits per row plus per-tile hit counts; ranks and both
-// masks are then produced by a scan over tile counts and one streaming kernel
-// that writes every mask element exactly once (no memset, no select, no
-// scatter).  For submanifold maps (sources == targets, symmetric offsets) the
-// source mask of offset o is read off the hit bits of the mirrored offset.
-#include "mn_common.cuh"
+// Here the map build is two launches over packed 64-bit keys.
+//
+// search_kernel: a block owns 512 consecutive rows (targets).  Two
+// warp-cooperative 32-ary ballot searches find the window of the sorted table
+// (sources) that can match the tile over all offsets; the window is staged in
+// shared memory as a hash set of CELLS (32 consecutive values of the last
+// dimension -> {cell id, 32-bit occupancy}).  Every key is entered twice, once
+// in the cells aligned at 0 and once in the cells aligned at 16, so that any
+// strip of up to 17 consecutive last-dimension values lies inside ONE cell of
+// one of the two families: offsets that differ only in the last dimension (a
+// "group", split so that its span is at most 16) are answered by a single
+// two-bucket probe per row.  Tiles whose window does not fit the hash are
+// processed group range by group range, and ranges that still do not fit fall
+// back to binary search in global memory.  The kernel writes kernel-map rows
+// or, for the fused build, one 32-bit word of per-offset hit bits per row.
+//
+// emit_masks_kernel (cooperative launch, all blocks resident): every block
+// owns a contiguous range of 512-row tiles.  Phase 1 counts the hits per
+// offset of its range (32x32 bit-matrix transposes turn 32 hit words into 32
+// per-offset row masks); one grid barrier later every block knows its rank
+// offset per offset and the total sizes, hence the stable size order; phase 2
+// turns each tile's row masks into ranks in a shared-memory staging tile
+// (pre-filled with -1, only the hits are patched) and writes every mask row
+// segment with one bulk asynchronous copy (cp.async.bulk shared -> global),
+// whatever the alignment of the row pitch.  No memset, no select, no scatter,
+// no separate scan kernel.  For submanifold maps (sources == targets,
+// symmetric offsets) the source mask of offset o is read off the hit bits of
+// the mirrored offset.
+#include "mn_grid.cuh"
 
 #include <algorithm>
 #include <vector>
@@ -31,18 +45,17 @@ namespace mn {
 
 namespace {
 
-#ifndef MN_QTHREADS
-#define MN_QTHREADS 128
-#endif
-constexpr int kQThreads = MN_QTHREADS;
+constexpr int kQThreads = 256;
 constexpr int kQWarps = kQThreads / 32;
-constexpr int kQRows = 4;                    // rows per thread
+constexpr int kQRows = 2;                    // rows per thread
 constexpr int kQTile = kQThreads * kQRows;   // 512 rows per block
-constexpr int kQWindow = 2048;               // table keys staged per pass
-constexpr int kQHash = 2048;                 // slots of the shared-memory hash of cells
+constexpr int kQSlots = 4096;                // hash slots of 8 bytes; two per bucket
+constexpr int kQBuckets = kQSlots / 2;
+constexpr int kQMaxWindow = 1280;            // table keys per hashed stage (two entries each)
+constexpr int kQMaxSpan = 16;                // last-dimension span of one group
+constexpr uint32_t kQPad = 64;               // relative keys start at kQPad
 constexpr uint32_t kHashEmpty = 0xffffffffu;
-constexpr uint32_t kQPad = 4096;             // slack below/above the window in relative keys
-constexpr uint64_t kKeyInf = ~0ull;
+constexpr uint64_t kRelLimit = 0xffffffffull - 4ull * kQPad;
 
 __device__ __forceinline__ unsigned lanemask_lt() {
   unsigned m;
@@ -51,12 +64,12 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 }
 
 // Warp-cooperative 32-ary search in global memory: lower bound (first index
-// with t[i] >= q) or upper bound (first index with t[i] > q).  Every lane
-// probes one pivot per round, a ballot narrows the range 32-fold; ~4 rounds for
-// half a million keys.  All 32 lanes must call with identical arguments.
-__device__ __forceinline__ int64_t warp_bound(const uint64_t *__restrict__ t, int64_t n,
-                                              uint64_t q, bool upper, int lane) {
-  int64_t lo = 0, hi = n;
+// with t[i] >= q) or upper bound (first index with t[i] > q) inside [lo, hi).
+// Every lane probes one pivot per round, a ballot narrows the range 32-fold;
+// ~4 rounds for half a million keys.  All 32 lanes must call with identical
+// arguments.
+__device__ __forceinline__ int64_t warp_bound(const uint64_t *__restrict__ t, int64_t lo,
+                                              int64_t hi, uint64_t q, bool upper, int lane) {
   for (int round = 0; round < 16; round++) {
     const int64_t len = hi - lo;
     if (len <= 0) break;
@@ -81,121 +94,104 @@ struct SearchArgs {
   const uint64_t *table;
   int64_t n_rows;
   int64_t n_table;
-  int32_t *kernel_map;   // kMap:  [O, n_rows]
-  uint32_t *hit_words;   // kBits: [n_rows]
-  int32_t *tile_counts;  // kBits: [O, n_tiles]
+  int32_t *kernel_map;     // kMap:  [O, n_rows]
+  uint32_t *hit_words;     // kBits / kBitsRev: [n_rows]
+  uint32_t *table_words;   // kBitsRev: [n_table], zeroed; bit o of entry s is set when row t hits s
   int32_t n_tiles;
-  int32_t shift[4];
-  int32_t fast_ok;       // every last-dimension offset is within +-kQPad
 };
 
 // One launch can serve two searches (e.g. targets->sources and sources->targets).
 struct SearchPair {
   SearchArgs a[2];
   OffsetTable tab[2];
+  SpecRef spec;
   int32_t tiles0;   // blocks of the first search
 };
 
-enum SearchMode { kMap = 0, kBits = 1 };
-
-// lower bound of q in win[a, b); trip count depends only on b - a (uniform)
-template <typename K>
-__device__ __forceinline__ int lower_bound_win(const K *win, int a, int b, K q) {
-  int base = a, len = b - a;
-  while (len > 1) {
-    const int half = len >> 1;
-    base = (win[base + half - 1] < q) ? base + half : base;
-    len -= half;
-  }
-  return (len == 1 && win[base] < q) ? base + 1 : base;
-}
-
-// One result of one (row, offset): either a kernel-map entry or a hit bit.
-template <int kMode>
-__device__ __forceinline__ void emit(const SearchArgs &a, int o, int64_t row, bool vec_ok,
-                                     const bool (&live)[kQRows], const int32_t (&idx)[kQRows],
-                                     uint32_t (&bits)[kQRows]) {
-  if (kMode == kMap) {
-    int32_t *dst = a.kernel_map + (int64_t)o * a.n_rows + row;
-    if (vec_ok && live[kQRows - 1]) {
-      *reinterpret_cast<int4 *>(dst) = make_int4(idx[0], idx[1], idx[2], idx[3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < kQRows; j++) if (live[j]) dst[j] = idx[j];
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < kQRows; j++) bits[j] |= (idx[j] >= 0 ? 1u : 0u) << o;
-  }
-}
-
-// The hash set is kQHash / 2 buckets of two {cell, mask} slots (16 bytes).  Inserts
-// fill slot 0 of a bucket first, then slot 1, then move on to the next bucket, so a
-// bucket whose slot 1 is empty never overflowed.
-constexpr int kQBuckets = kQHash / 2;
+// kMap: kernel-map rows; kBits: per-row hit words; kBitsRev: hit words of the rows
+// and, through atomicOr at the matched table position, of the table entries
+// (one search then serves both masks of a map whose two sides differ).
+enum SearchMode { kMap = 0, kBits = 1, kBitsRev = 2 };
 
 __device__ __forceinline__ uint32_t hash_bucket(uint32_t k) {
-  return (k * 0x9E3779B1u) >> 22;  // top 10 bits: 1024 buckets
+  return (k * 0x9E3779B1u) >> 21;  // top 11 bits: 2048 buckets
 }
 
-// Occupancy mask of cell c (0 when the cell is absent) and the slot that holds it.
-// The home bucket and its successor are read up front with two 16-byte loads; only
-// a cell pushed further than that (rare at these load factors) takes the loop, so
-// the lanes of a warp stay converged.
+// Occupancy mask of cell key c (0 when absent) and the slot that holds it.  The
+// home bucket and its successor are read up front with two 16-byte loads and
+// compared without branches; only a cell pushed further than that (rare at
+// these load factors) takes the loop, so the lanes of a warp stay converged.
+// Inserts fill slot 0 of a bucket first, then slot 1, then move on to the next
+// bucket, so a bucket whose slot 1 is empty never overflowed.
+template <bool kWantSlot>
 __device__ __forceinline__ uint32_t find_cell(const uint2 *slots, uint32_t c, uint32_t *slot) {
   const uint4 *buckets = reinterpret_cast<const uint4 *>(slots);
   uint32_t b = hash_bucket(c);
   const uint4 a0 = buckets[b];
   const uint32_t b1 = (b + 1) & (kQBuckets - 1);
   const uint4 a1 = buckets[b1];
-  if (a0.x == c) { *slot = 2 * b; return a0.y; }
-  if (a0.z == c) { *slot = 2 * b + 1; return a0.w; }
-  if (a0.z == kHashEmpty) { *slot = 0; return 0u; }
-  if (a1.x == c) { *slot = 2 * b1; return a1.y; }
-  if (a1.z == c) { *slot = 2 * b1 + 1; return a1.w; }
-  if (a1.z == kHashEmpty) { *slot = 0; return 0u; }
-  b = b1;
-  for (int probe = 2; probe < kQBuckets; probe++) {
-    b = (b + 1) & (kQBuckets - 1);
-    const uint4 v = buckets[b];
-    if (v.x == c) { *slot = 2 * b; return v.y; }
-    if (v.z == c) { *slot = 2 * b + 1; return v.w; }
-    if (v.z == kHashEmpty) break;
+  uint32_t m = a0.x == c ? a0.y : 0u;
+  m = a0.z == c ? a0.w : m;
+  m = a1.x == c ? a1.y : m;
+  m = a1.z == c ? a1.w : m;
+  if (kWantSlot) {
+    uint32_t h = 2 * b;
+    h = a0.z == c ? 2 * b + 1 : h;
+    h = a1.x == c ? 2 * b1 : h;
+    h = a1.z == c ? 2 * b1 + 1 : h;
+    *slot = h;
   }
-  *slot = 0;
-  return 0u;
+  if (m == 0u && a0.z != kHashEmpty && a1.z != kHashEmpty) {   // both buckets full, no match
+    b = b1;
+    for (int probe = 2; probe < kQBuckets; probe++) {
+      b = (b + 1) & (kQBuckets - 1);
+      const uint4 v = buckets[b];
+      if (v.x == c) { if (kWantSlot) *slot = 2 * b; return v.y; }
+      if (v.z == c) { if (kWantSlot) *slot = 2 * b + 1; return v.w; }
+      if (v.z == kHashEmpty) break;
+    }
+  }
+  return m;
 }
 
-// A block owns 512 consecutive rows, a thread 4 consecutive rows.
-//
-// Fast path (the table window that can match the tile, over ALL offsets, holds
-// at most kQWindow keys spanning less than 2^32 - 4*kQPad, and no offset moves
-// the last dimension by more than kQPad): two warp-cooperative 32-ary searches
-// find the window of the sorted table.  The block stages that sorted block in
-// shared memory as a hash set of CELLS: 32 consecutive values of the last
-// dimension share one slot {cell id, 32-bit occupancy mask} (plus the position
-// of the cell's first key when kernel-map entries are wanted; the rest follows
-// by popcount because the table is sorted).  The offsets of a group differ only
-// in the last dimension, so one probe usually answers the whole group, and the
-// probes of a thread do not depend on each other.
-// General path (huge or wide windows): per-group windows, 64-bit keys, staged
-// when they fit, binary-searched in global memory otherwise.
+__device__ __forceinline__ uint32_t insert_cell(uint2 *slots, uint32_t c, uint32_t bit) {
+  uint32_t b = hash_bucket(c), h = 0;
+  for (int probe = 0; probe < kQBuckets; probe++) {
+    uint32_t old = atomicCAS(&slots[2 * b].x, kHashEmpty, c);
+    if (old == kHashEmpty || old == c) { h = 2 * b; break; }
+    old = atomicCAS(&slots[2 * b + 1].x, kHashEmpty, c);
+    if (old == kHashEmpty || old == c) { h = 2 * b + 1; break; }
+    b = (b + 1) & (kQBuckets - 1);
+  }
+  atomicOr(&slots[h].y, 1u << bit);
+  return h;
+}
+
+// Cell key of relative key k in family 0 (cells aligned at 0) or 1 (aligned at 16).
+__device__ __forceinline__ uint32_t cell_key(uint32_t k, uint32_t family) {
+  return (((k + 16u * family) >> 5) << 1) | family;
+}
+
 template <int kMode>
-__global__ void __launch_bounds__(kQThreads, 8)
+__global__ void __launch_bounds__(kQThreads, kMode == kBits ? 5 : 4)
 search_kernel(const __grid_constant__ SearchPair sp) {
+  constexpr bool kPos = kMode != kBits;   // table positions are needed
   // blocks [0, tiles0) serve direction 0, the rest direction 1 (rows and table swapped)
   const int dir = (int)blockIdx.x >= sp.tiles0 ? 1 : 0;
   const int bid = (int)blockIdx.x - dir * sp.tiles0;
   const SearchArgs &a = sp.a[dir];
   const OffsetTable &tab = sp.tab[dir];
-  __shared__ __align__(16) uint64_t s_win[kQWindow + 2];          // hash slots / general path
-  __shared__ uint16_t s_hpos[kMode == kMap ? kQHash : 1];         // first position of a cell
+  const mn_keyspec &spec = spec_of(sp.spec);
+  __shared__ __align__(16) uint2 s_slots[kQSlots];
+  __shared__ uint16_t s_hpos[kPos ? kQSlots : 2];   // first position of a cell
   __shared__ int64_t s_delta[MN_MAX_OFFSETS];
+  __shared__ int64_t s_gdelta[MN_MAX_OFFSETS];       // per group: delta of its first member
+  __shared__ uint32_t s_gmeta[MN_MAX_OFFSETS];       // span | first offset << 8 | members << 16 | compact << 24
   __shared__ int64_t s_glo[MN_MAX_OFFSETS], s_ghi[MN_MAX_OFFSETS];
-  __shared__ int32_t s_stage_gbeg[MN_MAX_OFFSETS + 1];
-  __shared__ int32_t s_counts[MN_MAX_OFFSETS];
+  __shared__ int64_t s_slo[MN_MAX_OFFSETS], s_shi[MN_MAX_OFFSETS];
+  __shared__ uint8_t s_stage_gbeg[MN_MAX_OFFSETS + 1];
   __shared__ int32_t s_num_stages;
-  static_assert(kQHash <= kQWindow + 2, "the hash slots live in s_win");
+  __shared__ int64_t s_union[2];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int O = tab.num_offsets, G = tab.num_groups;
@@ -206,19 +202,31 @@ search_kernel(const __grid_constant__ SearchPair sp) {
 
   for (int o = tid; o < O; o += kQThreads) {
     int64_t d = 0;
-    for (int k = 0; k < tab.ndim; k++) d += (int64_t)tab.off[o][k] * ((int64_t)1 << a.shift[k]);
+    for (int k = 0; k < tab.ndim; k++) d += (int64_t)tab.off[o][k] * ((int64_t)1 << spec.shift[k]);
     s_delta[o] = d;
-    s_counts[o] = 0;
+  }
+  for (int g = tid; g < G; g += kQThreads) {
+    const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+    const int o_first = tab.member[mb];
+    int64_t d = 0;
+    for (int k = 0; k < tab.ndim; k++) d += (int64_t)tab.off[o_first][k] * ((int64_t)1 << spec.shift[k]);
+    s_gdelta[g] = d;
+    // compact: member i is offset o_first + i and sits i values further along the last dimension
+    bool compact = true;
+    for (int m = mb; m < me; m++)
+      compact &= tab.member[m] == o_first + (m - mb) &&
+                 tab.off[tab.member[m]][last] - tab.off[o_first][last] == m - mb;
+    const int span = tab.off[tab.member[me - 1]][last] - tab.off[o_first][last];
+    s_gmeta[g] = (uint32_t)span | ((uint32_t)o_first << 8) | ((uint32_t)(me - mb) << 16) |
+                 ((compact ? 1u : 0u) << 24);
   }
 
   uint64_t key[kQRows];
   bool live[kQRows];
   if (tid * kQRows + kQRows <= tile_rows && (reinterpret_cast<uintptr_t>(a.rows) & 15) == 0) {
-    const ulonglong2 v0 = __ldg(reinterpret_cast<const ulonglong2 *>(a.rows + row0));
-    const ulonglong2 v1 = __ldg(reinterpret_cast<const ulonglong2 *>(a.rows + row0) + 1);
-    key[0] = v0.x; key[1] = v0.y; key[2] = v1.x; key[3] = v1.y;
-#pragma unroll
-    for (int j = 0; j < kQRows; j++) live[j] = true;
+    const ulonglong2 v = __ldg(reinterpret_cast<const ulonglong2 *>(a.rows + row0));
+    key[0] = v.x; key[1] = v.y;
+    live[0] = live[1] = true;
   } else {
 #pragma unroll
     for (int j = 0; j < kQRows; j++) {
@@ -228,170 +236,164 @@ search_kernel(const __grid_constant__ SearchPair sp) {
   }
   const uint64_t kfirst = __ldg(a.rows + tile0);
   const uint64_t klast = __ldg(a.rows + tile0 + tile_rows - 1);
-  const bool vec_ok = kMode == kMap && (a.n_rows & 3) == 0 &&
-                      (reinterpret_cast<uintptr_t>(a.kernel_map) & 15) == 0;
   __syncthreads();
 
-  // window of the table over all offsets: groups are ordered by delta
-  __shared__ int64_t s_union[2];
+  // window of the table over all offsets: members are ordered by delta
   if (warp < 2) {
     const uint64_t q = warp == 0 ? kfirst + (uint64_t)s_delta[tab.member[0]]
                                  : klast + (uint64_t)s_delta[tab.member[O - 1]];
-    const int64_t r = warp_bound(a.table, a.n_table, q, warp == 1, lane);
+    const int64_t r = warp_bound(a.table, 0, a.n_table, q, warp == 1, lane);
     if (lane == 0) s_union[warp] = r;
   }
-  uint2 *slots = reinterpret_cast<uint2 *>(s_win);
-  for (int i = tid; i < kQHash; i += kQThreads) slots[i] = make_uint2(kHashEmpty, 0u);
   __syncthreads();
-  const int64_t ulo = s_union[0], uhi = max(s_union[0], s_union[1]);
-  const int wn = (int)min(uhi - ulo, (int64_t)kQWindow + 1);
-  bool fast = a.fast_ok && uhi - ulo <= kQWindow;
-  uint64_t base = 0;
-  if (fast && wn > 0) {
-    base = __ldg(a.table + ulo);
-    fast = __ldg(a.table + uhi - 1) - base < 0xffffffffull - 4ull * kQPad;
-  }
-
-  uint32_t bits[kQRows] = {0u, 0u, 0u, 0u};
-  if (fast) {
-    // keys relative to base - kQPad, so that "query below the window" needs no test
-    for (int w = tid; w < wn; w += kQThreads) {
-      const uint64_t tk = __ldg(a.table + ulo + w);
-      const uint32_t k = (uint32_t)(tk - base) + kQPad;
-      const uint32_t cell = k >> 5;
-      uint32_t b = hash_bucket(cell), h = 0;
-      for (int probe = 0; probe < kQBuckets; probe++) {
-        uint32_t old = atomicCAS(&slots[2 * b].x, kHashEmpty, cell);
-        if (old == kHashEmpty || old == cell) { h = 2 * b; break; }
-        old = atomicCAS(&slots[2 * b + 1].x, kHashEmpty, cell);
-        if (old == kHashEmpty || old == cell) { h = 2 * b + 1; break; }
-        b = (b + 1) & (kQBuckets - 1);
+  {
+    const int64_t ulo = s_union[0], uhi = max(s_union[0], s_union[1]);
+    bool one_stage = uhi - ulo <= kQMaxWindow;
+    if (one_stage && uhi > ulo)
+      one_stage = __ldg(a.table + uhi - 1) - __ldg(a.table + ulo) < kRelLimit;
+    if (one_stage) {
+      if (tid == 0) {
+        s_num_stages = 1;
+        s_stage_gbeg[0] = 0;
+        s_stage_gbeg[1] = (uint8_t)G;
+        s_slo[0] = ulo;
+        s_shi[0] = uhi;
       }
-      atomicOr(&slots[h].y, 1u << (k & 31));
-      if (kMode == kMap) {
-        // the table is sorted: exactly one key of a cell has a predecessor in another cell
-        const bool first = w == 0 ||
-            (((uint32_t)(__ldg(a.table + ulo + w - 1) - base) + kQPad) >> 5) != cell;
-        if (first) s_hpos[h] = (uint16_t)w;
-      }
-    }
-    __syncthreads();
-    int64_t rel[kQRows];
-#pragma unroll
-    for (int j = 0; j < kQRows; j++) rel[j] = (int64_t)(key[j] - base) + kQPad;
-    for (int g = 0; g < G; g++) {
-      const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
-      const int o_first = tab.member[mb];
-      const int e_first = tab.off[o_first][last];
-      const int e_span = tab.off[tab.member[me - 1]][last] - e_first;  // >= 0, members ascend
-      const int64_t dg = s_delta[o_first] - e_first;  // the last dimension sits at bit 0
-      // Per row: the 64 consecutive last-dimension values starting at the cell of
-      // the group's first query, as one 64-bit occupancy mask (low cell | high cell).
-      uint32_t sh[kQRows], mlo[kQRows], mhi[kQRows], slo[kQRows], shi[kQRows];
-      uint32_t c0[kQRows];
-      bool ok[kQRows];
-#pragma unroll
-      for (int j = 0; j < kQRows; j++) {
-        const uint64_t t = (uint64_t)(rel[j] + dg);
-        ok[j] = live[j] && t < 0xffffffffull - 2ull * kQPad;  // t +- kQPad stays inside 32 bits
-        const uint32_t q0 = (uint32_t)t + (uint32_t)e_first;
-        c0[j] = q0 >> 5;
-        sh[j] = q0 & 31;
-      }
-#pragma unroll
-      for (int j = 0; j < kQRows; j++) {
-        const uint32_t m0 = find_cell(slots, c0[j], &slo[j]);
-        mlo[j] = ok[j] ? m0 : 0u;
-        mhi[j] = 0u;
-        shi[j] = 0u;
-        if (ok[j] && (int)sh[j] + e_span > 31)   // the group reaches into the next cell
-          mhi[j] = find_cell(slots, c0[j] + 1, &shi[j]);
-      }
-      if (kMode == kBits && e_span <= 32) {
-        // hit bits only: every offset of the group is one bit of the row's 64-value
-        // strip, extracted without branches so that the warp stays converged
-        uint64_t strip[kQRows];
-#pragma unroll
-        for (int j = 0; j < kQRows; j++)
-          strip[j] = (((uint64_t)mhi[j] << 32) | mlo[j]) >> sh[j];
-        for (int m = mb; m < me; m++) {
-          const int o = tab.member[m];
-          const int de = tab.off[o][last] - e_first;   // 0..32
-#pragma unroll
-          for (int j = 0; j < kQRows; j++)
-            bits[j] |= ((uint32_t)(strip[j] >> de) & 1u) << o;
-        }
-        continue;
-      }
-      for (int m = mb; m < me; m++) {
-        const int o = tab.member[m];
-        const int de = tab.off[o][last] - e_first;
-        int32_t idx[kQRows];
-#pragma unroll
-        for (int j = 0; j < kQRows; j++) {
-          const int b = (int)sh[j] + de;   // bit index into the 64-value strip (or beyond)
-          idx[j] = -1;
-          if (b < 32) {
-            if ((mlo[j] >> b) & 1u)
-              idx[j] = kMode == kMap
-                  ? (int32_t)(ulo + s_hpos[slo[j]] + __popc(mlo[j] & ((1u << b) - 1u))) : 0;
-          } else if (b < 64) {
-            if ((mhi[j] >> (b - 32)) & 1u)
-              idx[j] = kMode == kMap
-                  ? (int32_t)(ulo + s_hpos[shi[j]] + __popc(mhi[j] & ((1u << (b - 32)) - 1u))) : 0;
-          } else if (ok[j]) {   // offsets more than 63 apart inside one group: probe per member
-            const uint32_t q = (c0[j] << 5) + (uint32_t)b;
-            const uint32_t c = q >> 5;
-            uint32_t h = 0;
-            const uint32_t um = find_cell(slots, c, &h);
-            if ((um >> (q & 31)) & 1u)
-              idx[j] = kMode == kMap
-                  ? (int32_t)(ulo + s_hpos[h] + __popc(um & ((1u << (q & 31)) - 1u))) : 0;
-          }
-        }
-        emit<kMode>(a, o, row0, vec_ok, live, idx, bits);
-      }
-    }
-  } else {
-    // ---- general path -----------------------------------------------------
-    for (int g = warp; g < G; g += kQWarps) {
-      const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
-      const uint64_t qlo = kfirst + (uint64_t)s_delta[tab.member[mb]];
-      const uint64_t qhi = klast + (uint64_t)s_delta[tab.member[me - 1]];
-      const int64_t lo = warp_bound(a.table, a.n_table, qlo, false, lane);
-      const int64_t hi = warp_bound(a.table, a.n_table, qhi, true, lane);
-      if (lane == 0) { s_glo[g] = lo; s_ghi[g] = max(lo, hi); }
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int ns = 0, g = 0;
-      while (g < G) {
-        s_stage_gbeg[ns++] = g;
-        int64_t lo = s_glo[g], hi = s_ghi[g];
-        g++;
-        if (hi - lo <= kQWindow) {
-          while (g < G) {
-            const int64_t nlo = min(lo, s_glo[g]), nhi = max(hi, s_ghi[g]);
-            if (nhi - nlo > kQWindow) break;
-            lo = nlo; hi = nhi; g++;
-          }
-        }
-      }
-      s_stage_gbeg[ns] = G;
-      s_num_stages = ns;
-    }
-    __syncthreads();
-    const int num_stages = s_num_stages;
-    for (int st = 0; st < num_stages; st++) {
-      const int gb = s_stage_gbeg[st], ge = s_stage_gbeg[st + 1];
-      int64_t lo = s_glo[gb], hi = s_ghi[gb];
-      for (int g = gb + 1; g < ge; g++) { lo = min(lo, s_glo[g]); hi = max(hi, s_ghi[g]); }
-      const int64_t n = hi - lo;
-      const bool staged = n <= kQWindow;
-      if (staged) {
-        for (int i = tid; i < (int)n; i += kQThreads) s_win[i] = __ldg(a.table + lo + i);
+    } else {
+      // per-group windows inside the union window, then consecutive groups are
+      // merged into stages for as long as their joint window fits the hash
+      for (int g = warp; g < G; g += kQWarps) {
+        const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
+        const uint64_t qlo = kfirst + (uint64_t)s_delta[tab.member[mb]];
+        const uint64_t qhi = klast + (uint64_t)s_delta[tab.member[me - 1]];
+        const int64_t lo = warp_bound(a.table, ulo, uhi, qlo, false, lane);
+        const int64_t hi = warp_bound(a.table, ulo, uhi, qhi, true, lane);
+        if (lane == 0) { s_glo[g] = lo; s_ghi[g] = max(lo, hi); }
       }
       __syncthreads();
+      if (tid == 0) {
+        int ns = 0, g = 0;
+        while (g < G) {
+          s_stage_gbeg[ns] = (uint8_t)g;
+          int64_t lo = s_glo[g], hi = s_ghi[g];
+          g++;
+          if (hi - lo <= kQMaxWindow) {
+            while (g < G) {
+              const int64_t nlo = min(lo, s_glo[g]), nhi = max(hi, s_ghi[g]);
+              if (nhi - nlo > kQMaxWindow) break;
+              lo = nlo; hi = nhi; g++;
+            }
+          }
+          s_slo[ns] = lo;
+          s_shi[ns] = hi;
+          ns++;
+        }
+        s_stage_gbeg[ns] = (uint8_t)G;
+        s_num_stages = ns;
+      }
+    }
+  }
+  __syncthreads();
+
+  uint32_t bits[kQRows] = {0u, 0u};
+  const bool vec_ok = kMode == kMap && (a.n_rows & 1) == 0 &&
+                      (reinterpret_cast<uintptr_t>(a.kernel_map) & 7) == 0 && live[kQRows - 1];
+  const int num_stages = s_num_stages;
+  for (int st = 0; st < num_stages; st++) {
+    const int gb = s_stage_gbeg[st], ge = s_stage_gbeg[st + 1];
+    const int64_t lo = s_slo[st], hi = s_shi[st];
+    const int wn = (int)min(hi - lo, (int64_t)kQMaxWindow + 1);
+    bool hashed = hi - lo <= kQMaxWindow;
+    uint64_t base = 0;
+    if (hashed && wn > 0) {
+      base = __ldg(a.table + lo);
+      hashed = __ldg(a.table + hi - 1) - base < kRelLimit;
+    }
+    if (hashed) {
+      {
+        uint4 *clear = reinterpret_cast<uint4 *>(s_slots);
+        for (int i = tid; i < kQSlots / 2; i += kQThreads)
+          clear[i] = make_uint4(kHashEmpty, 0u, kHashEmpty, 0u);
+      }
+      __syncthreads();
+      // relative keys start at kQPad, so that a query below the window stays non-negative
+      for (int w = tid; w < wn; w += kQThreads) {
+        const uint32_t k = (uint32_t)(__ldg(a.table + lo + w) - base) + kQPad;
+        const uint32_t h0 = insert_cell(s_slots, cell_key(k, 0u), k & 31u);
+        const uint32_t h1 = insert_cell(s_slots, cell_key(k, 1u), (k + 16u) & 31u);
+        if (kPos) {
+          // the table is sorted: exactly one key of a cell has a predecessor in another cell
+          uint32_t pk = 0;
+          if (w > 0) pk = (uint32_t)(__ldg(a.table + lo + w - 1) - base) + kQPad;
+          if (w == 0 || cell_key(pk, 0u) != cell_key(k, 0u)) s_hpos[h0] = (uint16_t)w;
+          if (w == 0 || cell_key(pk, 1u) != cell_key(k, 1u)) s_hpos[h1] = (uint16_t)w;
+        }
+      }
+      __syncthreads();
+      int64_t rel[kQRows];
+#pragma unroll
+      for (int j = 0; j < kQRows; j++)   // a dead row gets a value that no window can reach
+        rel[j] = live[j] ? (int64_t)(key[j] - base) + kQPad : (int64_t)1 << 62;
+      for (int g = gb; g < ge; g++) {
+        const int64_t dg = s_gdelta[g];
+        const uint32_t meta = s_gmeta[g];
+        const uint32_t e_span = meta & 0xffu, o_first = (meta >> 8) & 0xffu,
+                       members = (meta >> 16) & 0xffu;
+        uint32_t sh[kQRows], mask[kQRows], slot[kQRows];
+#pragma unroll
+        for (int j = 0; j < kQRows; j++) {
+          const uint64_t t0 = (uint64_t)(rel[j] + dg);
+          const uint32_t q0 = (uint32_t)t0;
+          const uint32_t fam = ((q0 & 31u) + e_span > 31u) ? 1u : 0u;
+          sh[j] = (q0 + 16u * fam) & 31u;
+          const uint32_t m = find_cell<kPos>(s_slots, cell_key(q0, fam), &slot[j]);
+          mask[j] = t0 < kRelLimit ? m : 0u;
+        }
+        if (kMode == kBits && (meta >> 24) != 0u) {
+#pragma unroll
+          for (int j = 0; j < kQRows; j++)
+            bits[j] |= ((mask[j] >> sh[j]) & ((1u << members) - 1u)) << o_first;
+          continue;
+        }
+        const int mb = tab.group_begin[g], me = mb + (int)members;
+        const int e_first = tab.off[o_first][last];
+        for (int m = mb; m < me; m++) {
+          const int o = tab.member[m];
+          const int de = tab.off[o][last] - e_first;
+          if (kMode == kBits) {
+#pragma unroll
+            for (int j = 0; j < kQRows; j++) bits[j] |= ((mask[j] >> (sh[j] + de)) & 1u) << o;
+          } else {
+            int32_t idx[kQRows];
+#pragma unroll
+            for (int j = 0; j < kQRows; j++) {
+              const uint32_t b = sh[j] + (uint32_t)de;
+              idx[j] = ((mask[j] >> b) & 1u)
+                           ? (int32_t)(lo + s_hpos[slot[j]] + __popc(mask[j] & ((1u << b) - 1u))) : -1;
+            }
+            if (kMode == kBitsRev) {
+#pragma unroll
+              for (int j = 0; j < kQRows; j++) {
+                if (idx[j] >= 0) {
+                  bits[j] |= 1u << o;
+                  atomicOr(a.table_words + idx[j], 1u << o);
+                }
+              }
+            } else {
+              int32_t *dst = a.kernel_map + (int64_t)o * a.n_rows + row0;
+              if (vec_ok) {
+                *reinterpret_cast<int2 *>(dst) = make_int2(idx[0], idx[1]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < kQRows; j++) if (live[j]) dst[j] = idx[j];
+              }
+            }
+          }
+        }
+      }
+      __syncthreads();
+    } else {
+      // ---- window too large or too wide for the hash: binary search in global memory
       for (int g = gb; g < ge; g++) {
         const int mb = tab.group_begin[g], me = tab.group_begin[g + 1];
         const int64_t glo = s_glo[g], ghi = s_ghi[g];
@@ -399,16 +401,12 @@ search_kernel(const __grid_constant__ SearchPair sp) {
 #pragma unroll
         for (int j = 0; j < kQRows; j++) {
           const uint64_t q0 = key[j] + (uint64_t)s_delta[tab.member[mb]];
-          if (staged) {
-            pos[j] = lo + lower_bound_win<uint64_t>(s_win, (int)(glo - lo), (int)(ghi - lo), q0);
-          } else {
-            int64_t l = glo, h = ghi;
-            while (l < h) {
-              const int64_t mid = (l + h) >> 1;
-              if (__ldg(a.table + mid) < q0) l = mid + 1; else h = mid;
-            }
-            pos[j] = l;
+          int64_t l = glo, h = ghi;
+          while (l < h) {
+            const int64_t mid = (l + h) >> 1;
+            if (__ldg(a.table + mid) < q0) l = mid + 1; else h = mid;
           }
+          pos[j] = l;
         }
         for (int m = mb; m < me; m++) {
           const int o = tab.member[m];
@@ -417,69 +415,311 @@ search_kernel(const __grid_constant__ SearchPair sp) {
           for (int j = 0; j < kQRows; j++) {
             const uint64_t q = key[j] + (uint64_t)s_delta[o];
             int64_t p = pos[j];
-            uint64_t v = kKeyInf;
-            while (p < ghi) {
-              v = staged ? s_win[p - lo] : __ldg(a.table + p);
+            uint64_t v = ~0ull;
+            while (p < ghi) {   // at most kQMaxSpan steps: the table holds distinct keys
+              v = __ldg(a.table + p);
               if (v >= q) break;
               p++;
-              v = kKeyInf;
+              v = ~0ull;
             }
             pos[j] = p;
             idx[j] = (live[j] && v == q) ? (int32_t)p : -1;
           }
-          emit<kMode>(a, o, row0, vec_ok, live, idx, bits);
+          if (kMode == kMap) {
+            int32_t *dst = a.kernel_map + (int64_t)o * a.n_rows + row0;
+#pragma unroll
+            for (int j = 0; j < kQRows; j++) if (live[j]) dst[j] = idx[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < kQRows; j++) {
+              if (idx[j] >= 0) {
+                bits[j] |= 1u << o;
+                if (kMode == kBitsRev) atomicOr(a.table_words + idx[j], 1u << o);
+              }
+            }
+          }
         }
       }
-      __syncthreads();
     }
   }
 
-  if (kMode == kBits) {
-    if (live[kQRows - 1] && (reinterpret_cast<uintptr_t>(a.hit_words) & 15) == 0) {
-      *reinterpret_cast<uint4 *>(a.hit_words + row0) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+  if (kMode != kMap) {
+    if (live[kQRows - 1] && (reinterpret_cast<uintptr_t>(a.hit_words) & 7) == 0) {
+      *reinterpret_cast<uint2 *>(a.hit_words + row0) = make_uint2(bits[0], bits[1]);
     } else {
 #pragma unroll
       for (int j = 0; j < kQRows; j++) if (live[j]) a.hit_words[row0 + j] = bits[j];
     }
-    // per-offset hit counts of the warp, four offsets at a time: the four bits of
-    // a word are spread into four byte lanes by a multiply, summed over the rows
-    // and reduced over the warp with one redux
-    for (int o0 = 0; o0 < O; o0 += 4) {
-      uint32_t packed = 0;
-#pragma unroll
-      for (int j = 0; j < kQRows; j++)
-        packed += (((bits[j] >> o0) & 0xfu) * 0x00204081u) & 0x01010101u;
-      packed = __reduce_add_sync(0xffffffffu, packed);  // each byte <= 128
-      if (lane < 4 && o0 + lane < O) {
-        const int c = (packed >> (8 * lane)) & 0xff;
-        if (c != 0) atomicAdd(&s_counts[o0 + lane], c);
-      }
-    }
-    __syncthreads();
-    for (int o = tid; o < O; o += kQThreads)
-      a.tile_counts[(int64_t)o * a.n_tiles + bid] = s_counts[o];
   }
 }
 
 // ---------------------------------------------------------------------------
-// plan: per-offset exclusive scan of the tile counts, sizes
+// masks from hit words (fused build)
 // ---------------------------------------------------------------------------
-// Block (o, dir) turns row o of counts[dir] ([O, tiles]) into its exclusive
-// prefix, in place, and writes the row total to sizes[dir * O + o].
-struct ScanArgs {
-  int32_t *counts[2];
-  int32_t tiles[2];
+constexpr int kEThreads = 512;
+constexpr int kEWarps = kEThreads / 32;
+constexpr int kETile = 512;           // rows per tile: one 32-row segment per warp
+constexpr int kEPitch = kETile + 4;   // staging row pitch (elements), a multiple of 4
+
+struct EmitArgs {
+  const uint32_t *words_t;   // [T] hit bits of target rows
+  const uint32_t *words_s;   // [S] hit bits of source rows (== words_t when mirrored)
+  int32_t *target_masks;     // [O, T]
+  int32_t *source_masks;     // [O, S]
+  int32_t *order_out;        // [O] offset at mask row p
+  int32_t *sizes_out;        // [O + 1] size of mask row p, then a copy of the status word
+  int32_t *agg;              // workspace [64 pairs][grid]: hit counts of every block's tile
+                             // range, then their exclusive prefix; pair = direction * 32 + offset
+  int32_t *total;            // workspace [64]
+  int32_t *ctrl;
+  int64_t T, S;
+  int32_t tiles_t, tiles_s;
   int32_t num_offsets;
-  int32_t *sizes;  // [2, O]
+  int32_t reorder;
+  uint8_t mirror[32];        // source direction: which offset's bit to read
 };
 
-__global__ void __launch_bounds__(1024) scan_tiles_kernel(const ScanArgs p) {
+// Transpose of the 32x32 bit matrix held one row per lane: on return lane j
+// holds column j (bit i = bit j of lane i's input).
+__device__ __forceinline__ uint32_t transpose32(uint32_t x, int lane) {
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) {
+    const uint32_t low = s == 16 ? 0x0000ffffu : s == 8 ? 0x00ff00ffu : s == 4 ? 0x0f0f0f0fu
+                       : s == 2 ? 0x33333333u : 0x55555555u;
+    const uint32_t y = __shfl_xor_sync(0xffffffffu, x, s);
+    x = (lane & s) ? ((x & ~low) | ((y & ~low) >> s)) : ((x & low) | ((y & low) << s));
+  }
+  return x;
+}
+
+__device__ __forceinline__ void bulk_store(void *dst_global, const void *src_shared, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_global),
+               "r"((uint32_t)__cvta_generic_to_shared(src_shared)), "r"(bytes)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kEThreads)
+emit_masks_kernel(const __grid_constant__ EmitArgs e) {
+  extern __shared__ __align__(16) int32_t s_stage[];   // [O][kEPitch]
+  __shared__ int32_t s_wcnt[32][kEWarps + 1];           // per offset: warp counts, then warp bases
+  __shared__ int32_t s_run[2][32];                      // rank of the next hit, per direction / offset
+  __shared__ int32_t s_size[32], s_pos[32];
+  __shared__ int32_t s_mis[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int O = e.num_offsets;
+  const int G = (int)gridDim.x, b = (int)blockIdx.x;
+  const int total_tiles = e.tiles_t + e.tiles_s;
+  const int t_begin = (int)((int64_t)total_tiles * b / G);
+  const int t_end = (int)((int64_t)total_tiles * (b + 1) / G);
+  const unsigned lt = lanemask_lt();
+  const int my_mirror = lane < O ? e.mirror[lane] : 0;
+
+  // ---- phase 1: hits per offset of this block's tile range ---------------------
+  int cnt0 = 0, cnt1 = 0;   // lane o: hits of offset o, per direction
+  for (int tile = t_begin; tile < t_end; tile++) {
+    const int dir = tile >= e.tiles_t ? 1 : 0;
+    const int64_t r = (int64_t)(tile - dir * e.tiles_t) * kETile + warp * 32 + lane;
+    const uint32_t *words = dir ? e.words_s : e.words_t;
+    const int64_t n = dir ? e.S : e.T;
+    const uint32_t w = r < n ? __ldg(words + r) : 0u;
+    if (__ballot_sync(0xffffffffu, w != 0u) == 0u) continue;
+    uint32_t plane = transpose32(w, lane);
+    if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
+    if (dir) cnt1 += __popc(plane); else cnt0 += __popc(plane);
+  }
+  for (int d = 0; d < 2; d++) {
+    if (lane < O) s_wcnt[lane][warp] = d ? cnt1 : cnt0;
+    __syncthreads();
+    if (tid < 32) {
+      int sum = 0;
+      if (tid < O)
+        for (int w = 0; w < kEWarps; w++) sum += s_wcnt[tid][w];
+      e.agg[(int64_t)(d * 32 + tid) * G + b] = sum;
+    }
+    __syncthreads();
+  }
+  grid_barrier(e.ctrl, (unsigned)G);
+
+  // ---- one warp per (direction, offset): exclusive prefix over the blocks ----------
+  for (int pair = b * kEWarps + warp; pair < 64; pair += G * kEWarps) {
+    {
+      int32_t *row = e.agg + (int64_t)pair * G;
+      int carry = 0;
+      for (int b0 = 0; b0 < G; b0 += 32) {
+        const int bb = b0 + lane;
+        const int v = bb < G ? __ldcg(row + bb) : 0;
+        int inc = v;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, inc, s);
+          if (lane >= s) inc += t;
+        }
+        if (bb < G) row[bb] = carry + inc - v;
+        carry += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) e.total[pair] = carry;
+    }
+  }
+  grid_barrier(e.ctrl, (unsigned)G);
+
+  // ---- rank offsets of this block, total sizes, size order ---------------------
+  if (tid < 64) s_run[tid >> 5][tid & 31] = __ldcg(e.agg + (int64_t)tid * G + b);
+  if (tid < 32) s_size[tid] = __ldcg(e.total + tid);
+  __syncthreads();
+  if (tid < O) {
+    int pos = tid;
+    if (e.reorder) {
+      // stable ascending sizes: ties keep the offset order
+      const int mine = s_size[tid];
+      pos = 0;
+      for (int j = 0; j < O; j++) {
+        const int other = s_size[j];
+        pos += (other < mine) || (other == mine && j < tid);
+      }
+    }
+    s_pos[tid] = pos;
+    if (b == 0) {
+      e.order_out[pos] = tid;
+      e.sizes_out[pos] = s_size[tid];
+    }
+  }
+  if (b == 0 && tid == 0) e.sizes_out[O] = e.ctrl[MN_CTRL_STATUS];
+  __syncthreads();
+
+  // ---- phase 2: ranks, staged per tile, one bulk copy per mask row segment ------
+  bool pending = false;   // threads < O: a bulk group of mine may still be reading the stage
+  for (int tile = t_begin; tile < t_end; tile++) {
+    const int dir = tile >= e.tiles_t ? 1 : 0;
+    const int64_t tile_row0 = (int64_t)(tile - dir * e.tiles_t) * kETile;
+    const uint32_t *words = dir ? e.words_s : e.words_t;
+    const int64_t n = dir ? e.S : e.T;
+    int32_t *out = dir ? e.source_masks : e.target_masks;
+    const int rows_here = (int)min((int64_t)kETile, n - tile_row0);
+    const int seg = warp * 32;
+
+    uint32_t plane;
+    {
+      const int64_t r = tile_row0 + seg + lane;
+      const uint32_t w = r < n ? __ldg(words + r) : 0u;
+      plane = transpose32(w, lane);
+      if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
+      if (lane >= O) plane = 0u;
+    }
+    if (lane < O) s_wcnt[lane][warp] = __popc(plane);
+    // the previous tile's copies must have read the stage before it is refilled
+    if (pending) {
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      pending = false;
+    }
+    __syncthreads();
+    if (tid < O) {
+      // exclusive prefix over the warps on top of the running rank; where the
+      // row segment of this offset starts relative to a 16-byte boundary
+      int run = s_run[dir][tid];
+#pragma unroll
+      for (int w = 0; w < kEWarps; w++) {
+        const int c = s_wcnt[tid][w];
+        s_wcnt[tid][w] = run;
+        run += c;
+      }
+      s_run[dir][tid] = run;
+      const int64_t g0 = (int64_t)s_pos[tid] * n + tile_row0;
+      s_mis[tid] = (int)(((reinterpret_cast<uintptr_t>(out) >> 2) + (uint64_t)g0) & 3u);
+    }
+    {
+      int4 *fill = reinterpret_cast<int4 *>(s_stage);
+      const int n_vec = O * kEPitch / 4;
+      for (int i = tid; i < n_vec; i += kEThreads) fill[i] = make_int4(-1, -1, -1, -1);
+    }
+    __syncthreads();
+    // sparse planes: the owning lane walks its hits; dense planes: all lanes, one row each
+    {
+      int base = 0;
+      int32_t *row = s_stage;
+      if (lane < O) {
+        base = s_wcnt[lane][warp];
+        row = s_stage + lane * kEPitch + s_mis[lane] + seg;
+      }
+      const bool dense = __popc(plane) > 6;
+      uint32_t p = dense ? 0u : plane;
+      int r = base;
+      while (p != 0u) {
+        row[__ffs(p) - 1] = r++;
+        p &= p - 1u;
+      }
+      uint32_t todo = __ballot_sync(0xffffffffu, dense);
+      while (todo != 0u) {
+        const int o = __ffs(todo) - 1;
+        todo &= todo - 1u;
+        const uint32_t pl = __shfl_sync(0xffffffffu, plane, o);
+        const int bs = __shfl_sync(0xffffffffu, base, o);
+        if ((pl >> lane) & 1u) s_stage[o * kEPitch + s_mis[o] + seg + lane] = bs + __popc(pl & lt);
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid < O) {
+      const int mis = s_mis[tid];
+      const int32_t *src = s_stage + tid * kEPitch + mis;
+      int32_t *dst = out + (int64_t)s_pos[tid] * n + tile_row0;
+      const int head = min((4 - mis) & 3, rows_here);
+      const int body = (rows_here - head) & ~3;
+      if (body > 0) {
+        bulk_store(dst + head, src + head, (uint32_t)body * 4u);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        pending = true;
+      }
+      for (int i = 0; i < head; i++) dst[i] = src[i];
+      for (int i = head + body; i < rows_here; i++) dst[i] = src[i];
+    }
+  }
+  if (pending) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+__global__ void identity_order_kernel(int O, int32_t *order_out, int32_t *sizes_out,
+                                      const int32_t *ctrl) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o < O) { order_out[o] = o; sizes_out[o] = 0; }
+  if (o == O) sizes_out[O] = ctrl[MN_CTRL_STATUS];
+}
+
+// ---------------------------------------------------------------------------
+// reference-API pieces that start from a materialised kernel map
+// ---------------------------------------------------------------------------
+constexpr int kMTile = 1024;     // rows per tile of the kernels below
+constexpr int kMThreads = 256;
+
+// counts[o, tile] = valid entries of kernel_map[o, tile * kMTile ...)
+__global__ void __launch_bounds__(kMThreads)
+map_count_kernel(const int32_t *__restrict__ kernel_map, int64_t T, int n_tiles,
+                 int32_t *__restrict__ counts, int32_t *__restrict__ sizes_atomic) {
+  const int o = blockIdx.y, tile = blockIdx.x;
+  const int64_t t0 = (int64_t)tile * kMTile;
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < kMTile / kMThreads; j++) {
+    const int64_t t = t0 + j * kMThreads + threadIdx.x;
+    if (t < T) c += __ldg(kernel_map + (int64_t)o * T + t) != -1;
+  }
+  c = __reduce_add_sync(0xffffffffu, c);
+  __shared__ int s[kMThreads / 32];
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int w = 0; w < kMThreads / 32; w++) tot += s[w];
+    if (counts != nullptr) counts[(int64_t)o * n_tiles + tile] = tot;
+    if (sizes_atomic != nullptr && tot != 0) atomicAdd(sizes_atomic + o, tot);
+  }
+}
+
+// Block o turns row o of counts ([O, tiles]) into its exclusive prefix, in place.
+__global__ void __launch_bounds__(1024)
+scan_tiles_kernel(int32_t *__restrict__ counts, int n) {
   __shared__ int32_t s_warp[32];
   __shared__ int32_t s_carry;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int o = blockIdx.x, dir = blockIdx.y;
-  const int n = p.tiles[dir];
-  int32_t *row = p.counts[dir] + (int64_t)o * n;
+  int32_t *row = counts + (int64_t)blockIdx.x * n;
   if (threadIdx.x == 0) s_carry = 0;
   __syncthreads();
   for (int b0 = 0; b0 < n; b0 += 1024) {
@@ -500,192 +740,17 @@ __global__ void __launch_bounds__(1024) scan_tiles_kernel(const ScanArgs p) {
     if (threadIdx.x == 1023) s_carry = before + inc;
     __syncthreads();
   }
-  if (threadIdx.x == 0) p.sizes[dir * p.num_offsets + o] = s_carry;
-}
-
-// order[p] = offset at mask row p (stable ascending sizes), sizes_out[p] its size
-__device__ __forceinline__ void rank_offsets(const int32_t *sizes_raw, int O, int reorder,
-                                             int32_t *s_pos /* shared [O] */) {
-  for (int o = threadIdx.x; o < O; o += blockDim.x) {
-    int pos = o;
-    if (reorder) {
-      const int32_t mine = sizes_raw[o];
-      pos = 0;
-      for (int j = 0; j < O; j++) {
-        const int32_t other = sizes_raw[j];
-        pos += (other < mine) || (other == mine && j < o);
-      }
-    }
-    s_pos[o] = pos;
-  }
-}
-
-__global__ void identity_order_kernel(int O, int32_t *order_out, int32_t *sizes_out) {
-  const int o = blockIdx.x * blockDim.x + threadIdx.x;
-  if (o < O) { order_out[o] = o; sizes_out[o] = 0; }
-}
-
-// ---------------------------------------------------------------------------
-// masks from hit words
-// ---------------------------------------------------------------------------
-struct EmitArgs {
-  const uint32_t *words_t;   // [T] hit bits of target rows
-  const uint32_t *words_s;   // [S] hit bits of source rows (== words_t when mirrored)
-  const int32_t *prefix_t;   // [O, tiles_t] exclusive tile prefix, target direction
-  const int32_t *prefix_s;   // [O, tiles_s] source direction (== prefix_t when mirrored)
-  const int32_t *sizes_raw;  // [O] hits per offset (offset order)
-  int32_t *order_out;        // [O] offset at mask row p
-  int32_t *sizes_out;        // [O] size of mask row p
-  int32_t reorder;
-  int32_t *target_masks;     // [O, T]
-  int32_t *source_masks;     // [O, S]
-  int64_t T, S;
-  int32_t tiles_t, tiles_s;
-  int32_t num_offsets;
-  uint8_t mirror[MN_MAX_OFFSETS];  // source direction: which offset's bit/prefix to read
-};
-
-// One block = 1024 consecutive rows of one direction; thread t owns rows
-// 4t..4t+3.  For every offset the rank of a hit row is
-//   tile prefix + hits in lower warps + hits in lower lanes + own earlier hits,
-// and the four results leave as one 128-bit store when the row pitch allows it.
-__global__ void __launch_bounds__(kQThreads)
-emit_masks_kernel(const __grid_constant__ EmitArgs e) {
-  __shared__ int32_t s_wtot[32][kQWarps + 1];  // offsets handled 32 at a time
-  __shared__ int32_t s_pos[MN_MAX_OFFSETS];
-  __shared__ int32_t s_pre[MN_MAX_OFFSETS];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  rank_offsets(e.sizes_raw, e.num_offsets, e.reorder, s_pos);
-  {
-    // this tile's rank offset for every output row, fetched once per block
-    const bool src_dir0 = blockIdx.x >= (unsigned)e.tiles_t;
-    const int tile0 = src_dir0 ? blockIdx.x - e.tiles_t : blockIdx.x;
-    const int32_t *prefix0 = src_dir0 ? e.prefix_s : e.prefix_t;
-    const int n_tiles0 = src_dir0 ? e.tiles_s : e.tiles_t;
-    for (int o = tid; o < e.num_offsets; o += kQThreads) {
-      const int b = src_dir0 ? e.mirror[o] : o;
-      s_pre[o] = __ldg(prefix0 + (int64_t)b * n_tiles0 + tile0);
-    }
-  }
-  __syncthreads();
-  if (blockIdx.x == 0) {
-    for (int o = tid; o < e.num_offsets; o += kQThreads) {
-      e.order_out[s_pos[o]] = o;
-      e.sizes_out[s_pos[o]] = e.sizes_raw[o];
-    }
-  }
-  const bool src_dir = blockIdx.x >= (unsigned)e.tiles_t;
-  const int tile = src_dir ? blockIdx.x - e.tiles_t : blockIdx.x;
-  const uint32_t *words = src_dir ? e.words_s : e.words_t;
-  const int32_t *prefix = src_dir ? e.prefix_s : e.prefix_t;
-  const int n_tiles = src_dir ? e.tiles_s : e.tiles_t;
-  const int64_t n = src_dir ? e.S : e.T;
-  int32_t *out = src_dir ? e.source_masks : e.target_masks;
-  const int O = e.num_offsets;
-  const unsigned lt = lanemask_lt();
-
-  const int64_t row0 = (int64_t)tile * kQTile + tid * 4;
-  uint32_t w[4] = {0u, 0u, 0u, 0u};
-  const bool vec_in = (row0 + 3 < n) && ((reinterpret_cast<uintptr_t>(words) & 15) == 0);
-  if (vec_in) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(words + row0));
-    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; i++) if (row0 + i < n) w[i] = __ldg(words + row0 + i);
-  }
-  const bool vec_out = ((n & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-
-  for (int o0 = 0; o0 < O; o0 += 32) {
-    const int oc = min(32, O - o0);
-    // warp totals of this chunk of offsets
-    for (int oo = 0; oo < oc; oo++) {
-      const int b = src_dir ? e.mirror[o0 + oo] : (o0 + oo);
-      int c = ((w[0] >> b) & 1u) + ((w[1] >> b) & 1u) + ((w[2] >> b) & 1u) + ((w[3] >> b) & 1u);
-      c = __reduce_add_sync(0xffffffffu, c);
-      if (lane == 0) s_wtot[oo][warp] = c;
-    }
-    __syncthreads();
-    if (tid < oc) {
-      int run = 0;
-#pragma unroll
-      for (int ww = 0; ww < kQWarps; ww++) {
-        const int t = s_wtot[tid][ww];
-        s_wtot[tid][ww] = run;
-        run += t;
-      }
-    }
-    __syncthreads();
-    for (int oo = 0; oo < oc; oo++) {
-      const int o = o0 + oo;
-      const int b = src_dir ? e.mirror[o] : o;
-      const int v0 = (w[0] >> b) & 1u, v1 = (w[1] >> b) & 1u, v2 = (w[2] >> b) & 1u,
-                v3 = (w[3] >> b) & 1u;
-      const int mine = v0 + v1 + v2 + v3;
-      // exclusive prefix of `mine` over the lanes of this warp
-      int inc = mine;
-#pragma unroll
-      for (int s = 1; s < 32; s <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, s);
-        if (lane >= s) inc += t;
-      }
-      int r = s_pre[o] + s_wtot[oo][warp] + inc - mine;
-      int4 res;
-      res.x = v0 ? r : -1; r += v0;
-      res.y = v1 ? r : -1; r += v1;
-      res.z = v2 ? r : -1; r += v2;
-      res.w = v3 ? r : -1;
-      int32_t *dst = out + (int64_t)s_pos[o] * n + row0;
-      if (vec_out) {
-        if (row0 < n) *reinterpret_cast<int4 *>(dst) = res;
-      } else {
-        if (row0 + 0 < n) dst[0] = res.x;
-        if (row0 + 1 < n) dst[1] = res.y;
-        if (row0 + 2 < n) dst[2] = res.z;
-        if (row0 + 3 < n) dst[3] = res.w;
-      }
-    }
-    __syncthreads();
-  }
-  (void)lt;
-}
-
-// ---------------------------------------------------------------------------
-// reference-API pieces that start from a materialised kernel map
-// ---------------------------------------------------------------------------
-// counts[o, tile] = valid entries of kernel_map[o, tile*1024 ...)
-__global__ void __launch_bounds__(kQThreads)
-map_count_kernel(const int32_t *__restrict__ kernel_map, int64_t T, int n_tiles,
-                 int32_t *__restrict__ counts, int32_t *__restrict__ sizes_atomic) {
-  const int o = blockIdx.y, tile = blockIdx.x;
-  const int64_t t0 = (int64_t)tile * kQTile;
-  int c = 0;
-#pragma unroll
-  for (int j = 0; j < kQRows; j++) {
-    const int64_t t = t0 + j * kQThreads + threadIdx.x;
-    if (t < T) c += __ldg(kernel_map + (int64_t)o * T + t) != -1;
-  }
-  c = __reduce_add_sync(0xffffffffu, c);
-  __shared__ int s[kQWarps];
-  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int tot = 0;
-    for (int w = 0; w < kQWarps; w++) tot += s[w];
-    if (counts != nullptr) counts[(int64_t)o * n_tiles + tile] = tot;
-    if (sizes_atomic != nullptr && tot != 0) atomicAdd(sizes_atomic + o, tot);
-  }
 }
 
 // rank valid entries of row o by t; write the target mask densely and the
 // source mask (pre-filled with -1) by scatter
-__global__ void __launch_bounds__(kQThreads)
+__global__ void __launch_bounds__(kMThreads)
 map_masks_kernel(const int32_t *__restrict__ kernel_map, int64_t S, int64_t T, int n_tiles,
                  const int32_t *__restrict__ prefix, int32_t *__restrict__ source_masks,
                  int32_t *__restrict__ target_masks) {
   const int o = blockIdx.y, tile = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t t0 = (int64_t)tile * kQTile + threadIdx.x * 4;
+  const int64_t t0 = (int64_t)tile * kMTile + threadIdx.x * 4;
   int32_t s_idx[4];
   int mine = 0;
 #pragma unroll
@@ -699,7 +764,7 @@ map_masks_kernel(const int32_t *__restrict__ kernel_map, int64_t S, int64_t T, i
     const int t = __shfl_up_sync(0xffffffffu, inc, s);
     if (lane >= s) inc += t;
   }
-  __shared__ int s_w[kQWarps];
+  __shared__ int s_w[kMThreads / 32];
   if (lane == 31) s_w[warp] = inc;
   __syncthreads();
   int r = prefix[(int64_t)o * n_tiles + tile] + inc - mine;
@@ -716,26 +781,21 @@ map_masks_kernel(const int32_t *__restrict__ kernel_map, int64_t S, int64_t T, i
 }
 
 void fill_search_args(SearchArgs *a, const uint64_t *rows, int64_t n_rows, const uint64_t *table,
-                      int64_t n_table, const OffsetTable &tab, const mn_keyspec &spec,
-                      int32_t *kernel_map, uint32_t *hit_words, int32_t *tile_counts) {
+                      int64_t n_table, int32_t *kernel_map, uint32_t *hit_words) {
   *a = SearchArgs{};
   a->rows = rows; a->table = table; a->n_rows = n_rows; a->n_table = n_table;
-  a->kernel_map = kernel_map; a->hit_words = hit_words; a->tile_counts = tile_counts;
+  a->kernel_map = kernel_map; a->hit_words = hit_words;
   a->n_tiles = (int)div_up(n_rows, kQTile);
-  for (int k = 0; k < 4; k++) a->shift[k] = spec.shift[k];
-  a->fast_ok = spec.shift[spec.ndim - 1] == 0;
-  for (int o = 0; o < tab.num_offsets; o++) {
-    const int e = tab.off[o][tab.ndim - 1];
-    if (e > (int)kQPad || e < -(int)kQPad) a->fast_ok = 0;
-  }
 }
 
 // Launches one search, or two in the same grid when `second` is given.
-mn_status run_search(int mode, const SearchArgs &first, const OffsetTable &tab_first,
-                     const SearchArgs *second, const OffsetTable *tab_second, cudaStream_t st) {
+mn_status run_search(int mode, const mn_keyspec &spec, const SearchArgs &first,
+                     const OffsetTable &tab_first, const SearchArgs *second,
+                     const OffsetTable *tab_second, cudaStream_t st) {
   thread_local static SearchPair sp;   // ~5 KB: kept off the stack; passed by value per launch
   sp.a[0] = first;
   sp.tab[0] = tab_first;
+  sp.spec = make_spec_ref(spec);
   sp.tiles0 = first.n_tiles;
   int blocks = first.n_tiles;
   if (second != nullptr) {
@@ -745,9 +805,11 @@ mn_status run_search(int mode, const SearchArgs &first, const OffsetTable &tab_f
   }
   if (blocks == 0) return MN_OK;
   {
-    LaunchScope scope(mode == kMap ? "search_kernel<map>" : "search_kernel<bits>", st);
+    LaunchScope scope(mode == kMap ? "search_kernel<map>" : mode == kBits ? "search_kernel<bits>"
+                                                                         : "search_kernel<bits,rev>", st);
     if (mode == kMap) search_kernel<kMap><<<blocks, kQThreads, 0, st>>>(sp);
-    else search_kernel<kBits><<<blocks, kQThreads, 0, st>>>(sp);
+    else if (mode == kBits) search_kernel<kBits><<<blocks, kQThreads, 0, st>>>(sp);
+    else search_kernel<kBitsRev><<<blocks, kQThreads, 0, st>>>(sp);
   }
   MN_CHECK_LAUNCH();
   return MN_OK;
@@ -779,14 +841,20 @@ mn_status make_offset_table(const int32_t *offsets, int64_t O, int ndim, int sig
       if (out->off[x][k] != out->off[y][k]) return out->off[x][k] < out->off[y][k];
     return false;
   });
-  int g = 0;
+  // a group: same offset in every dimension but the last, last-dimension span <= kQMaxSpan
+  int g = 0, first = 0;
   for (int64_t i = 0; i < O; i++) {
     out->member[i] = (uint8_t)idx[i];
     bool new_group = i == 0;
-    if (i > 0)
+    if (i > 0) {
       for (int k = 0; k + 1 < ndim; k++)
         new_group |= out->off[idx[i]][k] != out->off[idx[i - 1]][k];
-    if (new_group) out->group_begin[g++] = (uint8_t)i;
+      new_group |= out->off[idx[i]][ndim - 1] - out->off[first][ndim - 1] > kQMaxSpan;
+    }
+    if (new_group) {
+      out->group_begin[g++] = (uint8_t)i;
+      first = idx[i];
+    }
   }
   out->group_begin[g] = (uint8_t)O;
   out->num_groups = g;
@@ -801,9 +869,10 @@ extern "C" size_t mn_map_workspace_bytes(int64_t S, int64_t T, int64_t O) {
   const int64_t n = std::max<int64_t>(std::max(S, T), 1);
   size_t sort = 2 * align_up((size_t)n * 8, 256) + 2 * align_up((size_t)n * 4, 256) +
                 radix_sort_workspace_bytes(n) + align_up((size_t)div_up(n, 2048) * 4, 256) + 512;
-  const int64_t tiles = div_up(S, kQTile) + div_up(T, kQTile) + 2;
+  const int64_t tiles = div_up(S, kMTile) + div_up(T, kMTile) + 2;
   size_t map = align_up((size_t)S * 4, 256) + align_up((size_t)T * 4, 256) +
-               2 * align_up((size_t)std::max<int64_t>(O, 1) * tiles * 4, 256) + 4 * 1024;
+               2 * align_up((size_t)std::max<int64_t>(O, 1) * tiles * 4, 256) +
+               align_up((size_t)kMaxCoopBlocks * 64 * 4, 256) + 4 * 1024;
   size_t bbox = (size_t)kNumSMs * 4 * 8 * 4 + 256;
   return std::max(std::max(sort, map), bbox) + 4096;
 }
@@ -820,9 +889,14 @@ extern "C" mn_status mn_query_sorted_index_with_offsets(
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(target_keys != nullptr && kernel_map_out != nullptr && (S == 0 || source_keys != nullptr),
                "query: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (S == 0) {
+    MN_CHECK_CUDA(cudaMemsetAsync(kernel_map_out, 0xff, sizeof(int32_t) * O * T, st));
+    return MN_OK;
+  }
   SearchArgs a;
-  fill_search_args(&a, target_keys, T, source_keys, S, tab, *spec, kernel_map_out, nullptr, nullptr);
-  return run_search(kMap, a, tab, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+  fill_search_args(&a, target_keys, T, source_keys, S, kernel_map_out, nullptr);
+  return run_search(kMap, *spec, a, tab, nullptr, nullptr, st);
 }
 
 extern "C" mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int64_t O, int64_t T,
@@ -834,9 +908,10 @@ extern "C" mn_status mn_compute_kernel_map_sizes(const int32_t *kernel_map, int6
   MN_CHECK_CUDA(cudaMemsetAsync(sizes_out, 0, sizeof(int32_t) * O, st));
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(kernel_map != nullptr, "sizes: null kernel map");
-  const int n_tiles = (int)div_up(T, kQTile);
-  MN_LAUNCH("map_count_kernel", st, map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, nullptr,
-                                                                     sizes_out));
+  const int n_tiles = (int)div_up(T, kMTile);
+  MN_LAUNCH("map_count_kernel", st,
+            map_count_kernel<<<dim3(n_tiles, (unsigned)O), kMThreads, 0, st>>>(
+                kernel_map, T, n_tiles, nullptr, sizes_out));
   return MN_OK;
 }
 
@@ -856,17 +931,16 @@ extern "C" mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int6
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(kernel_map != nullptr && target_masks_out != nullptr, "masks: null pointer");
   Workspace ws(ws_ptr, ws_bytes);
-  const int n_tiles = (int)div_up(T, kQTile);
+  const int n_tiles = (int)div_up(T, kMTile);
   int32_t *counts = ws.take<int32_t>((size_t)O * n_tiles);
-  int32_t *scratch = ws.take<int32_t>(4 * MN_MAX_OFFSETS);
   MN_CHECK_WS(ws);
-  MN_LAUNCH("map_count_kernel", st, map_count_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(kernel_map, T, n_tiles, counts,
-                                                                     nullptr));
-  ScanArgs p{};
-  p.counts[0] = counts; p.tiles[0] = n_tiles; p.num_offsets = (int)O; p.sizes = scratch;
-  MN_LAUNCH("scan_tiles_kernel", st, scan_tiles_kernel<<<dim3((unsigned)O, 1), 1024, 0, st>>>(p));
-  MN_LAUNCH("map_masks_kernel", st, map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kQThreads, 0, st>>>(
-      kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out));
+  MN_LAUNCH("map_count_kernel", st,
+            map_count_kernel<<<dim3(n_tiles, (unsigned)O), kMThreads, 0, st>>>(
+                kernel_map, T, n_tiles, counts, nullptr));
+  MN_LAUNCH("scan_tiles_kernel", st, scan_tiles_kernel<<<(unsigned)O, 1024, 0, st>>>(counts, n_tiles));
+  MN_LAUNCH("map_masks_kernel", st,
+            map_masks_kernel<<<dim3(n_tiles, (unsigned)O), kMThreads, 0, st>>>(
+                kernel_map, S, T, n_tiles, counts, source_masks_out, target_masks_out));
   return MN_OK;
 }
 
@@ -875,8 +949,8 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
                                          const int32_t *offsets, int64_t O,
                                          const mn_keyspec *spec, int reorder,
                                          int32_t *source_masks_out, int32_t *target_masks_out,
-                                         int32_t *order_out, int32_t *sizes_out, void *ws_ptr,
-                                         size_t ws_bytes, void *stream) {
+                                         int32_t *order_out, int32_t *sizes_out, int32_t *ctrl,
+                                         void *ws_ptr, size_t ws_bytes, void *stream) {
   MN_CHECK_ARG(S >= 0 && T >= 0, "build_kernel_map: negative size");
   MN_CHECK_ARG(spec != nullptr, "build_kernel_map: null key spec");
   MN_CHECK_ARG(S < (1ll << 31) && T < (1ll << 31), "build_kernel_map: more than 2^31-1 rows");
@@ -885,11 +959,23 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
               "mn_query_sorted_index_with_offsets + mn_compute_kernel_map_masks", (long long)O);
     return MN_ERR_UNSUPPORTED;
   }
-  MN_CHECK_ARG(order_out != nullptr && sizes_out != nullptr, "build_kernel_map: null pointer");
+  MN_CHECK_ARG(order_out != nullptr && sizes_out != nullptr && ctrl != nullptr,
+               "build_kernel_map: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int ndim = spec->ndim;
   OffsetTable fwd;
   MN_RETURN_IF(make_offset_table(offsets, O, ndim, +1, spec, &fwd));
+
+  if (T == 0 || S == 0) {
+    // nothing can match: every mask entry is -1, every size 0
+    if (S > 0) MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
+    if (T > 0) MN_CHECK_CUDA(cudaMemsetAsync(target_masks_out, 0xff, sizeof(int32_t) * O * T, st));
+    MN_LAUNCH("identity_order_kernel", st,
+              identity_order_kernel<<<1, MN_MAX_OFFSETS + 32, 0, st>>>((int)O, order_out, sizes_out, ctrl));
+    return MN_OK;
+  }
+  MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
+                   target_masks_out != nullptr, "build_kernel_map: null pointer");
 
   // mirrored offset of every offset, if the table is symmetric
   bool symmetric = true;
@@ -905,54 +991,58 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   }
   const bool mirrored = symmetric && source_keys == target_keys && S == T;
 
-  Workspace ws(ws_ptr, ws_bytes);
-  const int tiles_t = (int)div_up(T, kQTile), tiles_s = (int)div_up(S, kQTile);
-  uint32_t *words_t = ws.take<uint32_t>(std::max<int64_t>(T, 1));
-  int32_t *counts_t = ws.take<int32_t>((size_t)O * std::max(tiles_t, 1));
-  uint32_t *words_s = words_t;
-  int32_t *counts_s = counts_t;
-  if (!mirrored) {
-    words_s = ws.take<uint32_t>(std::max<int64_t>(S, 1));
-    counts_s = ws.take<int32_t>((size_t)O * std::max(tiles_s, 1));
+  // grid of the cooperative emission kernel: every block resident at once
+  const size_t stage_bytes = (size_t)O * kEPitch * sizeof(int32_t);
+  static thread_local int coresident_for[kMaxDevices][33] = {{0}};
+  int device = 0;
+  MN_CHECK_CUDA(cudaGetDevice(&device));
+  MN_CHECK_ARG(device >= 0 && device < kMaxDevices, "build_kernel_map: device index %d out of range", device);
+  int &coresident = coresident_for[device][O];
+  if (coresident == 0) {
+    MN_CHECK_CUDA(cudaFuncSetAttribute(emit_masks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       32 * kEPitch * (int)sizeof(int32_t)));
+    coresident = std::min(kMaxCoopBlocks, max_coresident_blocks(emit_masks_kernel, kEThreads, stage_bytes));
+    if (coresident <= 0) {
+      coresident = 0;
+      set_error("build_kernel_map: cannot size the cooperative grid");
+      return MN_ERR_CUDA;
+    }
   }
-  int32_t *sizes_raw = ws.take<int32_t>(2 * MN_MAX_OFFSETS);
+  const int tiles_t = (int)div_up(T, kETile), tiles_s = (int)div_up(S, kETile);
+  const int grid = std::min(tiles_t + tiles_s, coresident);
+
+  Workspace ws(ws_ptr, ws_bytes);
+  uint32_t *words_t = ws.take<uint32_t>(T);
+  uint32_t *words_s = mirrored ? words_t : ws.take<uint32_t>(S);
+  int32_t *agg = ws.take<int32_t>((size_t)grid * 64);
+  int32_t *total = ws.take<int32_t>(64);
   MN_CHECK_WS(ws);
 
-  if (T == 0 || S == 0) {
-    // nothing can match: every mask entry is -1, every size 0
-    if (S > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
-    if (T > 0 && O > 0) MN_CHECK_CUDA(cudaMemsetAsync(target_masks_out, 0xff, sizeof(int32_t) * O * T, st));
-    MN_LAUNCH("identity_order_kernel", st,
-              identity_order_kernel<<<1, MN_MAX_OFFSETS, 0, st>>>((int)O, order_out, sizes_out));
-    return MN_OK;
-  }
-  MN_CHECK_ARG(source_keys != nullptr && target_keys != nullptr && source_masks_out != nullptr &&
-                   target_masks_out != nullptr, "build_kernel_map: null pointer");
-
-  SearchArgs fwd_args, bwd_args;
-  fill_search_args(&fwd_args, target_keys, T, source_keys, S, fwd, *spec, nullptr, words_t, counts_t);
+  SearchArgs fwd_args;
+  fill_search_args(&fwd_args, target_keys, T, source_keys, S, nullptr, words_t);
   if (mirrored) {
-    MN_RETURN_IF(run_search(kBits, fwd_args, fwd, nullptr, nullptr, st));
+    MN_RETURN_IF(run_search(kBits, *spec, fwd_args, fwd, nullptr, nullptr, st));
   } else {
-    // second direction in the same launch: sources as rows, targets as table, -offsets
-    OffsetTable bwd;
-    MN_RETURN_IF(make_offset_table(offsets, O, ndim, -1, spec, &bwd));
-    fill_search_args(&bwd_args, source_keys, S, target_keys, T, bwd, *spec, nullptr, words_s, counts_s);
-    MN_RETURN_IF(run_search(kBits, fwd_args, fwd, &bwd_args, &bwd, st));
+    // one search with the targets as rows; every hit also sets its bit in the word of the
+    // source it found, so the source side needs no search of its own
+    MN_CHECK_CUDA(cudaMemsetAsync(words_s, 0, sizeof(uint32_t) * S, st));
+    fwd_args.table_words = words_s;
+    MN_RETURN_IF(run_search(kBitsRev, *spec, fwd_args, fwd, nullptr, nullptr, st));
   }
-  ScanArgs p{};
-  p.counts[0] = counts_t; p.tiles[0] = tiles_t;
-  p.counts[1] = counts_s; p.tiles[1] = tiles_s;
-  p.num_offsets = (int)O; p.sizes = sizes_raw;
-  MN_LAUNCH("scan_tiles_kernel", st,
-            scan_tiles_kernel<<<dim3((unsigned)O, mirrored ? 1 : 2), 1024, 0, st>>>(p));
 
   EmitArgs e{};
-  e.words_t = words_t; e.words_s = words_s; e.prefix_t = counts_t; e.prefix_s = counts_s;
-  e.sizes_raw = sizes_raw; e.order_out = order_out; e.sizes_out = sizes_out;
-  e.reorder = reorder ? 1 : 0; e.target_masks = target_masks_out; e.source_masks = source_masks_out;
-  e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s; e.num_offsets = (int)O;
+  e.words_t = words_t; e.words_s = words_s;
+  e.target_masks = target_masks_out; e.source_masks = source_masks_out;
+  e.order_out = order_out; e.sizes_out = sizes_out; e.agg = agg; e.total = total; e.ctrl = ctrl;
+  e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s;
+  e.num_offsets = (int)O; e.reorder = reorder ? 1 : 0;
   for (int64_t o = 0; o < O; o++) e.mirror[o] = mirrored ? neg[o] : (uint8_t)o;
-  MN_LAUNCH("emit_masks_kernel", st, emit_masks_kernel<<<tiles_t + tiles_s, kQThreads, 0, st>>>(e));
+  void *params[] = {&e};
+  {
+    LaunchScope scope("emit_masks_kernel", st);
+    MN_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(emit_masks_kernel), dim3(grid),
+                                              dim3(kEThreads), params, stage_bytes, st));
+  }
+  MN_CHECK_LAUNCH();
   return MN_OK;
 }

@@ -8,7 +8,8 @@
 // hand-written stable LSD radix sort (9-bit digits, warp match ranking) that
 // only visits the key bits the bounding box uses, and unique/compaction is one
 // count + scan + compact pipeline that can also unpack keys back to coordinates.
-#include "mn_common.cuh"
+#include "mn_grid.cuh"
+#include "mn_pack.cuh"
 
 #include <algorithm>
 #include <mutex>
@@ -18,14 +19,34 @@ namespace mn {
 namespace {
 
 // ---------------------------------------------------------------------------
-// radix sort
+// radix sort: one cooperative kernel for all passes
 // ---------------------------------------------------------------------------
-constexpr int kRsThreads = 256;
+// Stable LSD sort, 9-bit digits.  Every block (1024 threads, one per SM) owns a
+// contiguous chunk of the input and every warp a contiguous slice of that chunk,
+// so that "block order, then warp order, then position" is the input order.
+// Per pass:
+//   A  every warp counts the digits of its slice into its own row of a
+//      [32 warps][512 digits] shared-memory table (equal digits inside a group
+//      of 32 keys find each other with match.any, one lane adds the group's
+//      count); the block histogram goes to a digit-major global table
+//   -- grid barrier --
+//   B  one warp per digit turns that digit's row (one entry per block) into an
+//      exclusive prefix and writes the digit total
+//   -- grid barrier --
+//   C  every block scans the 512 digit totals, turns its per-warp counts into
+//      global positions and re-walks its chunk in the same order, writing every
+//      key (and payload) to its place
+//   -- grid barrier (the next pass reads what this one wrote) --
+// The first pass can build the keys itself from coordinate rows (floor to a
+// target stride and pack), so that the strided target-coordinate build needs no
+// separate packing launch.  The number of passes comes from the key layout,
+// which may live on the device only.
+constexpr int kRsThreads = 1024;
 constexpr int kRsWarps = kRsThreads / 32;
-constexpr int kRsItems = 4;                       // keys per thread
-constexpr int kRsTile = kRsThreads * kRsItems;    // 1024 keys per block
 constexpr int kRsBits = 9;                        // digit width: 4 passes cover 36 key bits
 constexpr int kRadix = 1 << kRsBits;
+constexpr int kRsMaxBlocks = 256;                 // workspace sizing
+constexpr size_t kRsSmemBytes = (size_t)kRsWarps * kRadix * sizeof(uint32_t);   // 64 KB
 
 __device__ __forceinline__ unsigned lanemask_lt() {
   unsigned m;
@@ -33,135 +54,162 @@ __device__ __forceinline__ unsigned lanemask_lt() {
   return m;
 }
 
-// block_hist[d * nblocks + b] = number of keys of block b whose digit is d
-__global__ void __launch_bounds__(kRsThreads)
-radix_hist_kernel(const uint64_t *__restrict__ keys, int64_t n, int shift,
-                  uint32_t *__restrict__ block_hist, int nblocks) {
-  __shared__ uint32_t hist[kRadix];
-  for (int d = threadIdx.x; d < kRadix; d += kRsThreads) hist[d] = 0;
-  __syncthreads();
-  const int64_t tile0 = (int64_t)blockIdx.x * kRsTile;
-#pragma unroll 4
-  for (int c = 0; c < kRsItems; c++) {
-    int64_t i = tile0 + c * kRsThreads + threadIdx.x;
-    if (i < n) atomicAdd(&hist[(keys[i] >> shift) & (kRadix - 1)], 1u);
-  }
-  __syncthreads();
-  for (int d = threadIdx.x; d < kRadix; d += kRsThreads)
-    block_hist[(size_t)d * nblocks + blockIdx.x] = hist[d];
-}
+struct SortArgs {
+  uint64_t *keys[2];          // ping-pong buffers; the input (or the packed keys) sits in [0]
+  int32_t *vals[2];           // optional payloads
+  int64_t n;
+  int32_t begin_bit;
+  int32_t end_bit;            // < 0: the key layout's total_bits
+  int32_t has_vals;
+  int32_t iota_vals;          // first pass: the payload is the element index
+  uint32_t *hist;             // [kRadix][grid] digit-major
+  uint32_t *total;            // [kRadix]
+  int32_t *result_in_second;  // out (may be NULL): 1 when the result is in keys[1] / vals[1]
+  int32_t *ctrl;
+  // optional key construction in front of the first pass
+  const int32_t *coords;      // NULL: keys[0] already holds the keys
+  const int64_t *batch_dims;
+  int32_t ndim, num_clouds;
+  PackParams pack;
+};
 
-// One warp per digit: exclusive scan of that digit's row over the blocks, in
-// place, and the digit total.
-__global__ void __launch_bounds__(kRsThreads)
-radix_scan_kernel(uint32_t *__restrict__ block_hist, int nblocks,
-                  uint32_t *__restrict__ digit_total) {
-  const int lane = threadIdx.x & 31;
-  const int d = blockIdx.x * kRsWarps + (threadIdx.x >> 5);
-  uint32_t *row = block_hist + (size_t)d * nblocks;
-  uint32_t carry = 0;
-  for (int b0 = 0; b0 < nblocks; b0 += 32) {
-    int b = b0 + lane;
-    uint32_t v = b < nblocks ? row[b] : 0u;
-    uint32_t inc = v;
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, inc, s);
-      if (lane >= s) inc += t;
-    }
-    if (b < nblocks) row[b] = carry + inc - v;
-    carry += __shfl_sync(0xffffffffu, inc, 31);
-  }
-  if (lane == 0) digit_total[d] = carry;
-}
-
-// Stable scatter.  Warp w owns kRsItems*32 consecutive keys of the tile and walks
-// them in chunks of 32 consecutive keys; inside a chunk lanes with equal
-// digits find each other with match.any, the lowest lane bumps the warp's digit
-// counter, and every lane's rank is counter + number of equal lanes below it.
-template <bool kHasVals>
-__global__ void __launch_bounds__(kRsThreads)
-radix_scatter_kernel(const uint64_t *__restrict__ keys_in, const int32_t *__restrict__ vals_in,
-                     int64_t n, int shift, const uint32_t *__restrict__ block_hist, int nblocks,
-                     const uint32_t *__restrict__ digit_total,
-                     uint64_t *__restrict__ keys_out, int32_t *__restrict__ vals_out) {
-  __shared__ uint32_t s_cnt[kRsWarps][kRadix];
+__global__ void __launch_bounds__(kRsThreads, 1)
+radix_sort_kernel(const __grid_constant__ SortArgs a) {
+  extern __shared__ __align__(16) uint32_t s_cnt[];   // [kRsWarps][kRadix]
   __shared__ uint32_t s_base[kRadix];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < kRsWarps * kRadix; i += kRsThreads) (&s_cnt[0][0])[i] = 0;
-  {
-    // exclusive scan of the digit totals by warp 0 (kRadix / 32 digits per lane)
-    if (warp == 0) {
-      constexpr int kPerLane = kRadix / 32;
-      uint32_t v[kPerLane], sum = 0;
+  __shared__ uint32_t s_scan[kRsWarps];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = (int)gridDim.x, b = (int)blockIdx.x;
+  const unsigned lt = lanemask_lt();
+  const mn_keyspec &spec = spec_of(a.pack.spec);
+  const int end_bit = a.end_bit >= 0 ? a.end_bit : spec.total_bits;
+  int passes = (end_bit - a.begin_bit + kRsBits - 1) / kRsBits;
+  passes = passes < 1 ? 1 : (passes > 8 ? 8 : passes);
+
+  // chunk of this block and slice of this warp (multiples of 32 keys)
+  const int64_t groups = (a.n + 31) >> 5;
+  const int64_t g_per_block = (groups + G - 1) / G;
+  const int64_t c0 = min(a.n, (int64_t)b * g_per_block * 32);
+  const int64_t c1 = min(a.n, c0 + g_per_block * 32);
+  const int64_t g_per_warp = (g_per_block + kRsWarps - 1) / kRsWarps;
+  const int64_t w0 = min(c1, c0 + (int64_t)warp * g_per_warp * 32);
+  const int64_t w1 = min(c1, w0 + g_per_warp * 32);
+
+  if (a.coords != nullptr) {
+    // keys of this block's chunk from the coordinate rows (the block is the only
+    // reader of its chunk until the first scatter)
+    bool bad = false;
+    for (int64_t r = c0 + tid; r < c1; r += kRsThreads) {
+      int c[4] = {0, 0, 0, 0};
+      for (int k = 0; k < a.ndim; k++) c[k] = __ldg(a.coords + r * a.ndim + k);
+      const uint64_t g = a.batch_dims != nullptr ? cloud_of(a.batch_dims, a.num_clouds, r) : 0;
+      a.keys[0][r] = pack_one(c, a.ndim, g, spec, a.pack, bad);
+    }
+    if (bad) atomicOr(a.ctrl + MN_CTRL_STATUS, MN_STATUS_KEY_BOX);
+    __syncthreads();
+  }
+
+  for (int p = 0; p < passes; p++) {
+    const int shift = a.begin_bit + p * kRsBits;
+    const uint64_t *kin = a.keys[p & 1];
+    uint64_t *kout = a.keys[(p & 1) ^ 1];
+    // ---- A: per-warp digit counts ------------------------------------------------
+    {
+      uint4 *z = reinterpret_cast<uint4 *>(s_cnt);
+      for (int i = tid; i < kRsWarps * kRadix / 4; i += kRsThreads) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    uint32_t *mine = s_cnt + warp * kRadix;
+    for (int64_t i0 = w0; i0 < w1; i0 += 32) {
+      const int64_t i = i0 + lane;
+      const bool valid = i < w1;
+      // .cg loads: other blocks rewrote this buffer since this SM last read it
+      const unsigned d = valid ? (unsigned)((__ldcg(kin + i) >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+      const unsigned peers = __match_any_sync(0xffffffffu, d);
+      if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    for (int d = tid; d < kRadix; d += kRsThreads) {
+      uint32_t sum = 0;
+#pragma unroll 8
+      for (int w = 0; w < kRsWarps; w++) sum += s_cnt[w * kRadix + d];
+      a.hist[(size_t)d * G + b] = sum;
+    }
+    grid_barrier(a.ctrl, (unsigned)G);
+    // ---- B: per digit, exclusive prefix over the blocks -----------------------------
+    for (int d = b * kRsWarps + warp; d < kRadix; d += G * kRsWarps) {
+      uint32_t *row = a.hist + (size_t)d * G;
+      uint32_t carry = 0;
+      for (int b0 = 0; b0 < G; b0 += 32) {
+        const int bb = b0 + lane;
+        const uint32_t v = bb < G ? __ldcg(row + bb) : 0u;
+        uint32_t inc = v;
 #pragma unroll
-      for (int j = 0; j < kPerLane; j++) { v[j] = digit_total[lane * kPerLane + j]; sum += v[j]; }
-      uint32_t inc = sum;
+        for (int s = 1; s < 32; s <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, inc, s);
+          if (lane >= s) inc += t;
+        }
+        if (bb < G) row[bb] = carry + inc - v;
+        carry += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) a.total[d] = carry;
+    }
+    grid_barrier(a.ctrl, (unsigned)G);
+    // ---- C: positions, scatter --------------------------------------------------------
+    if (tid < kRadix) {
+      // exclusive scan of the digit totals over the first 512 threads (16 warps)
+      const uint32_t t = __ldcg(a.total + tid);
+      uint32_t inc = t;
 #pragma unroll
       for (int s = 1; s < 32; s <<= 1) {
-        uint32_t t = __shfl_up_sync(0xffffffffu, inc, s);
-        if (lane >= s) inc += t;
+        const uint32_t u = __shfl_up_sync(0xffffffffu, inc, s);
+        if (lane >= s) inc += u;
       }
-      uint32_t run = inc - sum;
-#pragma unroll
-      for (int j = 0; j < kPerLane; j++) { s_base[lane * kPerLane + j] = run; run += v[j]; }
+      if (lane == 31) s_scan[warp] = inc;
+      s_base[tid] = inc - t;
     }
-  }
-  __syncthreads();
-
-  const int64_t seg0 = (int64_t)blockIdx.x * kRsTile + warp * (kRsItems * 32);
-  uint64_t key[kRsItems];
-  uint32_t rank[kRsItems];
-  const unsigned lt = lanemask_lt();
-#pragma unroll
-  for (int c = 0; c < kRsItems; c++) {
-    const int64_t i = seg0 + c * 32 + lane;
-    const bool valid = i < n;
-    key[c] = valid ? keys_in[i] : 0ull;
-    const unsigned d = valid ? (unsigned)((key[c] >> shift) & (kRadix - 1)) : (unsigned)kRadix;
-    const unsigned peers = __match_any_sync(0xffffffffu, d);
-    const int leader = __ffs(peers) - 1;
-    uint32_t old = 0;
-    if (lane == leader && valid) {
-      old = s_cnt[warp][d];
-      s_cnt[warp][d] = old + __popc(peers);
+    __syncthreads();
+    if (tid < kRadix) {
+      uint32_t before = 0;
+      for (int w = 0; w < warp; w++) before += s_scan[w];
+      uint32_t run = s_base[tid] + before + __ldcg(a.hist + (size_t)tid * G + b);
+#pragma unroll 8
+      for (int w = 0; w < kRsWarps; w++) {
+        const uint32_t c = s_cnt[w * kRadix + tid];
+        s_cnt[w * kRadix + tid] = run;
+        run += c;
+      }
     }
-    old = __shfl_sync(0xffffffffu, old, leader);
-    rank[c] = old + __popc(peers & lt);
-    __syncwarp();
-  }
-  __syncthreads();
-  for (int d = threadIdx.x; d < kRadix; d += kRsThreads) {
-    uint32_t run = s_base[d] + block_hist[(size_t)d * nblocks + blockIdx.x];
-#pragma unroll
-    for (int w = 0; w < kRsWarps; w++) {
-      uint32_t t = s_cnt[w][d];
-      s_cnt[w][d] = run;
-      run += t;
+    __syncthreads();
+    const int32_t *vin = a.vals[p & 1];
+    int32_t *vout = a.vals[(p & 1) ^ 1];
+    const bool iota = a.iota_vals && p == 0;
+    for (int64_t i0 = w0; i0 < w1; i0 += 32) {
+      const int64_t i = i0 + lane;
+      const bool valid = i < w1;
+      const uint64_t key = valid ? __ldcg(kin + i) : 0ull;
+      const unsigned d = valid ? (unsigned)((key >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+      const unsigned peers = __match_any_sync(0xffffffffu, d);
+      uint32_t pos = 0;
+      if (valid) {
+        pos = mine[d] + __popc(peers & lt);
+        kout[pos] = key;
+        if (a.has_vals) vout[pos] = iota ? (int32_t)i : __ldcg(vin + i);
+      }
+      __syncwarp();
+      if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+      __syncwarp();
     }
+    if (p + 1 < passes) grid_barrier(a.ctrl, (unsigned)G);
   }
-  __syncthreads();
-#pragma unroll
-  for (int c = 0; c < kRsItems; c++) {
-    const int64_t i = seg0 + c * 32 + lane;
-    if (i < n) {
-      const unsigned d = (unsigned)((key[c] >> shift) & (kRadix - 1));
-      const uint32_t pos = s_cnt[warp][d] + rank[c];
-      keys_out[pos] = key[c];
-      if (kHasVals) vals_out[pos] = vals_in != nullptr ? vals_in[i] : (int32_t)i;
-    }
-  }
+  if (b == 0 && tid == 0 && a.result_in_second != nullptr) *a.result_in_second = passes & 1;
 }
 
 __global__ void widen_index_kernel(const int32_t *__restrict__ in, int64_t n,
                                    int64_t *__restrict__ out) {
   const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz) out[i] = in[i];
-}
-
-__global__ void iota_index_kernel(int64_t n, int64_t *__restrict__ out) {
-  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz) out[i] = i;
 }
 
 // ---------------------------------------------------------------------------
@@ -193,14 +241,6 @@ struct RowsView {  // sorted coordinate rows
       if (batch_dims[lo] == i + 1) return true;
     }
     return false;
-  }
-};
-
-struct KeysView {  // sorted packed keys; the cloud id is part of the key
-  const uint64_t *keys;
-  int64_t n;
-  __device__ __forceinline__ bool closes(int64_t i) const {
-    return i + 1 >= n || keys[i] != keys[i + 1];
   }
 };
 
@@ -281,22 +321,6 @@ struct CoordSink {  // reference-API unique: rows + inclusive index array
   }
 };
 
-struct KeySink {  // fused path: unique keys + unpacked coordinates
-  const uint64_t *keys;
-  mn_keyspec spec;
-  uint64_t *out_keys;
-  int32_t *out_rows;
-  __device__ __forceinline__ void index(int64_t, uint32_t) const {}
-  __device__ __forceinline__ void emit(int64_t i, uint32_t pos) const {
-    const uint64_t key = keys[i];
-    out_keys[pos] = key;
-    for (int k = 0; k < spec.ndim; k++) {
-      uint64_t f = (key >> spec.shift[k]) & ((1ull << spec.bits[k]) - 1ull);
-      out_rows[(int64_t)pos * spec.ndim + k] = (int32_t)((int64_t)f + spec.base[k]);
-    }
-  }
-};
-
 template <typename View, typename Sink>
 __global__ void __launch_bounds__(kUqThreads)
 unique_compact_kernel(const View v, const Sink sink, const uint32_t *__restrict__ block_offsets) {
@@ -332,30 +356,112 @@ unique_compact_kernel(const View v, const Sink sink, const uint32_t *__restrict_
   }
 }
 
-// out_bd[g] = number of unique keys whose cloud id is < g.  One warp per cloud
-// boundary: a 32-ary ballot search (4 rounds of loads for half a million keys
-// instead of the 19 dependent loads of a binary search).
-__global__ void __launch_bounds__(128)
-cloud_starts_kernel(const uint64_t *__restrict__ keys, const int64_t *__restrict__ count,
-                    int cloud_shift, int num_clouds, int64_t *__restrict__ out_bd) {
-  const int lane = threadIdx.x & 31;
-  const int g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (g > num_clouds) return;
-  const uint64_t q = (uint64_t)g << cloud_shift;
-  int64_t lo = 0, hi = *count;
-  for (int round = 0; round < 16; round++) {
-    const int64_t len = hi - lo;
-    if (len <= 0) break;
-    const int64_t stride = (len + 31) >> 5;
-    const int64_t idx = lo + (int64_t)(lane + 1) * stride - 1;
-    const bool pred = idx < hi && keys[idx] < q;
-    const int c = __popc(__ballot_sync(0xffffffffu, pred));
-    if (stride == 1) { lo += c; break; }
-    const int64_t nlo = min(lo + (int64_t)c * stride, hi);
-    hi = min(hi, nlo + stride - 1);
-    lo = nlo;
+// ---------------------------------------------------------------------------
+// unique over sorted keys (strided target coordinates): one cooperative kernel
+// ---------------------------------------------------------------------------
+// Every block owns a contiguous chunk of the sorted keys.  It counts the keys
+// that open a run (differ from their predecessor), a grid barrier later sums
+// the counts of the blocks before it, and walks the chunk again: every opening
+// key goes to its rank in keys_out, is unpacked into a coordinate row, and, when
+// it is the first key of its cloud, fills the cloud-start table.  The count,
+// the cloud starts and a copy of the status word land in one int64 block
+// (meta), so that the host needs a single small read.
+constexpr int kUkThreads = 1024;
+constexpr int kUkWarps = kUkThreads / 32;
+
+struct UniqueKeysArgs {
+  const uint64_t *keys[2];           // sorted keys are in keys[*which] (which may be NULL: keys[0])
+  const int32_t *which;
+  int64_t n;
+  SpecRef spec;
+  uint64_t *keys_out;                // [n]
+  int32_t *rows_out;                 // [n, ndim]
+  int64_t *meta;                     // [num_clouds + 3]: count, cloud starts [num_clouds + 1], status
+  int32_t num_clouds;
+  uint32_t *block_counts;            // workspace [grid]
+  int32_t *ctrl;
+};
+
+__global__ void __launch_bounds__(kUkThreads, 1)
+unique_keys_kernel(const __grid_constant__ UniqueKeysArgs a) {
+  __shared__ uint32_t s_warp[kUkWarps];
+  __shared__ uint32_t s_before, s_total;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = (int)gridDim.x, b = (int)blockIdx.x;
+  const unsigned lt = (1u << lane) - 1u;
+  const mn_keyspec &spec = spec_of(a.spec);
+  const uint64_t *keys = a.keys[a.which != nullptr ? (*a.which & 1) : 0];
+  const int64_t per_block = ((a.n + G - 1) / G + kUkThreads - 1) / kUkThreads * kUkThreads;
+  const int64_t c0 = min(a.n, (int64_t)b * per_block), c1 = min(a.n, c0 + per_block);
+
+  // ---- count the run openers of this chunk -------------------------------------
+  uint32_t mine = 0;
+  for (int64_t i = c0 + tid; i < c1; i += kUkThreads)
+    mine += (i == 0 || __ldcg(keys + i) != __ldcg(keys + i - 1)) ? 1u : 0u;
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  if (lane == 0) s_warp[warp] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t t = 0;
+    for (int w = 0; w < kUkWarps; w++) t += s_warp[w];
+    a.block_counts[b] = t;
   }
-  if (lane == 0) out_bd[g] = lo;
+  grid_barrier(a.ctrl, (unsigned)G);
+  if (warp == 0) {
+    uint32_t before = 0, all = 0;
+    for (int bb = lane; bb < G; bb += 32) {
+      const uint32_t v = __ldcg(a.block_counts + bb);
+      all += v;
+      if (bb < b) before += v;
+    }
+    before = __reduce_add_sync(0xffffffffu, before);
+    all = __reduce_add_sync(0xffffffffu, all);
+    if (lane == 0) { s_before = before; s_total = all; }
+  }
+  __syncthreads();
+  uint32_t run = s_before;
+  const uint32_t total = s_total;
+
+  // ---- compact, unpack, cloud starts ----------------------------------------------
+  for (int64_t i0 = c0; i0 < c1; i0 += kUkThreads) {
+    const int64_t i = i0 + tid;
+    uint64_t key = 0, prev = 0;
+    bool opens = false;
+    if (i < c1) {
+      key = __ldcg(keys + i);
+      prev = i > 0 ? __ldcg(keys + i - 1) : 0;
+      opens = i == 0 || key != prev;
+    }
+    const unsigned votes = __ballot_sync(0xffffffffu, opens);
+    __syncthreads();   // s_warp of the previous round has been read
+    if (lane == 0) s_warp[warp] = __popc(votes);
+    __syncthreads();
+    uint32_t pos = run + __popc(votes & lt);
+    uint32_t round_total = 0;
+    for (int w = 0; w < kUkWarps; w++) {
+      const uint32_t c = s_warp[w];
+      if (w < warp) pos += c;
+      round_total += c;
+    }
+    run += round_total;
+    if (opens) {
+      a.keys_out[pos] = key;
+      for (int k = 0; k < spec.ndim; k++) {
+        const uint64_t f = (key >> spec.shift[k]) & ((1ull << spec.bits[k]) - 1ull);
+        a.rows_out[(int64_t)pos * spec.ndim + k] = (int32_t)((int64_t)f + spec.base[k]);
+      }
+      // first key of cloud c: every cloud after the previous key's cloud starts here
+      const int64_t c_here = (int64_t)(key >> spec.cloud_shift);
+      const int64_t c_prev = i == 0 ? -1 : (int64_t)(prev >> spec.cloud_shift);
+      for (int64_t g = c_prev + 1; g <= c_here && g <= a.num_clouds; g++) a.meta[1 + g] = pos;
+    }
+  }
+  if (b == 0 && tid == 0) {
+    a.meta[0] = total;
+    const int64_t c_last = a.n > 0 ? (int64_t)(__ldcg(keys + a.n - 1) >> spec.cloud_shift) : -1;
+    for (int64_t g = c_last + 1; g <= a.num_clouds; g++) a.meta[1 + g] = total;
+    a.meta[a.num_clouds + 2] = a.ctrl[MN_CTRL_STATUS];
+  }
 }
 
 __global__ void zero_index0_kernel(int64_t *indices) { indices[0] = 0; }
@@ -363,49 +469,92 @@ __global__ void zero_index0_kernel(int64_t *indices) { indices[0] = 0; }
 }  // namespace
 
 size_t radix_sort_workspace_bytes(int64_t n) {
-  int64_t nblocks = std::max<int64_t>(1, div_up(n, kRsTile));
-  return align_up((size_t)nblocks * kRadix * sizeof(uint32_t), 256) + align_up(kRadix * sizeof(uint32_t), 256);
+  (void)n;
+  return align_up((size_t)kRsMaxBlocks * kRadix * sizeof(uint32_t), 256) +
+         align_up(kRadix * sizeof(uint32_t), 256) + 256;
 }
 
-// Stable LSD sort of `keys` on bits [begin_bit, end_bit), ping-ponging between
-// keys and keys_tmp.  With vals/vals_tmp given, int32 payloads move with the
-// keys; iota_vals makes the first pass use the element index as payload instead
-// of reading vals.  *result_in_tmp tells which buffers hold the result.
-mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals,
-                            int32_t *vals_tmp, bool iota_vals, int64_t n, int begin_bit,
-                            int end_bit, Workspace &ws, bool *result_in_tmp,
+namespace {
+
+// Grid of a cooperative kernel with one 1024-thread block per SM, cached per device.
+template <typename Kernel>
+mn_status coop_grid_1024(Kernel kernel, size_t smem, int *cache, int *out) {
+  int device = 0;
+  MN_CHECK_CUDA(cudaGetDevice(&device));
+  MN_CHECK_ARG(device >= 0 && device < kMaxDevices, "device index %d out of range", device);
+  if (cache[device] == 0) {
+    if (smem > 48 * 1024)
+      MN_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cache[device] = std::min(kRsMaxBlocks, max_coresident_blocks(kernel, 1024, smem));
+    if (cache[device] <= 0) {
+      cache[device] = 0;
+      set_error("cannot size a cooperative grid on device %d", device);
+      return MN_ERR_CUDA;
+    }
+  }
+  *out = cache[device];
+  return MN_OK;
+}
+
+}  // namespace
+
+// Stable LSD sort of `keys` on bits [begin_bit, end_bit) (end_bit < 0: up to the
+// key layout's total_bits, read on the device), ping-ponging between keys and
+// keys_tmp.  With vals/vals_tmp given, int32 payloads move with the keys;
+// iota_vals makes the first pass use the element index as payload.  With
+// `coords` given the first pass builds the keys itself (floor to pack.tstride,
+// pack).  Where the result ends up is written to *result_in_second_dev (device,
+// may be NULL) and, when end_bit is known on the host, to *result_in_tmp.
+mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals, int32_t *vals_tmp,
+                            bool iota_vals, int64_t n, int begin_bit, int end_bit,
+                            const mn_keyspec &spec, const SortSource *source, int32_t *ctrl,
+                            int32_t *result_in_second_dev, Workspace &ws, bool *result_in_tmp,
                             cudaStream_t st) {
-  *result_in_tmp = false;
+  if (result_in_tmp != nullptr) *result_in_tmp = false;
   if (n == 0) return MN_OK;
   MN_CHECK_ARG(n < (1ll << 31), "radix sort: n = %lld exceeds 2^31-1", (long long)n);
-  if (end_bit <= begin_bit) end_bit = begin_bit + 1;
-  const int nblocks = (int)div_up(n, kRsTile);
-  uint32_t *block_hist = ws.take<uint32_t>((size_t)nblocks * kRadix);
-  uint32_t *digit_total = ws.take<uint32_t>(kRadix);
+  MN_CHECK_ARG(ctrl != nullptr, "radix sort: null control block");
+  static thread_local int grid_cache[kMaxDevices] = {0};
+  int coresident = 0;
+  MN_RETURN_IF(coop_grid_1024(radix_sort_kernel, kRsSmemBytes, grid_cache, &coresident));
+  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, 2048)));
+  SortArgs a{};
+  a.keys[0] = keys; a.keys[1] = keys_tmp;
+  a.vals[0] = vals; a.vals[1] = vals_tmp;
+  a.n = n;
+  a.begin_bit = begin_bit;
+  a.end_bit = end_bit;
+  a.has_vals = vals != nullptr && vals_tmp != nullptr;
+  a.iota_vals = iota_vals ? 1 : 0;
+  a.hist = ws.take<uint32_t>((size_t)kRsMaxBlocks * kRadix);
+  a.total = ws.take<uint32_t>(kRadix);
   MN_CHECK_WS(ws);
-  const bool has_vals = vals != nullptr && vals_tmp != nullptr;
-  uint64_t *kin = keys, *kout = keys_tmp;
-  int32_t *vin = vals, *vout = vals_tmp;
-  bool first = true;
-  for (int shift = begin_bit; shift < end_bit; shift += kRsBits) {
-    MN_LAUNCH("radix_hist_kernel", st, radix_hist_kernel<<<nblocks, kRsThreads, 0, st>>>(kin, n, shift, block_hist, nblocks));
-    MN_LAUNCH("radix_scan_kernel", st, radix_scan_kernel<<<kRadix / kRsWarps, kRsThreads, 0, st>>>(block_hist, nblocks, digit_total));
-    {
-    LaunchScope scope("radix_scatter_kernel", st);
-    if (has_vals) {
-      radix_scatter_kernel<true><<<nblocks, kRsThreads, 0, st>>>(
-          kin, (first && iota_vals) ? nullptr : vin, n, shift, block_hist, nblocks,
-          digit_total, kout, vout);
-    } else {
-      radix_scatter_kernel<false><<<nblocks, kRsThreads, 0, st>>>(
-          kin, nullptr, n, shift, block_hist, nblocks, digit_total, kout, nullptr);
+  a.result_in_second = result_in_second_dev;
+  a.ctrl = ctrl;
+  a.pack.spec = make_spec_ref(spec);
+  a.pack.has_stride = 0;
+  for (int k = 0; k < 4; k++) a.pack.tstride[k] = 1;
+  if (source != nullptr) {
+    a.coords = source->coords;
+    a.batch_dims = source->batch_dims;
+    a.ndim = source->ndim;
+    a.num_clouds = source->batch_dims != nullptr ? (int)source->num_clouds : 1;
+    for (int k = 0; k < source->ndim; k++) {
+      a.pack.tstride[k] = source->tstride != nullptr ? source->tstride[k] : 1;
+      if (a.pack.tstride[k] != 1) a.pack.has_stride = 1;
     }
-    }
-    MN_CHECK_LAUNCH();
-    std::swap(kin, kout);
-    std::swap(vin, vout);
-    *result_in_tmp = !*result_in_tmp;
-    first = false;
+  }
+  void *params[] = {&a};
+  {
+    LaunchScope scope("radix_sort_kernel", st);
+    MN_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(radix_sort_kernel), dim3(grid),
+                                              dim3(kRsThreads), params, kRsSmemBytes, st));
+  }
+  MN_CHECK_LAUNCH();
+  if (result_in_tmp != nullptr && end_bit >= 0) {
+    int passes = (end_bit - begin_bit + kRsBits - 1) / kRsBits;
+    passes = std::min(8, std::max(1, passes));
+    *result_in_tmp = (passes & 1) != 0;
   }
   return MN_OK;
 }
@@ -432,11 +581,11 @@ extern "C" mn_status mn_arg_sort_coordinates(const int32_t *coords, int64_t n, i
   uint64_t *keys = ws.take<uint64_t>(n), *keys_tmp = ws.take<uint64_t>(n);
   int32_t *vals = ws.take<int32_t>(n), *vals_tmp = ws.take<int32_t>(n);
   MN_CHECK_WS(ws);
-  MN_RETURN_IF(launch_pack(coords, n, ndim, batch_dims, num_clouds, nullptr, *spec, keys,
-                           status_dev, st));
+  MN_CHECK_ARG(spec->device_copy == nullptr, "arg_sort: needs a key spec whose layout is known on the host");
+  SortSource source{coords, batch_dims, num_clouds, ndim, nullptr};
   bool in_tmp = false;
   MN_RETURN_IF(launch_radix_sort(keys, keys_tmp, vals, vals_tmp, true, n, 0, spec->total_bits,
-                                 ws, &in_tmp, st));
+                                 *spec, &source, status_dev, nullptr, ws, &in_tmp, st));
   const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, 256));
   MN_LAUNCH("widen_index_kernel", st, widen_index_kernel<<<blocks, 256, 0, st>>>(in_tmp ? vals_tmp : vals, n, index_out));
   return MN_OK;
@@ -469,48 +618,51 @@ extern "C" mn_status mn_unique_coordinates(const int32_t *coords, int64_t n, int
 extern "C" mn_status mn_downsample_coordinates(
     const int32_t *coords, int64_t n, int ndim, const int64_t *batch_dims, int64_t num_clouds,
     const int32_t *tstride, const mn_keyspec *spec, int32_t *unique_out, uint64_t *keys_out,
-    int64_t *out_batch_dims, int64_t *count_dev, int32_t *status_dev, void *ws_ptr,
-    size_t ws_bytes, void *stream) {
+    int64_t *meta_out, int32_t *ctrl, void *ws_ptr, size_t ws_bytes, void *stream) {
   MN_CHECK_ARG(n >= 0 && ndim >= 1 && ndim <= MN_MAX_NDIM, "downsample: bad n/ndim");
   MN_CHECK_ARG(spec != nullptr && spec->ndim == ndim, "downsample: key spec missing or of another ndim");
-  MN_CHECK_ARG(tstride != nullptr && count_dev != nullptr && status_dev != nullptr,
-               "downsample: null pointer");
+  MN_CHECK_ARG(tstride != nullptr && meta_out != nullptr && ctrl != nullptr, "downsample: null pointer");
   MN_CHECK_ARG(n < (1ll << 31), "downsample: n exceeds 2^31-1");
+  if (batch_dims == nullptr) num_clouds = 1;
+  MN_CHECK_ARG(num_clouds >= 1, "downsample: num_clouds must be >= 1");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (n == 0) {
-    MN_CHECK_CUDA(cudaMemsetAsync(count_dev, 0, sizeof(int64_t), st));
-    if (batch_dims != nullptr && out_batch_dims != nullptr)
-      MN_CHECK_CUDA(cudaMemsetAsync(out_batch_dims, 0, sizeof(int64_t) * (num_clouds + 1), st));
-    return MN_OK;
-  }
-  MN_CHECK_ARG(coords != nullptr && unique_out != nullptr && keys_out != nullptr,
+  MN_CHECK_ARG(n == 0 || (coords != nullptr && unique_out != nullptr && keys_out != nullptr),
                "downsample: null pointer");
   for (int k = 0; k < ndim; k++)
     MN_CHECK_ARG(tstride[k] >= 1 && tstride[k] - 1 <= spec->margin,
                  "downsample: stride %d needs a key margin >= %d (have %d)", tstride[k],
                  tstride[k] - 1, spec->margin);
   Workspace ws(ws_ptr, ws_bytes);
-  uint64_t *keys = ws.take<uint64_t>(n), *keys_tmp = ws.take<uint64_t>(n);
-  const int nblocks = (int)div_up(n, kUqTile);
-  uint32_t *counts = ws.take<uint32_t>(nblocks);
-  uint32_t *total = ws.take<uint32_t>(1);
+  uint64_t *keys = ws.take<uint64_t>(std::max<int64_t>(n, 1)), *keys_tmp = ws.take<uint64_t>(std::max<int64_t>(n, 1));
+  int32_t *which = ws.take<int32_t>(1);
+  uint32_t *block_counts = ws.take<uint32_t>(kRsMaxBlocks);
   MN_CHECK_WS(ws);
-  MN_RETURN_IF(launch_pack(coords, n, ndim, batch_dims, num_clouds, tstride, *spec, keys,
-                           status_dev, st));
-  bool in_tmp = false;
+  SortSource source{coords, batch_dims, num_clouds, ndim, tstride};
   MN_RETURN_IF(launch_radix_sort(keys, keys_tmp, nullptr, nullptr, false, n, 0,
-                                 spec->total_bits, ws, &in_tmp, st));
-  const uint64_t *sorted = in_tmp ? keys_tmp : keys;
-  KeysView view{sorted, n};
-  KeySink sink{sorted, *spec, keys_out, unique_out};
-  MN_LAUNCH("unique_count_kernel", st, unique_count_kernel<KeysView><<<nblocks, kUqThreads, 0, st>>>(view, counts));
-  MN_LAUNCH("scan_blocks_kernel", st, scan_blocks_kernel<<<1, 1024, 0, st>>>(counts, nblocks, total, count_dev));
-  MN_LAUNCH("unique_compact_kernel", st, unique_compact_kernel<KeysView, KeySink><<<nblocks, kUqThreads, 0, st>>>(view, sink, counts));
-  if (batch_dims != nullptr && out_batch_dims != nullptr) {
-    const int nb = (int)num_clouds + 1;
-    MN_LAUNCH("cloud_starts_kernel", st, cloud_starts_kernel<<<(nb + 3) / 4, 128, 0, st>>>(keys_out, count_dev, spec->cloud_shift,
-                                                           (int)num_clouds, out_batch_dims));
+                                 spec->device_copy != nullptr ? -1 : spec->total_bits, *spec,
+                                 &source, ctrl, which, ws, nullptr, st));
+  static thread_local int grid_cache[kMaxDevices] = {0};
+  int coresident = 0;
+  MN_RETURN_IF(coop_grid_1024(unique_keys_kernel, 0, grid_cache, &coresident));
+  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, 2048)));
+  UniqueKeysArgs a{};
+  a.keys[0] = keys; a.keys[1] = keys_tmp;
+  a.which = n > 0 ? which : nullptr;
+  a.n = n;
+  a.spec = make_spec_ref(*spec);
+  a.keys_out = keys_out;
+  a.rows_out = unique_out;
+  a.meta = meta_out;
+  a.num_clouds = (int)num_clouds;
+  a.block_counts = block_counts;
+  a.ctrl = ctrl;
+  void *params[] = {&a};
+  {
+    LaunchScope scope("unique_keys_kernel", st);
+    MN_CHECK_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(unique_keys_kernel), dim3(grid),
+                                              dim3(kUkThreads), params, 0, st));
   }
+  MN_CHECK_LAUNCH();
   return MN_OK;
 }
 
@@ -528,7 +680,6 @@ namespace {
 constexpr int64_t kStaticUniqueMaxRows = 16ll << 20;  // 16 Mi rows per call
 constexpr int kStaticUniqueBlocks = (int)(kStaticUniqueMaxRows / kUqTile);  // 8192 block counts
 constexpr int kStaticUniqueWords = kStaticUniqueBlocks + 64;                // + the total
-constexpr int kMaxDevices = 64;
 }  // namespace
 
 static __device__ __align__(256) uint32_t g_unique_scratch[kStaticUniqueWords];

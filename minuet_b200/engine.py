@@ -79,16 +79,29 @@ def as_i64(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 STATUS_KEY_BOX = 2
 STATUS_TC_TIMEOUT = 4
 STATUS_KEY_BITS = 8
+STATUS_GRID_TIMEOUT = 16
 _status = {}
 _pending_status = {}
 
 
+def control_block(device) -> torch.Tensor:
+    """The ``MN_CTRL_WORDS`` int32 control block of (device, current stream): word 0
+    is the status word, the rest is grid-barrier state of the cooperative kernels.
+    One block per stream, because kernels of different streams may overlap."""
+    dev = torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(index).cuda_stream)
+    block = _status.get(key)
+    if block is None:
+        block = torch.zeros(_lib.MN_CTRL_WORDS, dtype=torch.int32,
+                            device=torch.device("cuda", index))
+        _status[key] = block
+    return block
+
+
 def status_word(device) -> torch.Tensor:
-    key = torch.device(device).index if torch.device(device).index is not None \
-        else torch.cuda.current_device()
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    """One-element view of the status word (the start of the control block)."""
+    return control_block(device)[:1]
 
 
 def decode_status(value: int) -> Optional[Exception]:
@@ -106,9 +119,12 @@ def decode_status(value: int) -> Optional[Exception]:
         parts.append("a coordinate lies outside the bounding box the sort/search keys were "
                      "built for (call KernelMapCache.reset() before feeding unrelated "
                      "coordinates)")
-    if value & ~(STATUS_KEY_BOX | STATUS_TC_TIMEOUT | STATUS_KEY_BITS):
+    if value & STATUS_GRID_TIMEOUT:
+        parts.append("a grid-wide barrier of a cooperative kernel timed out: its outputs are "
+                     "invalid (MN_ERR_DEVICE)")
+    if value & ~(STATUS_KEY_BOX | STATUS_TC_TIMEOUT | STATUS_KEY_BITS | STATUS_GRID_TIMEOUT):
         parts.append(f"unknown device status bits 0x{value:x}")
-    if value & STATUS_KEY_BITS and not value & STATUS_TC_TIMEOUT:
+    if value & STATUS_KEY_BITS and not value & (STATUS_TC_TIMEOUT | STATUS_GRID_TIMEOUT):
         return NotImplementedError("; ".join(parts))
     return RuntimeError("; ".join(parts))
 
@@ -116,7 +132,7 @@ def decode_status(value: int) -> Optional[Exception]:
 def raise_on_status(value: int, device):
     error = decode_status(value)
     if error is not None:
-        status_word(device).zero_()
+        control_block(device).zero_()      # also resets the barrier state after a timeout
         raise error
 
 
@@ -170,6 +186,30 @@ def make_keyspec(coord_tensors: Sequence[torch.Tensor], ndim: int, num_clouds: i
     return spec
 
 
+def make_keyspec_device(coords: torch.Tensor, ndim: int, num_clouds: int, margin: int):
+    """Bounding box and key layout in one launch, left on the device (no read-back).
+    Returns ``(spec, spec_dev)``: the host struct only carries ndim, margin and the
+    pointer to ``spec_dev``, which must stay alive for as long as the spec is used."""
+    device = coords.device
+    spec = KeySpec()
+    spec_dev = torch.empty(256, dtype=torch.uint8, device=device)
+    ws = workspace(lib().mn_map_workspace_bytes(0, 0, 0), device)
+    _lib.check(lib().mn_keyspec_device(ptr(coords), coords.shape[0], ndim, max(int(num_clouds), 1),
+                                       int(margin), ptr(spec_dev), ctypes.byref(spec),
+                                       ptr(control_block(device)), ptr(ws), ws.numel(),
+                                       stream_ptr(device)), "keyspec_device")
+    return spec, spec_dev
+
+
+def read_small(t: torch.Tensor) -> np.ndarray:
+    """Blocking device-to-host read of a small tensor through pinned memory (one DMA
+    transfer, no kernel)."""
+    pinned = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    pinned.copy_(t, non_blocking=True)
+    torch.cuda.current_stream(t.device).synchronize()
+    return pinned.numpy().copy()
+
+
 def pack_keys(coords: torch.Tensor, batch_dims: Optional[torch.Tensor], spec: KeySpec,
               tstride: Optional[Sequence[int]] = None) -> torch.Tensor:
     n, ndim = coords.shape
@@ -189,17 +229,26 @@ _host_copies = {}
 
 
 class PendingHostCopy:
-    """Asynchronous device-to-host copies of a small tensor and of the status word
-    into pinned memory (two DMA transfers, no kernel); the wait happens when (and
-    if) the host needs the values."""
+    """Asynchronous device-to-host copy of a small int32 tensor whose LAST element
+    is a snapshot of the status word (one DMA transfer into pinned memory, no
+    kernel); the wait happens when (and if) the host needs the values."""
 
-    def __init__(self, values: torch.Tensor):
-        device = values.device
+    _pool = []
+
+    def __init__(self, values_and_status: torch.Tensor):
+        device = values_and_status.device
         self.device = device
-        self.pinned = torch.empty(values.shape, dtype=values.dtype, pin_memory=True)
-        self.pinned_status = torch.empty(1, dtype=torch.int32, pin_memory=True)
-        self.pinned.copy_(values, non_blocking=True)
-        self.pinned_status.copy_(status_word(device), non_blocking=True)
+        n = values_and_status.numel()
+        pinned = None
+        for i, buf in enumerate(self._pool):
+            if buf.numel() >= n:
+                pinned = self._pool.pop(i)
+                break
+        if pinned is None:
+            pinned = torch.empty(max(n, 160), dtype=torch.int32, pin_memory=True)
+        self.pinned = pinned
+        self.n = n
+        pinned[:n].copy_(values_and_status, non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record(torch.cuda.current_stream(device))
         self.values = None
@@ -207,9 +256,12 @@ class PendingHostCopy:
     def get(self) -> np.ndarray:
         if self.values is None:
             self.event.synchronize()
-            raise_on_status(int(self.pinned_status[0]), self.device)
-            self.values = np.ascontiguousarray(self.pinned.numpy().copy())
+            host = self.pinned[:self.n].numpy().copy()
+            if len(self._pool) < 64:
+                self._pool.append(self.pinned)
             self.pinned = None
+            raise_on_status(int(host[-1]), self.device)
+            self.values = np.ascontiguousarray(host[:-1])
         return self.values
 
 

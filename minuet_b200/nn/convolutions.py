@@ -46,6 +46,7 @@ class KernelMapCache(object):
         self._offsets_cache = dict()
         self._keys = dict()          # stride -> (coordinates tensor, keys tensor)
         self._spec = None
+        self._spec_dev = None        # device copy of the key layout (kept alive with the spec)
         self._root = None            # (coords int32, batch_dims int64, num_clouds)
 
     # -- bookkeeping ------------------------------------------------------------
@@ -54,6 +55,7 @@ class KernelMapCache(object):
         self._kernel_maps_cache.clear()
         self._keys.clear()
         self._spec = None
+        self._spec_dev = None
         self._root = None
 
     def _get_kernel_offsets(self, source_stride, kernel_size, kernel_dilation) -> np.ndarray:
@@ -74,8 +76,9 @@ class KernelMapCache(object):
                           1 if bd is None else bd.numel() - 1)
         if self._spec is None or self._spec.margin < margin:
             coords, _, num_clouds = self._root
-            self._spec = engine.make_keyspec([coords], self._ndim, num_clouds,
-                                             max(int(margin), engine.DEFAULT_MARGIN))
+            # bounding box and key layout stay on the device: no read-back here
+            self._spec, self._spec_dev = engine.make_keyspec_device(
+                coords, self._ndim, num_clouds, max(int(margin), engine.DEFAULT_MARGIN))
             self._keys.clear()
         return self._spec
 
@@ -122,16 +125,17 @@ class KernelMapCache(object):
         ts = np.asarray(target_stride, dtype=np.int32)
         unique = torch.empty((n, ndim), dtype=torch.int32, device=device)
         keys = torch.empty(n, dtype=torch.int64, device=device)
-        meta = torch.zeros(nb + 2, dtype=torch.int64, device=device)  # [count, batch_dims...]
+        meta = torch.empty(nb + 3, dtype=torch.int64, device=device)  # count, batch_dims, status
         lib = engine.lib()
         ws = engine.workspace(lib.mn_map_workspace_bytes(n, n, 1), device)
         _lib.check(lib.mn_downsample_coordinates(
             engine.ptr(coords), n, ndim, engine.ptr(bd), nb, engine.np_ptr(ts), ctypes.byref(spec),
-            engine.ptr(unique), engine.ptr(keys),
-            ctypes.c_void_p(meta.data_ptr() + 8) if bd is not None else None,
-            engine.ptr(meta), engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
+            engine.ptr(unique), engine.ptr(keys), engine.ptr(meta),
+            engine.ptr(engine.control_block(device)), engine.ptr(ws), ws.numel(),
             engine.stream_ptr(device)), "downsample_coordinates")
-        host = torch.cat([meta, engine.status_word(device).to(torch.int64)]).cpu().numpy()
+        # the one blocking read of a strided level: the number of output rows sets
+        # the shapes of everything that follows
+        host = engine.read_small(meta)
         engine.raise_on_status(int(host[-1]), device)
         count = int(host[0])
         target_coordinates = unique[:count]
@@ -140,6 +144,7 @@ class KernelMapCache(object):
         target_batch_dims = None
         if source_batch_dims is not None:
             target_batch_dims = meta[1:nb + 2].to(source_batch_dims.dtype)
+            engine.remember_host(target_batch_dims, host[1:nb + 2].copy())
         self._keys[target_stride] = (target_coordinates, keys[:count])
         self._coordinates_cache[target_stride] = (target_coordinates, target_stride,
                                                   target_batch_dims)
@@ -194,7 +199,8 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
     source_masks = torch.empty((O, S), dtype=torch.int32, device=device)
     target_masks = torch.empty((O, T), dtype=torch.int32, device=device)
     order = torch.empty(O, dtype=torch.int32, device=device)
-    sizes = torch.empty(O, dtype=torch.int32, device=device)
+    sizes_status = torch.empty(O + 1, dtype=torch.int32, device=device)   # sizes, status word
+    sizes = sizes_status[:O]
     ws = engine.workspace(lib.mn_map_workspace_bytes(S, T, O), device)
     stream = engine.stream_ptr(device)
     if O <= 32:
@@ -202,8 +208,9 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
         _lib.check(lib.mn_build_kernel_map(
             engine.ptr(source_keys), S, engine.ptr(source_keys if same else target_keys), T,
             engine.np_ptr(offsets), O, ctypes.byref(spec), int(reorder), engine.ptr(source_masks),
-            engine.ptr(target_masks), engine.ptr(order), engine.ptr(sizes), engine.ptr(ws),
-            ws.numel(), stream), "build_kernel_map")
+            engine.ptr(target_masks), engine.ptr(order), engine.ptr(sizes_status),
+            engine.ptr(engine.control_block(device)), engine.ptr(ws), ws.numel(), stream),
+            "build_kernel_map")
     else:
         kernel_map = torch.empty((O, T), dtype=torch.int32, device=device)
         _lib.check(lib.mn_query_sorted_index_with_offsets(
@@ -212,17 +219,19 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
         _lib.check(lib.mn_compute_kernel_map_sizes(engine.ptr(kernel_map), O, T, engine.ptr(sizes),
                                                    stream), "compute_kernel_map_sizes")
         if reorder:
-            sizes, order64 = torch.sort(sizes, stable=True)
+            sorted_sizes, order64 = torch.sort(sizes, stable=True)
+            sizes.copy_(sorted_sizes)
             order = order64.to(torch.int32)
             kernel_map = kernel_map[order64]
         else:
             order = torch.arange(O, dtype=torch.int32, device=device)
+        sizes_status[O:].copy_(engine.status_word(device))
         _lib.check(lib.mn_compute_kernel_map_masks(
             engine.ptr(kernel_map), O, S, T, engine.ptr(source_masks), engine.ptr(target_masks),
             engine.ptr(ws), ws.numel(), stream), "compute_kernel_map_masks")
     # the GEMM plan needs the sizes on the host: start the copy (sizes + status
     # word) now, wait for it only when a convolution asks
-    engine.remember_host(sizes, engine.PendingHostCopy(sizes))
+    engine.remember_host(sizes, engine.PendingHostCopy(sizes_status))
     return source_masks, target_masks, (order if reorder else None), sizes
 
 

@@ -2,7 +2,8 @@
 
 Tolerances: fp32 within 1e-5 relative (of the output scale); fp16 element-wise
 |got - want| <= 1e-2 * |want| + 1e-3 against an fp64-accumulated computation on
-the same rounded inputs (bf16, which keeps 8 mantissa bits: four times those bounds).
+the same rounded inputs (bf16 keeps 8 mantissa bits against fp16's 11, so its
+bounds are eight times wider; the reference has no bf16 path to compare with).
 """
 import numpy as np
 import pytest
@@ -28,8 +29,8 @@ def assert_close(got, want, dtype):
         assert np.abs(got - want).max() <= 1e-5 * scale, np.abs(got - want).max() / scale
     else:
         # fp16: 1e-2 relative / 1e-3 absolute, element-wise; bf16 keeps 8 mantissa
-        # bits (eps = 3.9e-3), so its bounds are 4x wider
-        k = 1.0 if dtype == torch.float16 else 4.0
+        # bits against 11, so its bounds are 8x wider
+        k = 1.0 if dtype == torch.float16 else 8.0
         np.testing.assert_allclose(got, want, rtol=k * 1e-2, atol=k * 1e-3)
 
 
