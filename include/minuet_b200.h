@@ -44,19 +44,22 @@ typedef enum { MN_F32 = 0, MN_F16 = 1, MN_BF16 = 2 } mn_dtype;
 #define MN_MAX_NDIM 4
 #define MN_MAX_OFFSETS 128
 
-/* Control block: MN_CTRL_WORDS int32 words of DEVICE memory that the caller
- * zeroes once and then keeps for as long as it uses the library on that
- * stream.  Word MN_CTRL_STATUS collects MN_STATUS_* bits raised by kernels;
- * the other words are the state of the grid-wide barrier that the cooperative
- * kernels (mask emission, radix sort, unique) share, which is back to zero
- * whenever no kernel is in flight.  Every parameter called `ctrl` or
- * `status_dev` below points at such a block.  Calls whose kernels may overlap
- * on the GPU (different streams) need a block each. */
-#define MN_CTRL_WORDS 64
+/* Control block: MN_CTRL_WORDS int32 words of DEVICE memory (256-byte aligned)
+ * that the caller zeroes once and then keeps for as long as it uses the library
+ * on that stream.  Word MN_CTRL_STATUS collects MN_STATUS_* bits raised by
+ * kernels; the rest is the state of the grid-wide barrier that the cooperative
+ * kernels (key build, radix sort, unique, mask emission) share: an arrival
+ * counter on a cache line of its own and MN_CTRL_GEN_COPIES copies of the
+ * generation word, 128 bytes apart, so that the polling blocks spread over
+ * several L2 lines instead of queueing behind the arrivals.  The barrier state
+ * is back to its idle value whenever no kernel is in flight.  Every parameter
+ * called `ctrl` or `status_dev` below points at such a block.  Calls whose
+ * kernels may overlap on the GPU (different streams) need a block each. */
+#define MN_CTRL_WORDS 1024
 #define MN_CTRL_STATUS 0
-#define MN_CTRL_BARRIER_COUNT 8
-#define MN_CTRL_BARRIER_GEN 9
-#define MN_CTRL_LAST_BLOCK 10
+#define MN_CTRL_BARRIER_COUNT 32      /* byte offset 128 */
+#define MN_CTRL_BARRIER_GEN 64        /* copy k at word MN_CTRL_BARRIER_GEN + 32 * k */
+#define MN_CTRL_GEN_COPIES 16
 
 #define MN_STATUS_KEY_BOX 2       /* a coordinate fell outside the key box              */
 #define MN_STATUS_TC_TIMEOUT 4    /* a bounded barrier wait of a tensor-core kernel ran out */
@@ -82,6 +85,11 @@ typedef struct {
   int64_t extent[MN_MAX_NDIM]; /* largest legal field value                   */
   const void *device_copy;     /* NULL, or a device mn_keyspec that overrides the layout above */
 } mn_keyspec;
+
+/* Version of this interface; mn_version() returns the value the library was
+ * built with.  A binding should refuse a library whose version differs from the
+ * header it was written against: argument lists change between versions. */
+#define MN_ABI_VERSION 8
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -115,18 +123,20 @@ mn_status mn_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb,
 mn_status mn_keyspec_make(const int32_t *minmax_host, int ndim,
                           int64_t num_clouds, int32_t margin, mn_keyspec *spec);
 
-/* Bounding box and key layout in one launch, entirely on the device: the layout
- * is written to spec_dev (device memory, at least sizeof(mn_keyspec) bytes,
- * 16-byte aligned, owned by the caller for as long as keys built from it are
- * in use) and never read back; *spec (host) is filled with ndim, margin and
- * device_copy = spec_dev and can be passed wherever a key spec is expected.
- * A box that needs more than 63 key bits raises MN_STATUS_KEY_BITS in the
- * status word.  Same role as mn_bbox + mn_keyspec_make without the
- * device-to-host read between them (the reference blocks on that read,
- * arg_sort_coodrinates.cu:286-287).  ctrl: the control block. */
+/* Bounding box, key layout and (when keys_out != NULL) the keys of the same rows
+ * in one launch, entirely on the device: the layout is written to spec_dev
+ * (device memory, at least sizeof(mn_keyspec) bytes, 16-byte aligned, owned by
+ * the caller for as long as keys built from it are in use) and never read
+ * back; *spec (host) is filled with ndim, margin and device_copy = spec_dev and
+ * can be passed wherever a key spec is expected.  A box that needs more than 63
+ * key bits raises MN_STATUS_KEY_BITS in the status word.  Same role as mn_bbox +
+ * mn_keyspec_make + mn_pack_keys without the device-to-host read between them
+ * (the reference blocks on that read, arg_sort_coodrinates.cu:286-287).
+ * ctrl: the control block. */
 mn_status mn_keyspec_device(const int32_t *coords, int64_t n, int ndim,
-                            int64_t num_clouds, int32_t margin, void *spec_dev,
-                            mn_keyspec *spec, int32_t *ctrl, void *ws, size_t ws_bytes,
+                            const int64_t *batch_dims, int64_t num_clouds,
+                            int32_t margin, void *spec_dev, mn_keyspec *spec,
+                            uint64_t *keys_out, int32_t *ctrl, void *ws, size_t ws_bytes,
                             void *stream);
 
 /* Pack coordinates into keys.  tstride (host, may be NULL) floors every
@@ -218,14 +228,19 @@ mn_status mn_compute_kernel_map_masks(const int32_t *kernel_map, int64_t O, int6
  * (order[p] = offset index at mask row p; identity when reorder == 0),
  * sizes_out int32 [O + 1]: sizes of the mask rows (i.e. sorted), followed by a
  * copy of the status word taken when the masks were written, so that one
- * device-to-host copy brings back both.  ctrl: the control block. */
+ * device-to-host copy brings back both.  source_bits_out uint32 [S] and
+ * target_bits_out uint32 [T] (each may be NULL) receive one word per row whose
+ * bit p is set when mask row p has an entry for that row: the forward kernels
+ * walk a row's pairs through these words instead of scanning O mask rows.
+ * ctrl: the control block. */
 mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
                               const uint64_t *target_keys, int64_t T,
                               const int32_t *offsets, int64_t O,
                               const mn_keyspec *spec, int reorder,
                               int32_t *source_masks_out, int32_t *target_masks_out,
-                              int32_t *order_out, int32_t *sizes_out, int32_t *ctrl,
-                              void *ws, size_t ws_bytes, void *stream);
+                              int32_t *order_out, int32_t *sizes_out,
+                              uint32_t *source_bits_out, uint32_t *target_bits_out,
+                              int32_t *ctrl, void *ws, size_t ws_bytes, void *stream);
 
 /* Upper bound of the workspace any Map-step entry point needs. */
 size_t mn_map_workspace_bytes(int64_t S, int64_t T, int64_t O);
@@ -299,6 +314,46 @@ mn_status mn_sparse_convolution_forward_implicit(
     const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
     const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
     void *targets_out, int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
+
+/* ---- Pair-list forward (sparse kernel maps) and dense forward ------------------ */
+/* Same result as mn_sparse_convolution_forward followed by mn_apply_epilogue, for
+ * fp16/bf16 and kernel maps that came out of mn_build_kernel_map with their hit
+ * words (source_bits / target_bits).  It replaces the reference's gather,
+ * bucket GEMMs, scatter and centre GEMM (sparse_convolution.cu:505-661) by:
+ * a pair list built once per kernel map (mn_build_pair_list: the source row of
+ * every product row; mask row p owns a 128-aligned block of mn_pair_rows rows in
+ * total), one tensor-core kernel that multiplies the listed rows and keeps the
+ * products in fp32, and the tensor-core GEMM of the centre offset (taken when
+ * allow_shortcut != 0 and the last mask row is the identity) whose epilogue adds
+ * each output row's other products, applies scale / shift / residual / ReLU and
+ * rounds once.  No mask row is scanned; where a pair exists one mask word is
+ * read.  Same shape limits as the fused implicit kernel. */
+int mn_pairs_supported(int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype);
+int64_t mn_pair_rows(const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
+                     int allow_shortcut);
+mn_status mn_build_pair_list(const int32_t *source_masks, const uint32_t *source_bits,
+                             const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
+                             int allow_shortcut, int32_t *pair_src_out, void *stream);
+size_t mn_pairs_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
+                                int64_t c_in, int64_t c_out, int allow_shortcut);
+mn_status mn_sparse_convolution_forward_pairs(
+    int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
+    const void *sources, const void *weights, const int32_t *target_masks,
+    const uint32_t *target_bits, const int32_t *pair_src, const int32_t *order,
+    const int32_t *sizes_host, int allow_shortcut, const float *scale, const float *shift,
+    const void *residual, int relu, void *targets_out, int32_t *status_dev, void *ws,
+    size_t ws_bytes, void *stream);
+
+/* out = relu?((features @ weights) * scale + shift + residual) on the tensor cores:
+ * the 1x1x1 convolution, for which the reference calls torch.mm
+ * (minuet/nn/convolutions.py:448-454).  fp16/bf16, c_in a multiple of 8, c_out
+ * even and at most 256; weights [c_in, c_out]; scale, shift, residual may be NULL. */
+int mn_dense_supported(int64_t c_in, int64_t c_out, mn_dtype dtype);
+size_t mn_dense_workspace_bytes(int64_t c_in, int64_t c_out);
+mn_status mn_dense_forward(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype dtype,
+                           const void *features, const void *weights, const float *scale,
+                           const float *shift, const void *residual, int relu, void *out,
+                           int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
 
 /* In place: features[t, c] = relu?(features[t, c] * scale[c] + shift[c] + residual[t, c]);
  * scale / shift (fp32 [channels]) and residual ([rows, channels], feature dtype)

@@ -14,7 +14,8 @@ MN_OK, MN_ERR_BAD_ARG, MN_ERR_UNSUPPORTED, MN_ERR_WORKSPACE, MN_ERR_CUDA, MN_ERR
 MN_F32, MN_F16, MN_BF16 = 0, 1, 2
 MN_MAX_NDIM = 4
 MN_MAX_OFFSETS = 128
-MN_CTRL_WORDS = 64
+MN_CTRL_WORDS = 1024
+ABI_VERSION = 8          # must equal MN_ABI_VERSION of the header the library was built from
 
 c_i32p = ctypes.c_void_p
 c_ptr = ctypes.c_void_p
@@ -59,8 +60,8 @@ PROTOTYPES = {
     "mn_downsample_coordinates": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr,
                                           ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_ptr, c_ptr,
                                           c_ptr, c_size, c_ptr]),
-    "mn_keyspec_device": (c_int, [c_ptr, c_i64, c_int, c_i64, ctypes.c_int32, c_ptr,
-                                  ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_size, c_ptr]),
+    "mn_keyspec_device": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, ctypes.c_int32, c_ptr,
+                                  ctypes.POINTER(KeySpec), c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_query_sorted_index_with_offsets": (c_int, [c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64,
                                                    ctypes.POINTER(KeySpec), c_ptr, c_ptr]),
     "mn_compute_kernel_map_sizes": (c_int, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
@@ -68,7 +69,7 @@ PROTOTYPES = {
                                             c_size, c_ptr]),
     "mn_build_kernel_map": (c_int, [c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_i64,
                                     ctypes.POINTER(KeySpec), c_int, c_ptr, c_ptr, c_ptr, c_ptr,
-                                    c_ptr, c_ptr, c_size, c_ptr]),
+                                    c_ptr, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_map_workspace_bytes": (c_size, [c_i64, c_i64, c_i64]),
     "mn_plan_buckets": (c_int, [c_ptr, c_i64, c_int, c_dbl, c_ptr, c_ptr, c_ptr]),
     "mn_conv_workspace_bytes": (c_size, [c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
@@ -90,6 +91,18 @@ PROTOTYPES = {
                                                        c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                                        c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr,
                                                        c_size, c_ptr]),
+    "mn_pairs_supported": (c_int, [c_i64, c_i64, c_i64, c_int]),
+    "mn_pair_rows": (c_i64, [c_ptr, c_i64, c_i64, c_i64, c_int]),
+    "mn_build_pair_list": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr]),
+    "mn_pairs_workspace_bytes": (c_size, [c_ptr, c_i64, c_i64, c_i64, c_i64, c_i64, c_int]),
+    "mn_sparse_convolution_forward_pairs": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_int,
+                                                    c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                                                    c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_int,
+                                                    c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+    "mn_dense_supported": (c_int, [c_i64, c_i64, c_int]),
+    "mn_dense_workspace_bytes": (c_size, [c_i64, c_i64]),
+    "mn_dense_forward": (c_int, [c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                                 c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
 }
 
 _lib = None
@@ -104,6 +117,11 @@ def load():
                 f"{LIB_PATH} is missing: build it with `python -m minuet_b200.build` "
                 "(nvcc, sm_100a). minuet_b200 has no CPU or PyTorch fallback.")
         lib = ctypes.CDLL(LIB_PATH)
+        lib.mn_version.restype = c_int
+        if lib.mn_version() != ABI_VERSION:
+            raise ImportError(
+                f"{LIB_PATH} implements interface version {lib.mn_version()}, this binding "
+                f"expects {ABI_VERSION}: rebuild it with `python -m minuet_b200.build`")
         for name, (restype, argtypes) in PROTOTYPES.items():
             fn = getattr(lib, name)
             fn.restype = restype

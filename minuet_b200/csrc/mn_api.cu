@@ -93,7 +93,7 @@ extern "C" int mn_profile_report(char *buf, int buf_bytes) {
 
 extern "C" const char *mn_last_error(void) { return g_error; }
 
-extern "C" int mn_version(void) { return 1; }
+extern "C" int mn_version(void) { return MN_ABI_VERSION; }
 
 extern "C" mn_status mn_bbox(const int32_t *a, int64_t na, const int32_t *b, int64_t nb, int ndim,
                              int32_t *minmax_dev, void *ws_ptr, size_t ws_bytes, void *stream) {

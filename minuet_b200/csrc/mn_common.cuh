@@ -76,6 +76,20 @@ struct LaunchScope {
     MN_CHECK_LAUNCH();                            \
   } while (0)
 
+// Optional phase timing of a kernel (builds with -DMN_PHASE_TIMING only): thread 0
+// of the first blocks stores its SM cycle counter at numbered points into a
+// file-local array that a debug entry point copies out.
+#ifdef MN_PHASE_TIMING
+#define MN_MARKS_DECL(name) static __device__ long long name[2048 * 16]
+#define MN_MARK(name, slot)                                                          \
+  do {                                                                               \
+    if (threadIdx.x == 0 && blockIdx.x < 2048) name[blockIdx.x * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define MN_MARKS_DECL(name)
+#define MN_MARK(name, slot) do {} while (0)
+#endif
+
 #define MN_RETURN_IF(expr)              \
   do {                                  \
     mn_status s__ = (expr);             \

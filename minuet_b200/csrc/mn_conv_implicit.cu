@@ -50,7 +50,24 @@ struct ImArgs {
   int32_t sub;         // 128-row sub-tiles per CTA tile (1 or 2): they share every weight tile
   int32_t acc_bufs;    // accumulator sets in TMEM (2 when 2 * sub * n_pad <= 512, else 1)
   int32_t n_tiles128;  // entries of tile_bits
+  // pair mode (step 1 of the pair-list forward): the rows are PRODUCT rows, row r reads
+  // source row nbr[r], every tile has exactly one "offset" whose weight matrix follows from
+  // the mask row that owns the tile, and the fp32 accumulators are stored as they are
+  int32_t pair_mode;
+  int32_t pair_rows;                            // mask rows in pair_tile_prefix
+  int32_t pair_tile_prefix[MN_MAX_PAIR_ROWS + 1];
+  float *out_f32;                               // [T, N]
 };
+
+// mask row that owns 128-row tile `tile` of the product buffer
+__device__ __forceinline__ int pair_row_of_tile(const ImArgs &a, int tile) {
+  int lo = 0, hi = a.pair_rows;   // last p with prefix[p] <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (a.pair_tile_prefix[mid] <= tile) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 
 // 16-byte asynchronous copy; src_bytes = 0 writes 16 zero bytes instead (the fill
 // travels the same path as the copies, so no proxy fence is needed for it)
@@ -118,8 +135,10 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       for (int h = 0; h < 2; h++) {
         t[h] = ((int64_t)tile * sub + h) * kBM + r;
         row_live[h] = h < sub && t[h] < args.T;
-        if (h < sub && tile * sub + h < args.n_tiles128) rest |= __ldg(args.tile_bits + tile * sub + h);
+        if (h < sub && tile * sub + h < args.n_tiles128)
+          rest |= args.pair_mode ? 1u : __ldg(args.tile_bits + tile * sub + h);
       }
+      const int pair_row = args.pair_mode ? pair_row_of_tile(args, tile) : 0;
       // software pipeline over the active offsets: the next offset's source rows are
       // requested before the current ones are copied
       int p = rest != 0u ? __ffs(rest) - 1 : -1;
@@ -142,7 +161,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           if (!ok) { alive = false; break; }
           uint8_t *sa = stage_base + (size_t)stage * args.stage_bytes;
           if (r == 0) {
-            const int widx = args.order != nullptr ? __ldg(args.order + p) : p;
+            const int wrow = args.pair_mode ? pair_row : p;
+            const int widx = args.order != nullptr ? __ldg(args.order + wrow) : wrow;
             mbar_expect_tx(&bar_full[stage], b_bytes);
             tma_load_3d(sa + args.a_bytes, &map_b, kb * kBK, 0, widx, &bar_full[stage]);
           }
@@ -187,7 +207,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * args.sub * args.n_pad);
         uint32_t tb = 0u;
         for (int h = 0; h < args.sub; h++)
-          if (tile * args.sub + h < args.n_tiles128) tb |= __ldg(args.tile_bits + tile * args.sub + h);
+          if (tile * args.sub + h < args.n_tiles128)
+            tb |= args.pair_mode ? 1u : __ldg(args.tile_bits + tile * args.sub + h);
         const int n_stage = __popc(tb) * args.k_blocks;
         uint32_t accumulate = 0u;
         for (int it = 0; it < n_stage; it++) {
@@ -227,7 +248,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t tb = 0u;
       for (int h = 0; h < args.sub; h++)
-        if (tile * args.sub + h < args.n_tiles128) tb |= __ldg(args.tile_bits + tile * args.sub + h);
+        if (tile * args.sub + h < args.n_tiles128)
+          tb |= args.pair_mode ? 1u : __ldg(args.tile_bits + tile * args.sub + h);
       const bool empty_tile = tb == 0u;   // no pair in the whole tile: no MMA ran, the rows are zero
       for (int h = 0; h < args.sub; h++) {
       const int out_row = (tile * args.sub + h) * kBM + quarter * 32;
@@ -246,6 +268,18 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           for (int i = 32; i < 64; i++) rr[i] = 0u;
         }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (args.out_f32 != nullptr) {
+          // pair mode: the fp32 accumulators of this row go out as they are
+          if (row < args.T) {
+            float4 *dst = reinterpret_cast<float4 *>(args.out_f32 + row * n + c0);
+#pragma unroll
+            for (int v = 0; v < 16; v++)
+              if (c0 + 4 * v < n)
+                dst[v] = make_float4(__uint_as_float(rr[4 * v]), __uint_as_float(rr[4 * v + 1]),
+                                     __uint_as_float(rr[4 * v + 2]), __uint_as_float(rr[4 * v + 3]));
+          }
+          continue;
+        }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         __syncwarp();
 #pragma unroll
@@ -366,6 +400,53 @@ neighbor_table_kernel(const int32_t *__restrict__ target_masks, int64_t T, int O
 }
 
 }  // namespace
+
+mn_status launch_pair_products(const PairPlan &plan, int64_t S, int64_t c_in, int64_t c_out, bool bf16,
+                               const void *sources, const void *weights_t, int O,
+                               const int32_t *pair_src, const int32_t *order, float *products,
+                               int32_t *status_dev, cudaStream_t st) {
+  (void)S;
+  MN_CHECK_ARG(plan.total_rows > 0 && plan.total_rows % kBM == 0 && plan.total_rows < (1ll << 31),
+               "pair products: bad product row count");
+  MN_CHECK_ARG(((reinterpret_cast<uintptr_t>(sources) | reinterpret_cast<uintptr_t>(products) |
+                 reinterpret_cast<uintptr_t>(weights_t)) & 15) == 0,
+               "pair products: arrays must be 16-byte aligned");
+  ImArgs a{};
+  a.in = static_cast<const uint8_t *>(sources);
+  a.nbr = pair_src;
+  a.tile_bits = nullptr;
+  a.order = order;
+  a.status = status_dev;
+  a.T = plan.total_rows;
+  a.K = (int)c_in;
+  a.N = (int)c_out;
+  a.n_pad = (int)align_up((size_t)c_out, 16);
+  a.k_blocks = (int)div_up(c_in, kBK);
+  a.n_tiles128 = (int)(plan.total_rows / kBM);
+  a.sub = 1;
+  a.acc_bufs = 2;
+  a.a_bytes = kBM * kBK * 2;
+  a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
+  a.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / a.stage_bytes));
+  a.elem_is_bf16 = bf16 ? 1 : 0;
+  a.num_tiles = a.n_tiles128;
+  a.pair_mode = 1;
+  a.pair_rows = plan.num_rows;
+  for (int p = 0; p <= MN_MAX_PAIR_ROWS; p++) a.pair_tile_prefix[p] = plan.tile_prefix[p];
+  a.out_f32 = products;
+  CUtensorMap map_b;
+  MN_RETURN_IF(make_kmajor_map(&map_b, weights_t, bf16, c_in, c_out, O, a.n_pad));
+  const size_t smem =
+      std::max<size_t>((size_t)a.stages * a.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
+  MN_CHECK_CUDA(cudaFuncSetAttribute(conv_implicit_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = std::min(a.num_tiles, kNumSMs);
+  // the output map is not used in pair mode; any valid map will do
+  MN_LAUNCH("conv_implicit_kernel<pairs>", st,
+            conv_implicit_kernel<<<grid, kImThreads, smem, st>>>(a, map_b, map_b));
+  return MN_OK;
+}
+
 }  // namespace mn
 
 using namespace mn;

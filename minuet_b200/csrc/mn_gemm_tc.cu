@@ -47,6 +47,10 @@ struct TcArgs {
   int32_t total_tiles;
   const int32_t *order;  // device, may be NULL
   int32_t *status;       // device status word (bit 2: bounded wait expired)
+  int32_t fused_epilogue; // direct problems: add product rows, scale/shift/residual/ReLU
+  int32_t plain_store;    // c_out is not a multiple of 8: rows leave with plain stores, no TMA
+  void *out_plain;        // [rows, c_out] output of the direct problem for plain_store
+  int64_t out_rows;
 };
 
 struct TilePos {
@@ -70,7 +74,8 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
                const __grid_constant__ CUtensorMap map_direct,  // input features [S, K]
                const __grid_constant__ CUtensorMap map_b,       // weights^T      [O, N, K]
                const __grid_constant__ CUtensorMap map_c,       // product buffer [rows, N]
-               const __grid_constant__ CUtensorMap map_c_direct) {  // output features [T, N]
+               const __grid_constant__ CUtensorMap map_c_direct,    // output features [T, N]
+               const __grid_constant__ PairEpilogue ep) {           // fused epilogue of direct problems
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kMaxStages], bar_empty[kMaxStages];
   __shared__ uint64_t bar_acc_full[2], bar_acc_empty[2];
@@ -194,6 +199,88 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
           for (int i = 32; i < 64; i++) r[i] = 0u;
         }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (direct && args.fused_epilogue) {
+          const int64_t t = (int64_t)out_row + lane;
+          const int n = args.c_out;
+          if (t < ep.T) {
+            if (ep.bits != nullptr) {
+              // the other offsets' products of this output row, named by its hit word
+              uint32_t w = __ldg(ep.bits + t) & ep.keep;
+              while (w != 0u) {
+                const int pr = __ffs(w) - 1;
+                w &= w - 1u;
+                const int m = __ldg(ep.target_masks + (int64_t)pr * ep.T + t);
+                if (m < 0) continue;
+                const float4 *src = reinterpret_cast<const float4 *>(
+                    ep.products + (ep.row_begin[pr] + m) * n + c0);
+#pragma unroll
+                for (int v = 0; v < 16; v++) {
+                  if (c0 + 4 * v < n) {
+                    const float4 a = __ldg(src + v);
+                    r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + a.x);
+                    r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + a.y);
+                    r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + a.z);
+                    r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + a.w);
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+              const int c = c0 + v * 8;
+              if (c < n) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[v * 8 + i]);
+                if (ep.scale != nullptr) {
+#pragma unroll
+                  for (int i = 0; i < 8; i++) f[i] *= __ldg(ep.scale + c + i);
+                }
+                if (ep.shift != nullptr) {
+#pragma unroll
+                  for (int i = 0; i < 8; i++) f[i] += __ldg(ep.shift + c + i);
+                }
+                if (ep.residual != nullptr) {
+                  const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(
+                      static_cast<const uint8_t *>(ep.residual) + (t * n + c) * 2));
+                  const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
+#pragma unroll
+                  for (int i = 0; i < 8; i++)
+                    f[i] += args.elem_is_bf16 ? __uint_as_float((uint32_t)r16[i] << 16)
+                                              : __half2float(__ushort_as_half(r16[i]));
+                }
+                if (ep.relu) {
+#pragma unroll
+                  for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) r[v * 8 + i] = __float_as_uint(f[i]);
+              }
+            }
+          }
+        }
+        if (args.plain_store) {
+          // row pitch not a multiple of 16 bytes: no tensor map exists for this output
+          const int64_t t = (int64_t)out_row + lane;
+          if (t < args.out_rows) {
+            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(args.out_plain) +
+                                                         t * args.c_out + c0);
+#pragma unroll
+            for (int h = 0; h < 32; h++) {
+              if (c0 + 2 * h + 1 < args.c_out) {
+                const float lo = __uint_as_float(r[2 * h]), hi = __uint_as_float(r[2 * h + 1]);
+                if (args.elem_is_bf16) {
+                  __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+                  dst[h] = *reinterpret_cast<uint32_t *>(&pk);
+                } else {
+                  __half2 pk = __floats2half2_rn(lo, hi);
+                  dst[h] = *reinterpret_cast<uint32_t *>(&pk);
+                }
+              }
+            }
+          }
+          continue;
+        }
         // the store that last read this buffer (two chunks ago) must be done with it
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         __syncwarp();
@@ -339,17 +426,74 @@ bool gemm_tc_supported(int c_in, int c_out, mn_dtype dtype) {
          c_out % 8 == 0 && c_out <= 256;
 }
 
+namespace {
+
+mn_status launch_gemm_tc_impl(const GemmTable &tab_in, const TcOperands &ops, int c_in, int c_out,
+                              mn_dtype dtype, const void *weights, const int32_t *order,
+                              const PairEpilogue *ep, bool weights_are_transposed, cudaStream_t st,
+                              bool *handled);
+
+}  // namespace
+
 mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_in, int c_out,
                          mn_dtype dtype, const void *weights, const int32_t *order,
                          cudaStream_t st, bool *handled) {
+  return launch_gemm_tc_impl(tab_in, ops, c_in, c_out, dtype, weights, order, nullptr, false, st,
+                             handled);
+}
+
+// Dense product of `rows` input rows with the weight matrix of mask row `centre`
+// (weights_t: already transposed [O, c_out, c_in]) and the fused epilogue.
+mn_status launch_centre_gemm(int64_t rows, int64_t c_in, int64_t c_out, bool bf16, const void *sources,
+                             const void *weights_t, int O, int centre, const int32_t *order,
+                             const PairEpilogue &ep, void *out, int32_t *status_dev, cudaStream_t st) {
+  GemmTable tab{};
+  tab.num_problems = 1;
+  tab.rows[0] = (int32_t)rows;
+  tab.weight_row[0] = centre;
+  tab.a[0] = sources;
+  tab.c[0] = out;
+  tab.a_row[0] = 0;
+  tab.direct[0] = 1;
+  TcOperands ops;
+  ops.sources = sources;
+  ops.source_rows = rows;
+  ops.out = out;
+  ops.out_rows = rows;
+  ops.weights_t = const_cast<void *>(weights_t);
+  ops.num_weights = O;
+  ops.status = status_dev;
+  bool handled = false;
+  MN_RETURN_IF(launch_gemm_tc_impl(tab, ops, (int)c_in, (int)c_out, bf16 ? MN_BF16 : MN_F16, nullptr,
+                                   order, &ep, true, st, &handled));
+  if (!handled) {
+    set_error("centre GEMM: shape not covered by the tensor-core kernel (c_in=%lld c_out=%lld)",
+              (long long)c_in, (long long)c_out);
+    return MN_ERR_UNSUPPORTED;
+  }
+  return MN_OK;
+}
+
+namespace {
+
+mn_status launch_gemm_tc_impl(const GemmTable &tab_in, const TcOperands &ops, int c_in, int c_out,
+                              mn_dtype dtype, const void *weights, const int32_t *order,
+                              const PairEpilogue *ep, bool weights_are_transposed, cudaStream_t st,
+                              bool *handled) {
   *handled = false;
-  if (!gemm_tc_supported(c_in, c_out, dtype) || ops.weights_t == nullptr || ops.status == nullptr)
+  // a dense problem with the fused epilogue also takes even c_out that are not a multiple
+  // of 8 (the rows then leave with plain stores instead of through a tensor map)
+  const bool plain_store = ep != nullptr && c_out % 8 != 0 && c_out % 2 == 0 && c_out <= 256 &&
+                           c_in >= 8 && c_in % 8 == 0 && (dtype == MN_F16 || dtype == MN_BF16);
+  if ((!gemm_tc_supported(c_in, c_out, dtype) && !plain_store) || ops.weights_t == nullptr ||
+      ops.status == nullptr)
     return MN_OK;
   const bool bf16 = dtype == MN_BF16;
   const int O = ops.num_weights;
 
   // weights [O, K, N] -> [O, N, K]
-  MN_RETURN_IF(launch_transpose_weights(weights, ops.weights_t, O, c_in, c_out, bf16, st));
+  if (!weights_are_transposed)
+    MN_RETURN_IF(launch_transpose_weights(weights, ops.weights_t, O, c_in, c_out, bf16, st));
 
   GemmTable tab = tab_in;
   tab.tile_rows = kBM;
@@ -371,6 +515,12 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
   args.total_tiles = total_tiles;
   args.order = order;
   args.status = ops.status;
+  args.fused_epilogue = ep != nullptr ? 1 : 0;
+  args.plain_store = plain_store ? 1 : 0;
+  args.out_plain = ops.out;
+  args.out_rows = ops.out_rows;
+  static const PairEpilogue no_epilogue{};
+  const PairEpilogue &epilogue = ep != nullptr ? *ep : no_epilogue;
 
   CUtensorMap map_a, map_direct, map_b, map_c, map_c_direct;
   // an operand that no problem uses still needs a valid map: point it at the other one
@@ -395,8 +545,13 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
                    (reinterpret_cast<uintptr_t>(prod_base) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(out_base) & 15) == 0,
                "gemm_tc: outputs must exist and be 16-byte aligned");
-  MN_RETURN_IF(make_kmajor_map(&map_c, prod_base, bf16, c_out, prod_rows, 0, 32));
-  MN_RETURN_IF(make_kmajor_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
+  if (plain_store) {
+    map_c = map_b;          // never used: the epilogue stores the rows itself
+    map_c_direct = map_b;
+  } else {
+    MN_RETURN_IF(make_kmajor_map(&map_c, prod_base, bf16, c_out, prod_rows, 0, 32));
+    MN_RETURN_IF(make_kmajor_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
+  }
 
   // at least 120 KB so that two CTAs (each allocating all 512 TMEM columns) can
   // never share an SM
@@ -408,16 +563,19 @@ mn_status launch_gemm_tc(const GemmTable &tab_in, const TcOperands &ops, int c_i
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MN_LAUNCH("gemm_tc_kernel", st,
               gemm_tc_kernel<__nv_bfloat16><<<grid, kTcThreads, smem, st>>>(
-                  tab, args, map_a, map_direct, map_b, map_c, map_c_direct));
+                  tab, args, map_a, map_direct, map_b, map_c, map_c_direct, epilogue));
   } else {
     MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__half>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MN_LAUNCH("gemm_tc_kernel", st,
               gemm_tc_kernel<__half><<<grid, kTcThreads, smem, st>>>(tab, args, map_a, map_direct,
-                                                                    map_b, map_c, map_c_direct));
+                                                                    map_b, map_c, map_c_direct,
+                                                                    epilogue));
   }
   *handled = true;
   return MN_OK;
 }
+
+}  // namespace
 
 }  // namespace mn

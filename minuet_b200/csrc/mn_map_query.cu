@@ -14,12 +14,12 @@
 // warp-cooperative 32-ary ballot searches find the window of the sorted table
 // (sources) that can match the tile over all offsets; the window is staged in
 // shared memory as a hash set of CELLS (32 consecutive values of the last
-// dimension -> {cell id, 32-bit occupancy}).  Every key is entered twice, once
-// in the cells aligned at 0 and once in the cells aligned at 16, so that any
-// strip of up to 17 consecutive last-dimension values lies inside ONE cell of
-// one of the two families: offsets that differ only in the last dimension (a
-// "group", split so that its span is at most 16) are answered by a single
-// two-bucket probe per row.  Tiles whose window does not fit the hash are
+// dimension -> {cell id, 32-bit occupancy}, 8-byte slots, linear probing): the
+// offsets that differ only in the last dimension (a "group", split so that its
+// span is at most 16) are answered by ONE lookup per row, plus a second one for
+// the few rows whose strip crosses a cell boundary; shared-memory bandwidth, not
+// instruction issue, is what bounds this kernel, hence the 64-bit single-slot
+// lookups.  Tiles whose window does not fit the hash are
 // processed group range by group range, and ranges that still do not fit fall
 // back to binary search in global memory.  The kernel writes kernel-map rows
 // or, for the fused build, one 32-bit word of per-offset hit bits per row.
@@ -49,9 +49,8 @@ constexpr int kQThreads = 256;
 constexpr int kQWarps = kQThreads / 32;
 constexpr int kQRows = 2;                    // rows per thread
 constexpr int kQTile = kQThreads * kQRows;   // 512 rows per block
-constexpr int kQSlots = 4096;                // hash slots of 8 bytes; two per bucket
-constexpr int kQBuckets = kQSlots / 2;
-constexpr int kQMaxWindow = 1280;            // table keys per hashed stage (two entries each)
+constexpr int kQSlots = 4096;                // hash slots of 8 bytes: {cell, occupancy}
+constexpr int kQMaxWindow = 1280;            // table keys per hashed stage (load factor <= 0.31)
 constexpr int kQMaxSpan = 16;                // last-dimension span of one group
 constexpr uint32_t kQPad = 64;               // relative keys start at kQPad
 constexpr uint32_t kHashEmpty = 0xffffffffu;
@@ -113,63 +112,37 @@ struct SearchPair {
 // (one search then serves both masks of a map whose two sides differ).
 enum SearchMode { kMap = 0, kBits = 1, kBitsRev = 2 };
 
-__device__ __forceinline__ uint32_t hash_bucket(uint32_t k) {
-  return (k * 0x9E3779B1u) >> 21;  // top 11 bits: 2048 buckets
+MN_MARKS_DECL(g_marks_search);
+MN_MARKS_DECL(g_marks_emit);
+
+__device__ __forceinline__ uint32_t hash_slot(uint32_t c) {
+  return (c * 0x9E3779B1u) >> 20;  // top 12 bits: 4096 slots
 }
 
-// Occupancy mask of cell key c (0 when absent) and the slot that holds it.  The
-// home bucket and its successor are read up front with two 16-byte loads and
-// compared without branches; only a cell pushed further than that (rare at
-// these load factors) takes the loop, so the lanes of a warp stay converged.
-// Inserts fill slot 0 of a bucket first, then slot 1, then move on to the next
-// bucket, so a bucket whose slot 1 is empty never overflowed.
-template <bool kWantSlot>
+// Occupancy mask of cell c (0 when absent) and the slot that holds it: linear
+// probing over 8-byte {cell, mask} slots, one 64-bit shared-memory load per step.
+// At the load factors used (<= 0.31) most lookups end at the first slot.
 __device__ __forceinline__ uint32_t find_cell(const uint2 *slots, uint32_t c, uint32_t *slot) {
-  const uint4 *buckets = reinterpret_cast<const uint4 *>(slots);
-  uint32_t b = hash_bucket(c);
-  const uint4 a0 = buckets[b];
-  const uint32_t b1 = (b + 1) & (kQBuckets - 1);
-  const uint4 a1 = buckets[b1];
-  uint32_t m = a0.x == c ? a0.y : 0u;
-  m = a0.z == c ? a0.w : m;
-  m = a1.x == c ? a1.y : m;
-  m = a1.z == c ? a1.w : m;
-  if (kWantSlot) {
-    uint32_t h = 2 * b;
-    h = a0.z == c ? 2 * b + 1 : h;
-    h = a1.x == c ? 2 * b1 : h;
-    h = a1.z == c ? 2 * b1 + 1 : h;
-    *slot = h;
+  uint32_t h = hash_slot(c);
+  for (int probe = 0; probe < kQSlots; probe++) {
+    const uint2 v = slots[h];
+    if (v.x == c) { *slot = h; return v.y; }
+    if (v.x == kHashEmpty) break;
+    h = (h + 1) & (kQSlots - 1);
   }
-  if (m == 0u && a0.z != kHashEmpty && a1.z != kHashEmpty) {   // both buckets full, no match
-    b = b1;
-    for (int probe = 2; probe < kQBuckets; probe++) {
-      b = (b + 1) & (kQBuckets - 1);
-      const uint4 v = buckets[b];
-      if (v.x == c) { if (kWantSlot) *slot = 2 * b; return v.y; }
-      if (v.z == c) { if (kWantSlot) *slot = 2 * b + 1; return v.w; }
-      if (v.z == kHashEmpty) break;
-    }
-  }
-  return m;
+  *slot = 0;
+  return 0u;
 }
 
 __device__ __forceinline__ uint32_t insert_cell(uint2 *slots, uint32_t c, uint32_t bit) {
-  uint32_t b = hash_bucket(c), h = 0;
-  for (int probe = 0; probe < kQBuckets; probe++) {
-    uint32_t old = atomicCAS(&slots[2 * b].x, kHashEmpty, c);
-    if (old == kHashEmpty || old == c) { h = 2 * b; break; }
-    old = atomicCAS(&slots[2 * b + 1].x, kHashEmpty, c);
-    if (old == kHashEmpty || old == c) { h = 2 * b + 1; break; }
-    b = (b + 1) & (kQBuckets - 1);
+  uint32_t h = hash_slot(c);
+  for (int probe = 0; probe < kQSlots; probe++) {
+    const uint32_t old = atomicCAS(&slots[h].x, kHashEmpty, c);
+    if (old == kHashEmpty || old == c) break;
+    h = (h + 1) & (kQSlots - 1);
   }
   atomicOr(&slots[h].y, 1u << bit);
   return h;
-}
-
-// Cell key of relative key k in family 0 (cells aligned at 0) or 1 (aligned at 16).
-__device__ __forceinline__ uint32_t cell_key(uint32_t k, uint32_t family) {
-  return (((k + 16u * family) >> 5) << 1) | family;
 }
 
 template <int kMode>
@@ -199,6 +172,7 @@ search_kernel(const __grid_constant__ SearchPair sp) {
   const int64_t tile0 = (int64_t)bid * kQTile;
   const int tile_rows = (int)min((int64_t)kQTile, a.n_rows - tile0);
   const int64_t row0 = tile0 + tid * kQRows;
+  MN_MARK(g_marks_search, 0);
 
   for (int o = tid; o < O; o += kQThreads) {
     int64_t d = 0;
@@ -237,6 +211,7 @@ search_kernel(const __grid_constant__ SearchPair sp) {
   const uint64_t kfirst = __ldg(a.rows + tile0);
   const uint64_t klast = __ldg(a.rows + tile0 + tile_rows - 1);
   __syncthreads();
+  MN_MARK(g_marks_search, 1);
 
   // window of the table over all offsets: members are ordered by delta
   if (warp < 2) {
@@ -294,6 +269,7 @@ search_kernel(const __grid_constant__ SearchPair sp) {
     }
   }
   __syncthreads();
+  MN_MARK(g_marks_search, 2);
 
   uint32_t bits[kQRows] = {0u, 0u};
   const bool vec_ok = kMode == kMap && (a.n_rows & 1) == 0 &&
@@ -313,23 +289,23 @@ search_kernel(const __grid_constant__ SearchPair sp) {
       {
         uint4 *clear = reinterpret_cast<uint4 *>(s_slots);
         for (int i = tid; i < kQSlots / 2; i += kQThreads)
-          clear[i] = make_uint4(kHashEmpty, 0u, kHashEmpty, 0u);
+          clear[i] = make_uint4(kHashEmpty, 0u, kHashEmpty, 0u);   // two {cell, mask} slots
       }
       __syncthreads();
+      MN_MARK(g_marks_search, 3);
       // relative keys start at kQPad, so that a query below the window stays non-negative
       for (int w = tid; w < wn; w += kQThreads) {
         const uint32_t k = (uint32_t)(__ldg(a.table + lo + w) - base) + kQPad;
-        const uint32_t h0 = insert_cell(s_slots, cell_key(k, 0u), k & 31u);
-        const uint32_t h1 = insert_cell(s_slots, cell_key(k, 1u), (k + 16u) & 31u);
+        const uint32_t h = insert_cell(s_slots, k >> 5, k & 31u);
         if (kPos) {
           // the table is sorted: exactly one key of a cell has a predecessor in another cell
           uint32_t pk = 0;
           if (w > 0) pk = (uint32_t)(__ldg(a.table + lo + w - 1) - base) + kQPad;
-          if (w == 0 || cell_key(pk, 0u) != cell_key(k, 0u)) s_hpos[h0] = (uint16_t)w;
-          if (w == 0 || cell_key(pk, 1u) != cell_key(k, 1u)) s_hpos[h1] = (uint16_t)w;
+          if (w == 0 || (pk >> 5) != (k >> 5)) s_hpos[h] = (uint16_t)w;
         }
       }
       __syncthreads();
+      MN_MARK(g_marks_search, 4);
       int64_t rel[kQRows];
 #pragma unroll
       for (int j = 0; j < kQRows; j++)   // a dead row gets a value that no window can reach
@@ -339,20 +315,28 @@ search_kernel(const __grid_constant__ SearchPair sp) {
         const uint32_t meta = s_gmeta[g];
         const uint32_t e_span = meta & 0xffu, o_first = (meta >> 8) & 0xffu,
                        members = (meta >> 16) & 0xffu;
-        uint32_t sh[kQRows], mask[kQRows], slot[kQRows];
+        // per row: the strip of last-dimension values [q0, q0 + 31] as one 32-bit mask, from
+        // the cell of q0 and, when the group reaches past its end, the next cell
+        uint32_t sh[kQRows], mlo[kQRows], mhi[kQRows], slo[kQRows], shi[kQRows];
 #pragma unroll
         for (int j = 0; j < kQRows; j++) {
           const uint64_t t0 = (uint64_t)(rel[j] + dg);
           const uint32_t q0 = (uint32_t)t0;
-          const uint32_t fam = ((q0 & 31u) + e_span > 31u) ? 1u : 0u;
-          sh[j] = (q0 + 16u * fam) & 31u;
-          const uint32_t m = find_cell<kPos>(s_slots, cell_key(q0, fam), &slot[j]);
-          mask[j] = t0 < kRelLimit ? m : 0u;
+          const bool ok = t0 < kRelLimit;
+          sh[j] = q0 & 31u;
+          slo[j] = shi[j] = 0u;
+          mlo[j] = mhi[j] = 0u;
+          if (ok) {
+            mlo[j] = find_cell(s_slots, q0 >> 5, &slo[j]);
+            if (sh[j] + e_span > 31u) mhi[j] = find_cell(s_slots, (q0 >> 5) + 1u, &shi[j]);
+          }
         }
         if (kMode == kBits && (meta >> 24) != 0u) {
 #pragma unroll
-          for (int j = 0; j < kQRows; j++)
-            bits[j] |= ((mask[j] >> sh[j]) & ((1u << members) - 1u)) << o_first;
+          for (int j = 0; j < kQRows; j++) {
+            const uint32_t strip = (uint32_t)((((uint64_t)mhi[j] << 32) | mlo[j]) >> sh[j]);
+            bits[j] |= (strip & ((1u << members) - 1u)) << o_first;
+          }
           continue;
         }
         const int mb = tab.group_begin[g], me = mb + (int)members;
@@ -362,14 +346,22 @@ search_kernel(const __grid_constant__ SearchPair sp) {
           const int de = tab.off[o][last] - e_first;
           if (kMode == kBits) {
 #pragma unroll
-            for (int j = 0; j < kQRows; j++) bits[j] |= ((mask[j] >> (sh[j] + de)) & 1u) << o;
+            for (int j = 0; j < kQRows; j++) {
+              const uint64_t both = ((uint64_t)mhi[j] << 32) | mlo[j];
+              bits[j] |= ((uint32_t)(both >> (sh[j] + de)) & 1u) << o;
+            }
           } else {
             int32_t idx[kQRows];
 #pragma unroll
             for (int j = 0; j < kQRows; j++) {
-              const uint32_t b = sh[j] + (uint32_t)de;
-              idx[j] = ((mask[j] >> b) & 1u)
-                           ? (int32_t)(lo + s_hpos[slot[j]] + __popc(mask[j] & ((1u << b) - 1u))) : -1;
+              const uint32_t b = sh[j] + (uint32_t)de;   // < 48
+              idx[j] = -1;
+              if (b < 32u) {
+                if ((mlo[j] >> b) & 1u)
+                  idx[j] = (int32_t)(lo + s_hpos[slo[j]] + __popc(mlo[j] & ((1u << b) - 1u)));
+              } else if ((mhi[j] >> (b - 32u)) & 1u) {
+                idx[j] = (int32_t)(lo + s_hpos[shi[j]] + __popc(mhi[j] & ((1u << (b - 32u)) - 1u)));
+              }
             }
             if (kMode == kBitsRev) {
 #pragma unroll
@@ -443,6 +435,7 @@ search_kernel(const __grid_constant__ SearchPair sp) {
     }
   }
 
+  MN_MARK(g_marks_search, 5);
   if (kMode != kMap) {
     if (live[kQRows - 1] && (reinterpret_cast<uintptr_t>(a.hit_words) & 7) == 0) {
       *reinterpret_cast<uint2 *>(a.hit_words + row0) = make_uint2(bits[0], bits[1]);
@@ -460,6 +453,7 @@ constexpr int kEThreads = 512;
 constexpr int kEWarps = kEThreads / 32;
 constexpr int kETile = 512;           // rows per tile: one 32-row segment per warp
 constexpr int kEPitch = kETile + 4;   // staging row pitch (elements), a multiple of 4
+constexpr int kEBatch = 8;            // tiles whose hit words are fetched together
 
 struct EmitArgs {
   const uint32_t *words_t;   // [T] hit bits of target rows
@@ -468,6 +462,8 @@ struct EmitArgs {
   int32_t *source_masks;     // [O, S]
   int32_t *order_out;        // [O] offset at mask row p
   int32_t *sizes_out;        // [O + 1] size of mask row p, then a copy of the status word
+  uint32_t *bits_t;          // optional [T]: bit p set when mask row p has an entry for the target
+  uint32_t *bits_s;          // optional [S]: the same for the sources
   int32_t *agg;              // workspace [64 pairs][grid]: hit counts of every block's tile
                              // range, then their exclusive prefix; pair = direction * 32 + offset
   int32_t *total;            // workspace [64]
@@ -503,8 +499,9 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
   extern __shared__ __align__(16) int32_t s_stage[];   // [O][kEPitch]
   __shared__ int32_t s_wcnt[32][kEWarps + 1];           // per offset: warp counts, then warp bases
   __shared__ int32_t s_run[2][32];                      // rank of the next hit, per direction / offset
-  __shared__ int32_t s_size[32], s_pos[32];
+  __shared__ int32_t s_size[32], s_pos[32], s_ord[32];
   __shared__ int32_t s_mis[32];
+  __shared__ uint32_t s_words[kEBatch][kETile];         // hit words of up to kEBatch tiles
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int O = e.num_offsets;
   const int G = (int)gridDim.x, b = (int)blockIdx.x;
@@ -514,18 +511,36 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
   const unsigned lt = lanemask_lt();
   const int my_mirror = lane < O ? e.mirror[lane] : 0;
 
+  MN_MARK(g_marks_emit, 0);
+  // hit words of tiles [first, first + kEBatch) of this block's range: all loads are in
+  // flight together; a thread only ever reads back the words it loaded itself
+  auto fetch_words = [&](int first) {
+#pragma unroll
+    for (int k = 0; k < kEBatch; k++) {
+      const int tile = first + k;
+      uint32_t w = 0u;
+      if (tile < t_end) {
+        const int dir = tile >= e.tiles_t ? 1 : 0;
+        const int64_t r = (int64_t)(tile - dir * e.tiles_t) * kETile + tid;
+        const int64_t n = dir ? e.S : e.T;
+        if (r < n) w = __ldg((dir ? e.words_s : e.words_t) + r);
+      }
+      s_words[k][tid] = w;
+    }
+  };
+
   // ---- phase 1: hits per offset of this block's tile range ---------------------
   int cnt0 = 0, cnt1 = 0;   // lane o: hits of offset o, per direction
-  for (int tile = t_begin; tile < t_end; tile++) {
-    const int dir = tile >= e.tiles_t ? 1 : 0;
-    const int64_t r = (int64_t)(tile - dir * e.tiles_t) * kETile + warp * 32 + lane;
-    const uint32_t *words = dir ? e.words_s : e.words_t;
-    const int64_t n = dir ? e.S : e.T;
-    const uint32_t w = r < n ? __ldg(words + r) : 0u;
-    if (__ballot_sync(0xffffffffu, w != 0u) == 0u) continue;
-    uint32_t plane = transpose32(w, lane);
-    if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
-    if (dir) cnt1 += __popc(plane); else cnt0 += __popc(plane);
+  for (int first = t_begin; first < t_end; first += kEBatch) {
+    fetch_words(first);
+    for (int tile = first; tile < min(first + kEBatch, t_end); tile++) {
+      const int dir = tile >= e.tiles_t ? 1 : 0;
+      const uint32_t w = s_words[tile - first][tid];
+      if (__ballot_sync(0xffffffffu, w != 0u) == 0u) continue;
+      uint32_t plane = transpose32(w, lane);
+      if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
+      if (dir) cnt1 += __popc(plane); else cnt0 += __popc(plane);
+    }
   }
   for (int d = 0; d < 2; d++) {
     if (lane < O) s_wcnt[lane][warp] = d ? cnt1 : cnt0;
@@ -538,7 +553,9 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
     }
     __syncthreads();
   }
+  MN_MARK(g_marks_emit, 1);
   grid_barrier(e.ctrl, (unsigned)G);
+  MN_MARK(g_marks_emit, 2);
 
   // ---- one warp per (direction, offset): exclusive prefix over the blocks ----------
   for (int pair = b * kEWarps + warp; pair < 64; pair += G * kEWarps) {
@@ -560,7 +577,9 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
       if (lane == 0) e.total[pair] = carry;
     }
   }
+  MN_MARK(g_marks_emit, 3);
   grid_barrier(e.ctrl, (unsigned)G);
+  MN_MARK(g_marks_emit, 4);
 
   // ---- rank offsets of this block, total sizes, size order ---------------------
   if (tid < 64) s_run[tid >> 5][tid & 31] = __ldcg(e.agg + (int64_t)tid * G + b);
@@ -578,6 +597,7 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
       }
     }
     s_pos[tid] = pos;
+    s_ord[pos] = tid;
     if (b == 0) {
       e.order_out[pos] = tid;
       e.sizes_out[pos] = s_size[tid];
@@ -586,24 +606,33 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
   if (b == 0 && tid == 0) e.sizes_out[O] = e.ctrl[MN_CTRL_STATUS];
   __syncthreads();
 
+  MN_MARK(g_marks_emit, 5);
   // ---- phase 2: ranks, staged per tile, one bulk copy per mask row segment ------
   bool pending = false;   // threads < O: a bulk group of mine may still be reading the stage
   for (int tile = t_begin; tile < t_end; tile++) {
+    // the words of the first kEBatch tiles are still in shared memory from phase 1
+    if (tile != t_begin && (tile - t_begin) % kEBatch == 0) fetch_words(tile);
+    if (tile == t_begin && t_end - t_begin > kEBatch) fetch_words(tile);
     const int dir = tile >= e.tiles_t ? 1 : 0;
     const int64_t tile_row0 = (int64_t)(tile - dir * e.tiles_t) * kETile;
-    const uint32_t *words = dir ? e.words_s : e.words_t;
     const int64_t n = dir ? e.S : e.T;
     int32_t *out = dir ? e.source_masks : e.target_masks;
     const int rows_here = (int)min((int64_t)kETile, n - tile_row0);
     const int seg = warp * 32;
 
-    uint32_t plane;
+    uint32_t plane = transpose32(s_words[(tile - t_begin) % kEBatch][tid], lane);
+    if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
+    if (lane >= O) plane = 0u;
     {
-      const int64_t r = tile_row0 + seg + lane;
-      const uint32_t w = r < n ? __ldg(words + r) : 0u;
-      plane = transpose32(w, lane);
-      if (dir) plane = __shfl_sync(0xffffffffu, plane, my_mirror);
-      if (lane >= O) plane = 0u;
+      // hit word of every row in mask-row order (bit p <-> mask row p), for the
+      // convolution kernels that walk a row's pairs without scanning the masks
+      uint32_t *bits_out = dir ? e.bits_s : e.bits_t;
+      if (bits_out != nullptr) {
+        uint32_t by_row = __shfl_sync(0xffffffffu, plane, lane < O ? s_ord[lane] : 0);
+        if (lane >= O) by_row = 0u;
+        by_row = transpose32(by_row, lane);
+        if (tile_row0 + seg + lane < n) bits_out[tile_row0 + seg + lane] = by_row;
+      }
     }
     if (lane < O) s_wcnt[lane][warp] = __popc(plane);
     // the previous tile's copies must have read the stage before it is refilled
@@ -673,7 +702,9 @@ emit_masks_kernel(const __grid_constant__ EmitArgs e) {
       for (int i = head + body; i < rows_here; i++) dst[i] = src[i];
     }
   }
+  MN_MARK(g_marks_emit, 6);
   if (pending) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  MN_MARK(g_marks_emit, 7);
 }
 
 __global__ void identity_order_kernel(int O, int32_t *order_out, int32_t *sizes_out,
@@ -949,8 +980,10 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
                                          const int32_t *offsets, int64_t O,
                                          const mn_keyspec *spec, int reorder,
                                          int32_t *source_masks_out, int32_t *target_masks_out,
-                                         int32_t *order_out, int32_t *sizes_out, int32_t *ctrl,
-                                         void *ws_ptr, size_t ws_bytes, void *stream) {
+                                         int32_t *order_out, int32_t *sizes_out,
+                                         uint32_t *source_bits_out, uint32_t *target_bits_out,
+                                         int32_t *ctrl, void *ws_ptr, size_t ws_bytes,
+                                         void *stream) {
   MN_CHECK_ARG(S >= 0 && T >= 0, "build_kernel_map: negative size");
   MN_CHECK_ARG(spec != nullptr, "build_kernel_map: null key spec");
   MN_CHECK_ARG(S < (1ll << 31) && T < (1ll << 31), "build_kernel_map: more than 2^31-1 rows");
@@ -970,6 +1003,8 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
     // nothing can match: every mask entry is -1, every size 0
     if (S > 0) MN_CHECK_CUDA(cudaMemsetAsync(source_masks_out, 0xff, sizeof(int32_t) * O * S, st));
     if (T > 0) MN_CHECK_CUDA(cudaMemsetAsync(target_masks_out, 0xff, sizeof(int32_t) * O * T, st));
+    if (S > 0 && source_bits_out != nullptr) MN_CHECK_CUDA(cudaMemsetAsync(source_bits_out, 0, sizeof(uint32_t) * S, st));
+    if (T > 0 && target_bits_out != nullptr) MN_CHECK_CUDA(cudaMemsetAsync(target_bits_out, 0, sizeof(uint32_t) * T, st));
     MN_LAUNCH("identity_order_kernel", st,
               identity_order_kernel<<<1, MN_MAX_OFFSETS + 32, 0, st>>>((int)O, order_out, sizes_out, ctrl));
     return MN_OK;
@@ -1034,6 +1069,7 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   e.words_t = words_t; e.words_s = words_s;
   e.target_masks = target_masks_out; e.source_masks = source_masks_out;
   e.order_out = order_out; e.sizes_out = sizes_out; e.agg = agg; e.total = total; e.ctrl = ctrl;
+  e.bits_t = target_bits_out; e.bits_s = source_bits_out;
   e.T = T; e.S = S; e.tiles_t = tiles_t; e.tiles_s = tiles_s;
   e.num_offsets = (int)O; e.reorder = reorder ? 1 : 0;
   for (int64_t o = 0; o < O; o++) e.mirror[o] = mirrored ? neg[o] : (uint8_t)o;
@@ -1046,3 +1082,14 @@ extern "C" mn_status mn_build_kernel_map(const uint64_t *source_keys, int64_t S,
   MN_CHECK_LAUNCH();
   return MN_OK;
 }
+
+#ifdef MN_PHASE_TIMING
+// Debug build only: copies the phase marks of the last search (which = 0) or mask
+// emission (which = 1) launch to the host (blocking).
+extern "C" int mn_debug_marks_query(int which, long long *out, int count) {
+  const size_t bytes = sizeof(long long) * (size_t)std::min(count, 2048 * 16);
+  cudaError_t e = which == 0 ? cudaMemcpyFromSymbol(out, g_marks_search, bytes)
+                             : cudaMemcpyFromSymbol(out, g_marks_emit, bytes);
+  return e == cudaSuccess ? 0 : 1;
+}
+#endif

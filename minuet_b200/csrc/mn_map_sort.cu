@@ -21,21 +21,21 @@ namespace {
 // ---------------------------------------------------------------------------
 // radix sort: one cooperative kernel for all passes
 // ---------------------------------------------------------------------------
-// Stable LSD sort, 9-bit digits.  Every block (1024 threads, one per SM) owns a
-// contiguous chunk of the input and every warp a contiguous slice of that chunk,
-// so that "block order, then warp order, then position" is the input order.
-// Per pass:
+// Stable LSD sort, 9-bit digits.  The work is latency bound (a few megabytes per
+// pass), so the grid is small: every block (1024 threads) owns a contiguous
+// chunk of about 8192 keys and every warp a contiguous slice of that chunk, so
+// that "block order, then warp order, then position" is the input order.  A
+// warp keeps its slice in registers for the whole pass when it fits (up to 8
+// keys per lane).  Per pass:
 //   A  every warp counts the digits of its slice into its own row of a
 //      [32 warps][512 digits] shared-memory table (equal digits inside a group
 //      of 32 keys find each other with match.any, one lane adds the group's
-//      count); the block histogram goes to a digit-major global table
+//      count); the block histogram goes to a [block][digit] global table
 //   -- grid barrier --
-//   B  one warp per digit turns that digit's row (one entry per block) into an
-//      exclusive prefix and writes the digit total
-//   -- grid barrier --
-//   C  every block scans the 512 digit totals, turns its per-warp counts into
-//      global positions and re-walks its chunk in the same order, writing every
-//      key (and payload) to its place
+//   C  every block reads the whole table (a few hundred KB in L2), derives its
+//      own base position per digit, turns its per-warp counts into global
+//      positions and walks its chunk again in the same order, writing every key
+//      (and payload) to its place
 //   -- grid barrier (the next pass reads what this one wrote) --
 // The first pass can build the keys itself from coordinate rows (floor to a
 // target stride and pack), so that the strided target-coordinate build needs no
@@ -46,6 +46,8 @@ constexpr int kRsWarps = kRsThreads / 32;
 constexpr int kRsBits = 9;                        // digit width: 4 passes cover 36 key bits
 constexpr int kRadix = 1 << kRsBits;
 constexpr int kRsMaxBlocks = 256;                 // workspace sizing
+constexpr int kRsKeysPerLane = 8;                 // register-resident slice: 256 keys per warp
+constexpr int kRsChunk = kRsWarps * 32 * kRsKeysPerLane;   // 8192 keys per block
 constexpr size_t kRsSmemBytes = (size_t)kRsWarps * kRadix * sizeof(uint32_t);   // 64 KB
 
 __device__ __forceinline__ unsigned lanemask_lt() {
@@ -62,8 +64,7 @@ struct SortArgs {
   int32_t end_bit;            // < 0: the key layout's total_bits
   int32_t has_vals;
   int32_t iota_vals;          // first pass: the payload is the element index
-  uint32_t *hist;             // [kRadix][grid] digit-major
-  uint32_t *total;            // [kRadix]
+  uint32_t *hist;             // [grid][kRadix]
   int32_t *result_in_second;  // out (may be NULL): 1 when the result is in keys[1] / vals[1]
   int32_t *ctrl;
   // optional key construction in front of the first pass
@@ -76,7 +77,7 @@ struct SortArgs {
 __global__ void __launch_bounds__(kRsThreads, 1)
 radix_sort_kernel(const __grid_constant__ SortArgs a) {
   extern __shared__ __align__(16) uint32_t s_cnt[];   // [kRsWarps][kRadix]
-  __shared__ uint32_t s_base[kRadix];
+  __shared__ uint32_t s_half[2][kRadix];
   __shared__ uint32_t s_scan[kRsWarps];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = (int)gridDim.x, b = (int)blockIdx.x;
@@ -94,6 +95,7 @@ radix_sort_kernel(const __grid_constant__ SortArgs a) {
   const int64_t g_per_warp = (g_per_block + kRsWarps - 1) / kRsWarps;
   const int64_t w0 = min(c1, c0 + (int64_t)warp * g_per_warp * 32);
   const int64_t w1 = min(c1, w0 + g_per_warp * 32);
+  const bool resident = g_per_warp <= kRsKeysPerLane;   // the slice stays in registers (uniform)
 
   if (a.coords != nullptr) {
     // keys of this block's chunk from the coordinate rows (the block is the only
@@ -113,93 +115,126 @@ radix_sort_kernel(const __grid_constant__ SortArgs a) {
     const int shift = a.begin_bit + p * kRsBits;
     const uint64_t *kin = a.keys[p & 1];
     uint64_t *kout = a.keys[(p & 1) ^ 1];
+    const int32_t *vin = a.vals[p & 1];
+    int32_t *vout = a.vals[(p & 1) ^ 1];
+    const bool iota = a.iota_vals && p == 0;
+    uint32_t *mine = s_cnt + warp * kRadix;
     // ---- A: per-warp digit counts ------------------------------------------------
     {
       uint4 *z = reinterpret_cast<uint4 *>(s_cnt);
       for (int i = tid; i < kRsWarps * kRadix / 4; i += kRsThreads) z[i] = make_uint4(0u, 0u, 0u, 0u);
     }
-    __syncthreads();
-    uint32_t *mine = s_cnt + warp * kRadix;
-    for (int64_t i0 = w0; i0 < w1; i0 += 32) {
-      const int64_t i = i0 + lane;
-      const bool valid = i < w1;
+    uint64_t key[kRsKeysPerLane];
+    if (resident) {
       // .cg loads: other blocks rewrote this buffer since this SM last read it
-      const unsigned d = valid ? (unsigned)((__ldcg(kin + i) >> shift) & (kRadix - 1)) : (unsigned)kRadix;
-      const unsigned peers = __match_any_sync(0xffffffffu, d);
-      if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
-      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < kRsKeysPerLane; j++) {
+        const int64_t i = w0 + j * 32 + lane;
+        key[j] = i < w1 ? __ldcg(kin + i) : 0ull;
+      }
+    }
+    __syncthreads();
+    if (resident) {
+#pragma unroll
+      for (int j = 0; j < kRsKeysPerLane; j++) {
+        const int64_t i = w0 + j * 32 + lane;
+        const bool valid = i < w1;
+        const unsigned d = valid ? (unsigned)((key[j] >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+        __syncwarp();
+      }
+    } else {
+      for (int64_t i0 = w0; i0 < w1; i0 += 32) {
+        const int64_t i = i0 + lane;
+        const bool valid = i < w1;
+        const unsigned d = valid ? (unsigned)((__ldcg(kin + i) >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+        __syncwarp();
+      }
     }
     __syncthreads();
     for (int d = tid; d < kRadix; d += kRsThreads) {
       uint32_t sum = 0;
 #pragma unroll 8
       for (int w = 0; w < kRsWarps; w++) sum += s_cnt[w * kRadix + d];
-      a.hist[(size_t)d * G + b] = sum;
-    }
-    grid_barrier(a.ctrl, (unsigned)G);
-    // ---- B: per digit, exclusive prefix over the blocks -----------------------------
-    for (int d = b * kRsWarps + warp; d < kRadix; d += G * kRsWarps) {
-      uint32_t *row = a.hist + (size_t)d * G;
-      uint32_t carry = 0;
-      for (int b0 = 0; b0 < G; b0 += 32) {
-        const int bb = b0 + lane;
-        const uint32_t v = bb < G ? __ldcg(row + bb) : 0u;
-        uint32_t inc = v;
-#pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-          const uint32_t t = __shfl_up_sync(0xffffffffu, inc, s);
-          if (lane >= s) inc += t;
-        }
-        if (bb < G) row[bb] = carry + inc - v;
-        carry += __shfl_sync(0xffffffffu, inc, 31);
-      }
-      if (lane == 0) a.total[d] = carry;
+      a.hist[(size_t)b * kRadix + d] = sum;
     }
     grid_barrier(a.ctrl, (unsigned)G);
     // ---- C: positions, scatter --------------------------------------------------------
-    if (tid < kRadix) {
-      // exclusive scan of the digit totals over the first 512 threads (16 warps)
-      const uint32_t t = __ldcg(a.total + tid);
-      uint32_t inc = t;
-#pragma unroll
-      for (int s = 1; s < 32; s <<= 1) {
-        const uint32_t u = __shfl_up_sync(0xffffffffu, inc, s);
-        if (lane >= s) inc += u;
-      }
-      if (lane == 31) s_scan[warp] = inc;
-      s_base[tid] = inc - t;
-    }
-    __syncthreads();
-    if (tid < kRadix) {
-      uint32_t before = 0;
-      for (int w = 0; w < warp; w++) before += s_scan[w];
-      uint32_t run = s_base[tid] + before + __ldcg(a.hist + (size_t)tid * G + b);
+    // two threads per digit add up the table column: keys of that digit in the blocks
+    // before this one, and in all blocks
+    {
+      const int d = tid & (kRadix - 1), half = tid >> kRsBits;
+      uint32_t before = 0, all = 0;
 #pragma unroll 8
-      for (int w = 0; w < kRsWarps; w++) {
-        const uint32_t c = s_cnt[w * kRadix + tid];
-        s_cnt[w * kRadix + tid] = run;
-        run += c;
+      for (int bb = half; bb < G; bb += 2) {
+        const uint32_t v = __ldcg(a.hist + (size_t)bb * kRadix + d);
+        all += v;
+        before += bb < b ? v : 0u;
+      }
+      if (half == 1) { s_half[0][d] = before; s_half[1][d] = all; }
+      __syncthreads();
+      uint32_t excl = 0;
+      if (half == 0) {
+        before += s_half[0][d];
+        all += s_half[1][d];
+        // exclusive scan of the digit totals over the first 512 threads (16 warps)
+        uint32_t inc = all;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+          const uint32_t u = __shfl_up_sync(0xffffffffu, inc, s);
+          if (lane >= s) inc += u;
+        }
+        if (lane == 31) s_scan[warp] = inc;
+        excl = inc - all;
+      }
+      __syncthreads();
+      if (half == 0) {
+        uint32_t run = excl + before;
+        for (int w = 0; w < warp; w++) run += s_scan[w];
+#pragma unroll 8
+        for (int w = 0; w < kRsWarps; w++) {
+          const uint32_t c = s_cnt[w * kRadix + d];
+          s_cnt[w * kRadix + d] = run;
+          run += c;
+        }
       }
     }
     __syncthreads();
-    const int32_t *vin = a.vals[p & 1];
-    int32_t *vout = a.vals[(p & 1) ^ 1];
-    const bool iota = a.iota_vals && p == 0;
-    for (int64_t i0 = w0; i0 < w1; i0 += 32) {
-      const int64_t i = i0 + lane;
-      const bool valid = i < w1;
-      const uint64_t key = valid ? __ldcg(kin + i) : 0ull;
-      const unsigned d = valid ? (unsigned)((key >> shift) & (kRadix - 1)) : (unsigned)kRadix;
-      const unsigned peers = __match_any_sync(0xffffffffu, d);
-      uint32_t pos = 0;
-      if (valid) {
-        pos = mine[d] + __popc(peers & lt);
-        kout[pos] = key;
-        if (a.has_vals) vout[pos] = iota ? (int32_t)i : __ldcg(vin + i);
+    if (resident) {
+#pragma unroll
+      for (int j = 0; j < kRsKeysPerLane; j++) {
+        const int64_t i = w0 + j * 32 + lane;
+        const bool valid = i < w1;
+        const unsigned d = valid ? (unsigned)((key[j] >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (valid) {
+          const uint32_t pos = mine[d] + __popc(peers & lt);
+          kout[pos] = key[j];
+          if (a.has_vals) vout[pos] = iota ? (int32_t)i : __ldcg(vin + i);
+        }
+        __syncwarp();
+        if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+        __syncwarp();
       }
-      __syncwarp();
-      if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
-      __syncwarp();
+    } else {
+      for (int64_t i0 = w0; i0 < w1; i0 += 32) {
+        const int64_t i = i0 + lane;
+        const bool valid = i < w1;
+        const uint64_t k = valid ? __ldcg(kin + i) : 0ull;
+        const unsigned d = valid ? (unsigned)((k >> shift) & (kRadix - 1)) : (unsigned)kRadix;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        if (valid) {
+          const uint32_t pos = mine[d] + __popc(peers & lt);
+          kout[pos] = k;
+          if (a.has_vals) vout[pos] = iota ? (int32_t)i : __ldcg(vin + i);
+        }
+        __syncwarp();
+        if (valid && (peers & lt) == 0u) mine[d] += __popc(peers);
+        __syncwarp();
+      }
     }
     if (p + 1 < passes) grid_barrier(a.ctrl, (unsigned)G);
   }
@@ -382,10 +417,13 @@ struct UniqueKeysArgs {
   int32_t *ctrl;
 };
 
+constexpr int kUkRounds = 8;                          // keys per thread and step
+constexpr int kUkStep = kUkThreads * kUkRounds;       // 8192 keys per block and step
+
 __global__ void __launch_bounds__(kUkThreads, 1)
 unique_keys_kernel(const __grid_constant__ UniqueKeysArgs a) {
-  __shared__ uint32_t s_warp[kUkWarps];
-  __shared__ uint32_t s_before, s_total;
+  __shared__ uint32_t s_cnt[kUkRounds][kUkWarps];     // openers per (round, warp), then their prefix
+  __shared__ uint32_t s_before, s_total, s_step_total;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = (int)gridDim.x, b = (int)blockIdx.x;
   const unsigned lt = (1u << lane) - 1u;
@@ -394,16 +432,29 @@ unique_keys_kernel(const __grid_constant__ UniqueKeysArgs a) {
   const int64_t per_block = ((a.n + G - 1) / G + kUkThreads - 1) / kUkThreads * kUkThreads;
   const int64_t c0 = min(a.n, (int64_t)b * per_block), c1 = min(a.n, c0 + per_block);
 
-  // ---- count the run openers of this chunk -------------------------------------
+  // ---- count the run openers of this chunk (a key opens a run when it differs from
+  // its predecessor); all loads of a step are issued before any is used -------------
   uint32_t mine = 0;
-  for (int64_t i = c0 + tid; i < c1; i += kUkThreads)
-    mine += (i == 0 || __ldcg(keys + i) != __ldcg(keys + i - 1)) ? 1u : 0u;
+  for (int64_t s0 = c0; s0 < c1; s0 += kUkStep) {
+    uint64_t k[kUkRounds], pk[kUkRounds];
+#pragma unroll
+    for (int j = 0; j < kUkRounds; j++) {
+      const int64_t i = s0 + j * kUkThreads + tid;
+      k[j] = i < c1 ? __ldcg(keys + i) : 0ull;
+      pk[j] = (i < c1 && i > 0) ? __ldcg(keys + i - 1) : 0ull;
+    }
+#pragma unroll
+    for (int j = 0; j < kUkRounds; j++) {
+      const int64_t i = s0 + j * kUkThreads + tid;
+      mine += (i < c1 && (i == 0 || k[j] != pk[j])) ? 1u : 0u;
+    }
+  }
   mine = __reduce_add_sync(0xffffffffu, mine);
-  if (lane == 0) s_warp[warp] = mine;
+  if (lane == 0) s_cnt[0][warp] = mine;
   __syncthreads();
   if (tid == 0) {
     uint32_t t = 0;
-    for (int w = 0; w < kUkWarps; w++) t += s_warp[w];
+    for (int w = 0; w < kUkWarps; w++) t += s_cnt[0][w];
     a.block_counts[b] = t;
   }
   grid_barrier(a.ctrl, (unsigned)G);
@@ -423,38 +474,59 @@ unique_keys_kernel(const __grid_constant__ UniqueKeysArgs a) {
   const uint32_t total = s_total;
 
   // ---- compact, unpack, cloud starts ----------------------------------------------
-  for (int64_t i0 = c0; i0 < c1; i0 += kUkThreads) {
-    const int64_t i = i0 + tid;
-    uint64_t key = 0, prev = 0;
-    bool opens = false;
-    if (i < c1) {
-      key = __ldcg(keys + i);
-      prev = i > 0 ? __ldcg(keys + i - 1) : 0;
-      opens = i == 0 || key != prev;
+  for (int64_t s0 = c0; s0 < c1; s0 += kUkStep) {
+    uint64_t k[kUkRounds], pk[kUkRounds];
+    unsigned votes[kUkRounds];
+#pragma unroll
+    for (int j = 0; j < kUkRounds; j++) {
+      const int64_t i = s0 + j * kUkThreads + tid;
+      k[j] = i < c1 ? __ldcg(keys + i) : 0ull;
+      pk[j] = (i < c1 && i > 0) ? __ldcg(keys + i - 1) : 0ull;
     }
-    const unsigned votes = __ballot_sync(0xffffffffu, opens);
-    __syncthreads();   // s_warp of the previous round has been read
-    if (lane == 0) s_warp[warp] = __popc(votes);
+    __syncthreads();   // the prefix table of the previous step has been read
+#pragma unroll
+    for (int j = 0; j < kUkRounds; j++) {
+      const int64_t i = s0 + j * kUkThreads + tid;
+      const bool opens = i < c1 && (i == 0 || k[j] != pk[j]);
+      votes[j] = __ballot_sync(0xffffffffu, opens);
+      if (lane == 0) s_cnt[j][warp] = __popc(votes[j]);
+    }
     __syncthreads();
-    uint32_t pos = run + __popc(votes & lt);
-    uint32_t round_total = 0;
-    for (int w = 0; w < kUkWarps; w++) {
-      const uint32_t c = s_warp[w];
-      if (w < warp) pos += c;
-      round_total += c;
-    }
-    run += round_total;
-    if (opens) {
-      a.keys_out[pos] = key;
-      for (int k = 0; k < spec.ndim; k++) {
-        const uint64_t f = (key >> spec.shift[k]) & ((1ull << spec.bits[k]) - 1ull);
-        a.rows_out[(int64_t)pos * spec.ndim + k] = (int32_t)((int64_t)f + spec.base[k]);
+    if (warp == 0) {
+      // exclusive prefix over the kUkRounds * kUkWarps counts, in (round, warp) order
+      uint32_t v[kUkRounds], sum = 0;
+#pragma unroll
+      for (int j = 0; j < kUkRounds; j++) { v[j] = (&s_cnt[0][0])[lane * kUkRounds + j]; sum += v[j]; }
+      uint32_t inc = sum;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, inc, s);
+        if (lane >= s) inc += t;
       }
-      // first key of cloud c: every cloud after the previous key's cloud starts here
-      const int64_t c_here = (int64_t)(key >> spec.cloud_shift);
-      const int64_t c_prev = i == 0 ? -1 : (int64_t)(prev >> spec.cloud_shift);
-      for (int64_t g = c_prev + 1; g <= c_here && g <= a.num_clouds; g++) a.meta[1 + g] = pos;
+      uint32_t r = inc - sum;
+#pragma unroll
+      for (int j = 0; j < kUkRounds; j++) { (&s_cnt[0][0])[lane * kUkRounds + j] = r; r += v[j]; }
+      if (lane == 31) s_step_total = inc;
     }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kUkRounds; j++) {
+      const int64_t i = s0 + j * kUkThreads + tid;
+      if ((votes[j] >> lane) & 1u) {
+        const uint32_t pos = run + s_cnt[j][warp] + __popc(votes[j] & lt);
+        const uint64_t key = k[j];
+        a.keys_out[pos] = key;
+        for (int d = 0; d < spec.ndim; d++) {
+          const uint64_t f = (key >> spec.shift[d]) & ((1ull << spec.bits[d]) - 1ull);
+          a.rows_out[(int64_t)pos * spec.ndim + d] = (int32_t)((int64_t)f + spec.base[d]);
+        }
+        // first key of cloud c: every cloud after the previous key's cloud starts here
+        const int64_t c_here = (int64_t)(key >> spec.cloud_shift);
+        const int64_t c_prev = i == 0 ? -1 : (int64_t)(pk[j] >> spec.cloud_shift);
+        for (int64_t g = c_prev + 1; g <= c_here && g <= a.num_clouds; g++) a.meta[1 + g] = pos;
+      }
+    }
+    run += s_step_total;
   }
   if (b == 0 && tid == 0) {
     a.meta[0] = total;
@@ -470,8 +542,7 @@ __global__ void zero_index0_kernel(int64_t *indices) { indices[0] = 0; }
 
 size_t radix_sort_workspace_bytes(int64_t n) {
   (void)n;
-  return align_up((size_t)kRsMaxBlocks * kRadix * sizeof(uint32_t), 256) +
-         align_up(kRadix * sizeof(uint32_t), 256) + 256;
+  return align_up((size_t)kRsMaxBlocks * kRadix * sizeof(uint32_t), 256) + 256;
 }
 
 namespace {
@@ -517,7 +588,7 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals, i
   static thread_local int grid_cache[kMaxDevices] = {0};
   int coresident = 0;
   MN_RETURN_IF(coop_grid_1024(radix_sort_kernel, kRsSmemBytes, grid_cache, &coresident));
-  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, 2048)));
+  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, kRsChunk)));
   SortArgs a{};
   a.keys[0] = keys; a.keys[1] = keys_tmp;
   a.vals[0] = vals; a.vals[1] = vals_tmp;
@@ -527,7 +598,6 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals, i
   a.has_vals = vals != nullptr && vals_tmp != nullptr;
   a.iota_vals = iota_vals ? 1 : 0;
   a.hist = ws.take<uint32_t>((size_t)kRsMaxBlocks * kRadix);
-  a.total = ws.take<uint32_t>(kRadix);
   MN_CHECK_WS(ws);
   a.result_in_second = result_in_second_dev;
   a.ctrl = ctrl;
@@ -644,7 +714,7 @@ extern "C" mn_status mn_downsample_coordinates(
   static thread_local int grid_cache[kMaxDevices] = {0};
   int coresident = 0;
   MN_RETURN_IF(coop_grid_1024(unique_keys_kernel, 0, grid_cache, &coresident));
-  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, 2048)));
+  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, kUkStep)));
   UniqueKeysArgs a{};
   a.keys[0] = keys; a.keys[1] = keys_tmp;
   a.which = n > 0 ? which : nullptr;

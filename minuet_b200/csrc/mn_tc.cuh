@@ -118,6 +118,45 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 
 }  // namespace tc
 
+// ---- pair-list forward (mn_conv_pairs.cu) -------------------------------------------
+constexpr int MN_MAX_PAIR_ROWS = 32;
+
+// Which mask rows of a kernel map go through the product buffer, and where.
+struct PairPlan {
+  int64_t row_begin[MN_MAX_PAIR_ROWS + 1];   // first product row of mask row p (128-aligned)
+  int32_t tile_prefix[MN_MAX_PAIR_ROWS + 1]; // first 128-row tile of mask row p
+  int64_t total_rows;
+  int32_t centre;                            // mask row handled as a dense product, or -1
+  int32_t num_rows;                          // O
+  uint32_t keep;                             // bit p set: mask row p has product rows
+};
+PairPlan make_pair_plan(const int32_t *sizes, int64_t O, int64_t S, int64_t T, int allow_shortcut);
+
+// Epilogue of the dense (centre / 1x1x1) GEMM: out = relu?((acc + sum of the product
+// rows named by the row's hit word) * scale + shift + residual), rounded once.
+struct PairEpilogue {
+  const float *scale;
+  const float *shift;
+  const void *residual;          // [T, c_out], feature dtype
+  const uint32_t *bits;          // [T] hit words, or NULL: nothing to add
+  const int32_t *target_masks;   // [O, T]
+  const float *products;         // [total_rows, c_out]
+  int64_t T;
+  int64_t row_begin[MN_MAX_PAIR_ROWS + 1];
+  uint32_t keep;
+  int32_t relu;
+};
+
+// step 1: products[r, :] = sources[pair_src[r], :] @ weights_t[order[p(r)]]^T, fp32
+mn_status launch_pair_products(const PairPlan &plan, int64_t S, int64_t c_in, int64_t c_out, bool bf16,
+                               const void *sources, const void *weights_t, int O,
+                               const int32_t *pair_src, const int32_t *order, float *products,
+                               int32_t *status_dev, cudaStream_t st);
+// step 2: out = epilogue(sources @ weights_t[order[centre]]^T)
+mn_status launch_centre_gemm(int64_t rows, int64_t c_in, int64_t c_out, bool bf16, const void *sources,
+                             const void *weights_t, int O, int centre, const int32_t *order,
+                             const PairEpilogue &ep, void *out, int32_t *status_dev, cudaStream_t st);
+
 // K-major operand map: dims (K, rows[, batch]), box (64, box_rows[, 1]), 128-byte swizzle,
 // 16-bit elements (mn_gemm_tc.cu)
 mn_status make_kmajor_map(CUtensorMap *map, const void *base, bool bf16, int64_t K, int64_t rows,

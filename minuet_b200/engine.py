@@ -14,6 +14,9 @@ from minuet_b200 import _lib
 from minuet_b200._lib import KeySpec
 
 DEFAULT_MARGIN = 64
+# When set to a list, every convolution appends a dict with its shape (S, T, O, E,
+# c_in, c_out, algorithm); benchmarks use it to compute per-layer rooflines.
+LAYER_LOG = None
 _DTYPE_CODE = {torch.float32: _lib.MN_F32, torch.float16: _lib.MN_F16,
                torch.bfloat16: _lib.MN_BF16}
 
@@ -186,19 +189,22 @@ def make_keyspec(coord_tensors: Sequence[torch.Tensor], ndim: int, num_clouds: i
     return spec
 
 
-def make_keyspec_device(coords: torch.Tensor, ndim: int, num_clouds: int, margin: int):
-    """Bounding box and key layout in one launch, left on the device (no read-back).
-    Returns ``(spec, spec_dev)``: the host struct only carries ndim, margin and the
-    pointer to ``spec_dev``, which must stay alive for as long as the spec is used."""
+def make_keyspec_device(coords: torch.Tensor, batch_dims: Optional[torch.Tensor], ndim: int,
+                        num_clouds: int, margin: int, with_keys: bool = True):
+    """Bounding box, key layout and (optionally) the keys of ``coords`` in one launch,
+    all left on the device (no read-back).  Returns ``(spec, spec_dev, keys)``: the
+    host struct only carries ndim, margin and the pointer to ``spec_dev``, which
+    must stay alive for as long as the spec is used."""
     device = coords.device
     spec = KeySpec()
     spec_dev = torch.empty(256, dtype=torch.uint8, device=device)
+    keys = torch.empty(coords.shape[0], dtype=torch.int64, device=device) if with_keys else None
     ws = workspace(lib().mn_map_workspace_bytes(0, 0, 0), device)
-    _lib.check(lib().mn_keyspec_device(ptr(coords), coords.shape[0], ndim, max(int(num_clouds), 1),
-                                       int(margin), ptr(spec_dev), ctypes.byref(spec),
-                                       ptr(control_block(device)), ptr(ws), ws.numel(),
-                                       stream_ptr(device)), "keyspec_device")
-    return spec, spec_dev
+    _lib.check(lib().mn_keyspec_device(ptr(coords), coords.shape[0], ndim, ptr(batch_dims),
+                                       max(int(num_clouds), 1), int(margin), ptr(spec_dev),
+                                       ctypes.byref(spec), ptr(keys), ptr(control_block(device)),
+                                       ptr(ws), ws.numel(), stream_ptr(device)), "keyspec_device")
+    return spec, spec_dev, keys
 
 
 def read_small(t: torch.Tensor) -> np.ndarray:
@@ -282,6 +288,28 @@ def host_copy(t: torch.Tensor, dtype=np.int32) -> np.ndarray:
 
 
 # ---------------------------------------------------------------------------
+# per-row hit words of kernel maps, keyed by the mask tensors they belong to
+# ---------------------------------------------------------------------------
+_hit_bits = {}
+
+
+def remember_bits(source_masks, target_masks, source_bits, target_bits):
+    """Keep the per-row hit words (bit p set <=> mask row p has an entry for the row)
+    that the fused map build produced, for as long as the masks live."""
+    for masks, bits in ((source_masks, source_bits), (target_masks, target_bits)):
+        key = id(masks)
+        _hit_bits[key] = (weakref.ref(masks, lambda _r, k=key: _hit_bits.pop(k, None)), bits)
+
+
+def hit_bits(masks: torch.Tensor) -> Optional[torch.Tensor]:
+    """Hit words of a mask tensor that came from the fused map build, else None."""
+    hit = _hit_bits.get(id(masks))
+    if hit is not None and hit[0]() is masks:
+        return hit[1]
+    return None
+
+
+# ---------------------------------------------------------------------------
 # neighbour tables of kernel maps (fused forward), keyed by the mask tensors
 # ---------------------------------------------------------------------------
 _neighbor_tables = {}
@@ -314,3 +342,37 @@ def neighbor_table(source_masks: torch.Tensor, target_masks: torch.Tensor,
     _neighbor_tables[key] = (weakref.ref(source_masks, drop), weakref.ref(target_masks, drop),
                              nbr, tile_bits)
     return nbr, tile_bits
+
+
+# ---------------------------------------------------------------------------
+# pair lists of kernel maps (pair-list forward), keyed by the mask tensors
+# ---------------------------------------------------------------------------
+_pair_lists = {}
+
+
+def pair_list(source_masks: torch.Tensor, target_masks: torch.Tensor, sizes_host: np.ndarray,
+              allow_shortcut: bool):
+    """``pair_src`` int32 ``[R]`` (the source row of every product row, -1 in the
+    padding) of the kernel map the masks describe, or None when the map did not come
+    with hit words; built on first use and kept for as long as the masks live."""
+    bits = hit_bits(source_masks)
+    if bits is None or hit_bits(target_masks) is None:
+        return None
+    key = (id(source_masks), id(target_masks), bool(allow_shortcut))
+    hit = _pair_lists.get(key)
+    if hit is not None and hit[0]() is source_masks and hit[1]() is target_masks:
+        return hit[2]
+    O, S = source_masks.shape
+    T = target_masks.shape[1]
+    device = source_masks.device
+    rows = int(lib().mn_pair_rows(np_ptr(sizes_host), O, S, T, int(bool(allow_shortcut))))
+    pair_src = torch.empty(max(rows, 1), dtype=torch.int32, device=device)
+    _lib.check(lib().mn_build_pair_list(ptr(source_masks), ptr(bits), np_ptr(sizes_host), O, S, T,
+                                        int(bool(allow_shortcut)), ptr(pair_src),
+                                        stream_ptr(device)), "build_pair_list")
+
+    def drop(_ref, k=key):
+        _pair_lists.pop(k, None)
+
+    _pair_lists[key] = (weakref.ref(source_masks, drop), weakref.ref(target_masks, drop), pair_src)
+    return pair_src

@@ -47,6 +47,7 @@ class KernelMapCache(object):
         self._keys = dict()          # stride -> (coordinates tensor, keys tensor)
         self._spec = None
         self._spec_dev = None        # device copy of the key layout (kept alive with the spec)
+        self._root_keys = None       # (coordinates tensor, keys) of the first tensor seen
         self._root = None            # (coords int32, batch_dims int64, num_clouds)
 
     # -- bookkeeping ------------------------------------------------------------
@@ -56,6 +57,7 @@ class KernelMapCache(object):
         self._keys.clear()
         self._spec = None
         self._spec_dev = None
+        self._root_keys = None
         self._root = None
 
     def _get_kernel_offsets(self, source_stride, kernel_size, kernel_dilation) -> np.ndarray:
@@ -75,17 +77,22 @@ class KernelMapCache(object):
             self._root = (engine.as_i32_coords(coordinates), bd,
                           1 if bd is None else bd.numel() - 1)
         if self._spec is None or self._spec.margin < margin:
-            coords, _, num_clouds = self._root
-            # bounding box and key layout stay on the device: no read-back here
-            self._spec, self._spec_dev = engine.make_keyspec_device(
-                coords, self._ndim, num_clouds, max(int(margin), engine.DEFAULT_MARGIN))
+            coords, bd, num_clouds = self._root
+            # bounding box, key layout and the keys of the first tensor in one launch;
+            # all of it stays on the device: no read-back here
+            self._spec, self._spec_dev, keys = engine.make_keyspec_device(
+                coords, bd, self._ndim, num_clouds, max(int(margin), engine.DEFAULT_MARGIN))
             self._keys.clear()
+            self._root_keys = (coordinates, keys)
         return self._spec
 
     def _keys_of(self, coordinates, batch_dims, stride):
         hit = self._keys.get(stride)
         if hit is not None and hit[0] is coordinates:
             return hit[1]
+        if self._root_keys is not None and self._root_keys[0] is coordinates:
+            self._keys[stride] = self._root_keys
+            return self._root_keys[1]
         keys = engine.pack_keys(engine.as_i32_coords(coordinates), engine.as_i64(batch_dims),
                                 self._spec)
         self._keys[stride] = (coordinates, keys)
@@ -204,13 +211,18 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
     ws = engine.workspace(lib.mn_map_workspace_bytes(S, T, O), device)
     stream = engine.stream_ptr(device)
     if O <= 32:
+        # per-row hit words in mask-row order, kept with the masks for the forward kernels
+        source_bits = torch.empty(S, dtype=torch.int32, device=device)
+        target_bits = torch.empty(T, dtype=torch.int32, device=device)
         same = source_keys.data_ptr() == target_keys.data_ptr() and S == T
         _lib.check(lib.mn_build_kernel_map(
             engine.ptr(source_keys), S, engine.ptr(source_keys if same else target_keys), T,
             engine.np_ptr(offsets), O, ctypes.byref(spec), int(reorder), engine.ptr(source_masks),
             engine.ptr(target_masks), engine.ptr(order), engine.ptr(sizes_status),
+            engine.ptr(source_bits), engine.ptr(target_bits),
             engine.ptr(engine.control_block(device)), engine.ptr(ws), ws.numel(), stream),
             "build_kernel_map")
+        engine.remember_bits(source_masks, target_masks, source_bits, target_bits)
     else:
         kernel_map = torch.empty((O, T), dtype=torch.int32, device=device)
         _lib.check(lib.mn_query_sorted_index_with_offsets(
@@ -390,8 +402,10 @@ class SparseConv(Module):
     def forward(self, inputs: SparseTensor) -> SparseTensor:
         features = inputs.F
         if self.is_trivial:
-            out = torch.mm(features, self.kernel.view(self.in_channels, self.out_channels))
-            coordinates, stride, batch_dims = inputs.C, inputs.stride, inputs.batch_dims
+            bias = None if self.bias is None else self.bias.detach().float()
+            out = F.dense_forward(features, self.kernel.view(self.in_channels, self.out_channels),
+                                  shift=bias)
+            return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         else:
             coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
                 self._lookup(inputs)
@@ -419,9 +433,8 @@ class SparseConv(Module):
                 (0.0 if shift is None else shift.float())
         features = inputs.F
         if self.is_trivial:
-            out = torch.mm(features, self.kernel.view(self.in_channels, self.out_channels))
-            if scale is not None or shift is not None or residual is not None or relu:
-                F.apply_epilogue(out, scale, shift, residual, relu)
+            out = F.dense_forward(features, self.kernel.view(self.in_channels, self.out_channels),
+                                  scale, shift, residual, relu)
             return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
             self._lookup(inputs)

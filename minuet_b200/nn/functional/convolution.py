@@ -2,7 +2,7 @@
 (mirror of minuet/nn/functional/convolution.py)."""
 __all__ = ['cuda_time_gather', 'cuda_time_scatter', 'sparse_convolution_forward',
            'sparse_convolution_forward_fused', 'apply_epilogue', 'cuda_time_gemm',
-           'set_gemm_parallel_level']
+           'set_gemm_parallel_level', 'dense_forward']
 
 import math
 from typing import Optional
@@ -170,6 +170,69 @@ def _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_t
     return out
 
 
+def _pairs_forward(sources, weights, sm, tm, order, sizes_host, out, allow_shortcut_matmul,
+                   scale=None, shift=None, residual=None, relu=False) -> bool:
+    """Pair-list forward (16-bit, kernel maps that carry hit words).  Returns False,
+    without touching ``out``, when this layer cannot take it."""
+    O, S = sm.shape
+    T = tm.shape[1]
+    c_in, c_out = weights.shape[1], weights.shape[2]
+    lib = engine.lib()
+    code = engine.dtype_code(weights.dtype)
+    if not lib.mn_pairs_supported(O, c_in, c_out, code):
+        return False
+    pair_src = engine.pair_list(sm, tm, sizes_host, allow_shortcut_matmul)
+    if pair_src is None:
+        return False
+    device = sources.device
+    shortcut = int(bool(allow_shortcut_matmul))
+    ws = engine.workspace(lib.mn_pairs_workspace_bytes(engine.np_ptr(sizes_host), O, S, T, c_in,
+                                                       c_out, shortcut), device)
+    _lib.check(lib.mn_sparse_convolution_forward_pairs(
+        S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights), engine.ptr(tm),
+        engine.ptr(engine.hit_bits(tm)), engine.ptr(pair_src), engine.ptr(order),
+        engine.np_ptr(sizes_host), shortcut, engine.ptr(scale), engine.ptr(shift),
+        engine.ptr(residual), int(bool(relu)), engine.ptr(out),
+        engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
+        engine.stream_ptr(device)), "sparse_convolution_forward_pairs")
+    return True
+
+
+def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=False):
+    """``relu?((features @ weight) * scale + shift + residual)`` for a 1x1x1
+    convolution: the tensor-core GEMM of this library for fp16/bf16 (c_in a multiple
+    of 8, c_out even, at most 256), a plain product plus the epilogue pass otherwise
+    (fp32 must not go through TF32: its 10-bit mantissa would break the 1e-5 bound)."""
+    engine.require_cuda(features)
+    features = features.contiguous()
+    weight = weight.contiguous()
+    rows, c_in = features.shape
+    c_out = weight.shape[1]
+    lib = engine.lib()
+    if features.dtype in (torch.float16, torch.bfloat16) and features.dtype == weight.dtype and \
+            lib.mn_dense_supported(c_in, c_out, engine.dtype_code(features.dtype)):
+        device = features.device
+        out = torch.empty((rows, c_out), dtype=features.dtype, device=device)
+        ws = engine.workspace(lib.mn_dense_workspace_bytes(c_in, c_out), device)
+        res = None if residual is None else residual.contiguous()
+        _lib.check(lib.mn_dense_forward(
+            rows, c_in, c_out, engine.dtype_code(features.dtype), engine.ptr(features),
+            engine.ptr(weight), engine.ptr(_f32(scale)), engine.ptr(_f32(shift)), engine.ptr(res),
+            int(bool(relu)), engine.ptr(out), engine.ptr(engine.status_word(device)),
+            engine.ptr(ws), ws.numel(), engine.stream_ptr(device)), "dense_forward")
+        if engine.LAYER_LOG is not None:
+            engine.LAYER_LOG.append({"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in,
+                                     "c_out": c_out, "algorithm": "dense"})
+        return out
+    out = torch.mm(features, weight)
+    if scale is not None or shift is not None or residual is not None or relu:
+        apply_epilogue(out, scale, shift, residual, relu)
+    if engine.LAYER_LOG is not None:
+        engine.LAYER_LOG.append({"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in,
+                                 "c_out": c_out, "algorithm": "mm"})
+    return out
+
+
 def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes_host, out,
                       scale=None, shift=None, residual=None, relu=False):
     O, S = source_masks.shape
@@ -231,6 +294,11 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
     has_epilogue = scale is not None or shift is not None or residual is not None or relu
 
     def run_explicit():
+        # sparse maps with hit words: pair lists, fp32 products, one rounding
+        if weights.dtype != torch.float32 and _pairs_forward(
+                sources, weights, sm, tm, order, sizes_host, out, allow_shortcut_matmul, scale,
+                shift, residual, relu):
+            return out
         _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_tile_size,
                           scatter_tile_size, allow_shortcut_matmul, threshold)
         if has_epilogue:
@@ -244,7 +312,12 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
         return _implicit_forward(sources, weights, sm, tm, order, sizes_host, out, scale, shift,
                                  residual, relu)
 
-    if _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit) == "implicit":
+    algorithm = _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit)
+    if engine.LAYER_LOG is not None:
+        engine.LAYER_LOG.append({"S": sm.shape[1], "T": T, "O": sm.shape[0],
+                                 "E": int(sizes_host.sum()), "c_in": weights.shape[1],
+                                 "c_out": c_out, "algorithm": algorithm})
+    if algorithm == "implicit":
         return run_implicit()
     return run_explicit()
 
