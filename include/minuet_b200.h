@@ -89,7 +89,7 @@ typedef struct {
 /* Version of this interface; mn_version() returns the value the library was
  * built with.  A binding should refuse a library whose version differs from the
  * header it was written against: argument lists change between versions. */
-#define MN_ABI_VERSION 8
+#define MN_ABI_VERSION 9
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -307,13 +307,16 @@ mn_status mn_build_neighbor_table(const int32_t *source_masks, const int32_t *ta
 
 /* out[t] = epilogue(sum_p sources[nbr[p, t]] @ weights[order ? order[p] : p]) with
  * epilogue(v) = relu?(v * scale[c] + shift[c] + residual[t, c]); scale, shift
- * (fp32 [c_out]) and residual ([T, c_out], feature dtype) may each be NULL. */
+ * (fp32 [c_out]) and residual ([T, c_out], feature dtype) may each be NULL.
+ * sub_tiles: 128-row sub-tiles per CTA tile (1..4; they share every weight tile);
+ * 0 lets the library choose from pairs_per_row = (number of pairs) / T. */
 size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out);
 mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
     const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
     const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
-    void *targets_out, int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
+    double pairs_per_row, int sub_tiles, void *targets_out, int32_t *status_dev, void *ws,
+    size_t ws_bytes, void *stream);
 
 /* ---- Pair-list forward (sparse kernel maps) and dense forward ------------------ */
 /* Same result as mn_sparse_convolution_forward followed by mn_apply_epilogue, for

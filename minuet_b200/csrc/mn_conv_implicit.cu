@@ -30,11 +30,12 @@ namespace {
 
 using namespace tc;
 
-constexpr int kImThreads = 288;
+constexpr int kImThreads = 288;        // warps 0..3 producers, warp 4 MMA issuer, warps 5..8 epilogue
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kMaxStages = 10;
+constexpr int kMaxSub = 4;             // 128-row sub-tiles per CTA tile
 
 struct ImArgs {
   const uint8_t *in;          // [S, K] 16-bit
@@ -47,9 +48,11 @@ struct ImArgs {
   int32_t *status;
   int64_t T;
   int32_t K, N, n_pad, k_blocks, stages, a_bytes, stage_bytes, elem_is_bf16, num_tiles, relu;
-  int32_t sub;         // 128-row sub-tiles per CTA tile (1 or 2): they share every weight tile
+  int32_t sub;         // 128-row sub-tiles per CTA tile (1..4): they share every weight tile
   int32_t acc_bufs;    // accumulator sets in TMEM (2 when 2 * sub * n_pad <= 512, else 1)
   int32_t n_tiles128;  // entries of tile_bits
+  int32_t num_offsets; // O
+  int32_t tmem_cols;   // TMEM columns this CTA allocates
   // pair mode (step 1 of the pair-list forward): the rows are PRODUCT rows, row r reads
   // source row nbr[r], every tile has exactly one "offset" whose weight matrix follows from
   // the mask row that owns the tile, and the fp32 accumulators are stored as they are
@@ -82,7 +85,7 @@ __device__ __forceinline__ float elem_to_f32(uint16_t v) {
   return __half2float(__ushort_as_half(v));
 }
 
-__global__ void __launch_bounds__(kImThreads, 1)
+__global__ void __launch_bounds__(kImThreads, 3)
 conv_implicit_kernel(const __grid_constant__ ImArgs args,
                      const __grid_constant__ CUtensorMap map_b,     // weights^T [O, N, K]
                      const __grid_constant__ CUtensorMap map_out) { // output    [T, N]
@@ -96,11 +99,11 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = args.stages;
-  const uint32_t tmem_cols = 512;
+  const uint32_t tmem_cols = (uint32_t)args.tmem_cols;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) {
-      mbar_init(&bar_full[s], kBM + 1);   // 128 row producers + the weight tile's expect_tx
+      mbar_init(&bar_full[s], kBM + 1);   // 128 producer lanes + the weight tile's expect_tx
       mbar_init(&bar_empty[s], 1);
     }
     for (int a = 0; a < 2; a++) { mbar_init(&bar_acc_full[a], 1); mbar_init(&bar_acc_empty[a], 4); }
@@ -121,77 +124,83 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
 
   if (warp < 4) {
     // ------------------------------ producers ---------------------------------
-    const int r = threadIdx.x;               // row owned by this thread in every 128-row sub-tile
+    // Four warps feed the ring; warp w owns rows 32w .. 32w+31 of every 128-row sub-tile
+    // and lane l holds the source row of row 32w + l (one coalesced load from the
+    // neighbour table per offset, the next offset's requested before the current one is
+    // copied).  Per stage eight lanes copy one row: a warp-wide cp.async reads four whole
+    // 128-byte lines (16 bytes of 32 different lines would cost a tag lookup per lane),
+    // zero fill where the kernel map has no source.  Each lane's arrival on the stage
+    // barrier fires when its copies have landed.  All sub-tiles of a CTA tile share every
+    // weight tile.  (One producer warp instead of four halves the kernel's speed: the
+    // copies of a stage are then issued by a single warp, and issue rate bounds it.)
     const int sub = args.sub;
     const uint32_t b_bytes = (uint32_t)(args.stage_bytes - args.a_bytes);
+    const int chunk = lane & 7;
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
-      int64_t t[2];
-      bool row_live[2];
       uint32_t rest = 0u;
 #pragma unroll
-      for (int h = 0; h < 2; h++) {
-        t[h] = ((int64_t)tile * sub + h) * kBM + r;
-        row_live[h] = h < sub && t[h] < args.T;
+      for (int h = 0; h < kMaxSub; h++)
         if (h < sub && tile * sub + h < args.n_tiles128)
           rest |= args.pair_mode ? 1u : __ldg(args.tile_bits + tile * sub + h);
-      }
       const int pair_row = args.pair_mode ? pair_row_of_tile(args, tile) : 0;
-      // software pipeline over the active offsets: the next offset's source rows are
-      // requested before the current ones are copied
       int p = rest != 0u ? __ffs(rest) - 1 : -1;
-      int src[2], src_next[2];
+      int src[kMaxSub], src_next[kMaxSub];
+      auto fetch = [&](int pp, int (&dst)[kMaxSub]) {
 #pragma unroll
-      for (int h = 0; h < 2; h++)
-        src[h] = (p >= 0 && row_live[h]) ? __ldg(args.nbr + (int64_t)p * args.T + t[h]) : -1;
+        for (int h = 0; h < kMaxSub; h++) {
+          const int64_t t = ((int64_t)tile * sub + h) * kBM + warp * 32 + lane;
+          dst[h] = (pp >= 0 && h < sub && t < args.T) ? __ldg(args.nbr + (int64_t)pp * args.T + t) : -1;
+        }
+      };
+      fetch(p, src);
       while (alive && p >= 0) {
         rest &= rest - 1u;
         const int p_next = rest != 0u ? __ffs(rest) - 1 : -1;
-#pragma unroll
-        for (int h = 0; h < 2; h++)
-          src_next[h] = (p_next >= 0 && row_live[h])
-                            ? __ldg(args.nbr + (int64_t)p_next * args.T + t[h]) : -1;
+        fetch(p_next, src_next);
         for (int kb = 0; kb < args.k_blocks; kb++) {
-          // one lane per warp polls the barrier; the others wait at the warp barrier
-          int ok = 1;
+          int ok = 1;   // one lane polls the barrier, the warp follows
           if (lane == 0) ok = mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag, args.status) ? 1 : 0;
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) { alive = false; break; }
           uint8_t *sa = stage_base + (size_t)stage * args.stage_bytes;
-          if (r == 0) {
+          if (threadIdx.x == 0) {
             const int wrow = args.pair_mode ? pair_row : p;
             const int widx = args.order != nullptr ? __ldg(args.order + wrow) : wrow;
             mbar_expect_tx(&bar_full[stage], b_bytes);
             tma_load_3d(sa + args.a_bytes, &map_b, kb * kBK, 0, widx, &bar_full[stage]);
           }
+          const int kcol = kb * kBK + chunk * 8;
 #pragma unroll
-          for (int h = 0; h < 2; h++) {
+          for (int h = 0; h < kMaxSub; h++) {
             if (h < sub) {
-              const uint8_t *src_row = args.in + (int64_t)(src[h] < 0 ? 0 : src[h]) * args.K * 2;
-              const uint32_t dst_row = smem_u32(sa) + (uint32_t)(h * kBM + r) * 128u;
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const int kcol = kb * kBK + j * 8;
-                const uint32_t dst = dst_row + (uint32_t)((j ^ (r & 7)) << 4);
-                const bool valid = src[h] >= 0 && kcol < args.K;
-                cp_async_16(dst, valid ? src_row + (size_t)kcol * 2 : args.in, valid ? 16u : 0u);
+              for (int i = 0; i < 8; i++) {
+                const int owner = 4 * i + (lane >> 3);           // lane that holds this row's index
+                const int s_idx = __shfl_sync(0xffffffffu, src[h], owner);
+                const int rr = warp * 32 + owner;                 // row inside the sub-tile
+                const uint32_t dst = smem_u32(sa) + (uint32_t)(h * kBM + rr) * 128u +
+                                     (uint32_t)((chunk ^ (rr & 7)) << 4);
+                const bool valid = s_idx >= 0 && kcol < args.K;
+                cp_async_16(dst, valid ? args.in + ((int64_t)s_idx * args.K + kcol) * 2 : args.in,
+                            valid ? 16u : 0u);
               }
             }
           }
-          // this thread's arrival fires when its copies above have landed: no stall here
+          // this lane's arrival fires when its copies above have landed: no stall here
           asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
                            smem_u32(&bar_full[stage]))
                        : "memory");
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         p = p_next;
-        src[0] = src_next[0];
-        src[1] = src_next[1];
+#pragma unroll
+        for (int h = 0; h < kMaxSub; h++) src[h] = src_next[h];
       }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this thread is in flight at exit
+    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this lane is in flight at exit
   } else if (warp == 4) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
@@ -241,6 +250,15 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
     uint32_t acc_phase = 0;
     const int n = args.N;
     for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
+      if (args.residual != nullptr) {
+        // the residual rows of this lane are on their way while the MMAs run
+        for (int h = 0; h < args.sub; h++) {
+          const int64_t rrow = (int64_t)(tile * args.sub + h) * kBM + quarter * 32 + lane;
+          if (rrow < args.T)
+            for (int off = 0; off < n * 2; off += 128)
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(args.residual + rrow * n * 2 + off));
+        }
+      }
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -259,70 +277,79 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
                              (uint32_t)((acc * args.sub + h) * args.n_pad);
       for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
         uint8_t *buf = cbuf + (chunk & 1) * 4096;
-        uint32_t rr[64];
-        tmem_ld_32x32(taddr + (uint32_t)c0, *reinterpret_cast<uint32_t (*)[32]>(&rr[0]));
-        if (c0 + 32 < args.n_pad) {
-          tmem_ld_32x32(taddr + (uint32_t)c0 + 32u, *reinterpret_cast<uint32_t (*)[32]>(&rr[32]));
-        } else {
+        bool buffer_free = false;
+        // 32 columns at a time: the two halves fill one 64-column staging tile
+        for (int half = 0; half < 2; half++) {
+          const int cb = c0 + 32 * half;
+          if (cb >= args.n_pad) break;
+          uint32_t rr[32];
+          tmem_ld_32x32(taddr + (uint32_t)cb, rr);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (args.out_f32 != nullptr) {
+            // pair mode: the fp32 accumulators of this row go out as they are
+            if (row < args.T) {
+              float4 *dst = reinterpret_cast<float4 *>(args.out_f32 + row * n + cb);
 #pragma unroll
-          for (int i = 32; i < 64; i++) rr[i] = 0u;
-        }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (args.out_f32 != nullptr) {
-          // pair mode: the fp32 accumulators of this row go out as they are
-          if (row < args.T) {
-            float4 *dst = reinterpret_cast<float4 *>(args.out_f32 + row * n + c0);
-#pragma unroll
-            for (int v = 0; v < 16; v++)
-              if (c0 + 4 * v < n)
-                dst[v] = make_float4(__uint_as_float(rr[4 * v]), __uint_as_float(rr[4 * v + 1]),
-                                     __uint_as_float(rr[4 * v + 2]), __uint_as_float(rr[4 * v + 3]));
+              for (int v = 0; v < 8; v++)
+                if (cb + 4 * v < n)
+                  dst[v] = make_float4(__uint_as_float(rr[4 * v]), __uint_as_float(rr[4 * v + 1]),
+                                       __uint_as_float(rr[4 * v + 2]), __uint_as_float(rr[4 * v + 3]));
+            }
+            continue;
           }
-          continue;
-        }
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        __syncwarp();
-#pragma unroll
-        for (int v = 0; v < 8; v++) {
-          float f[8];
-#pragma unroll
-          for (int i = 0; i < 8; i++) f[i] = empty_tile ? 0.f : __uint_as_float(rr[v * 8 + i]);
-          const int c = c0 + v * 8;
-          if (c < n) {
-            if (args.scale != nullptr) {
-#pragma unroll
-              for (int i = 0; i < 8; i++) f[i] *= __ldg(args.scale + c + i);
-            }
-            if (args.shift != nullptr) {
-#pragma unroll
-              for (int i = 0; i < 8; i++) f[i] += __ldg(args.shift + c + i);
-            }
-            if (args.residual != nullptr && row < args.T) {
-              const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(args.residual + (row * n + c) * 2));
-              const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
-#pragma unroll
-              for (int i = 0; i < 8; i++)
-                f[i] += args.elem_is_bf16 ? elem_to_f32<true>(r16[i]) : elem_to_f32<false>(r16[i]);
-            }
-            if (args.relu) {
-#pragma unroll
-              for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
-            }
+          if (!buffer_free) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            buffer_free = true;
           }
-          uint4 out;
-          uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
 #pragma unroll
-          for (int h = 0; h < 4; h++) {
-            if (args.elem_is_bf16) {
-              __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * h], f[2 * h + 1]);
-              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
-            } else {
-              __half2 pk = __floats2half2_rn(f[2 * h], f[2 * h + 1]);
-              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+          for (int v = 0; v < 4; v++) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = empty_tile ? 0.f : __uint_as_float(rr[v * 8 + i]);
+            const int c = cb + v * 8;
+            if (c < n) {
+              if (args.scale != nullptr) {   // n is a multiple of 8 here
+                const float4 s0 = __ldg(reinterpret_cast<const float4 *>(args.scale + c));
+                const float4 s1 = __ldg(reinterpret_cast<const float4 *>(args.scale + c) + 1);
+                f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
+                f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
+              }
+              if (args.shift != nullptr) {
+                const float4 s0 = __ldg(reinterpret_cast<const float4 *>(args.shift + c));
+                const float4 s1 = __ldg(reinterpret_cast<const float4 *>(args.shift + c) + 1);
+                f[0] += s0.x; f[1] += s0.y; f[2] += s0.z; f[3] += s0.w;
+                f[4] += s1.x; f[5] += s1.y; f[6] += s1.z; f[7] += s1.w;
+              }
+              if (args.residual != nullptr && row < args.T) {
+                const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(args.residual + (row * n + c) * 2));
+                const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                  f[i] += args.elem_is_bf16 ? elem_to_f32<true>(r16[i]) : elem_to_f32<false>(r16[i]);
+              }
+              if (args.relu) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
+              }
             }
+            uint4 out;
+            uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+              if (args.elem_is_bf16) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * h], f[2 * h + 1]);
+                o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+              } else {
+                __half2 pk = __floats2half2_rn(f[2 * h], f[2 * h + 1]);
+                o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+              }
+            }
+            const int piece = half * 4 + v;
+            *reinterpret_cast<uint4 *>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = out;
           }
-          *reinterpret_cast<uint4 *>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = out;
         }
+        if (args.out_f32 != nullptr) continue;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
@@ -427,7 +454,10 @@ mn_status launch_pair_products(const PairPlan &plan, int64_t S, int64_t c_in, in
   a.acc_bufs = 2;
   a.a_bytes = kBM * kBK * 2;
   a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
-  a.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / a.stage_bytes));
+  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, 3);
+  a.stages = sizing.stages;
+  a.tmem_cols = sizing.tmem_cols;
+  a.num_offsets = 1;
   a.elem_is_bf16 = bf16 ? 1 : 0;
   a.num_tiles = a.n_tiles128;
   a.pair_mode = 1;
@@ -436,11 +466,10 @@ mn_status launch_pair_products(const PairPlan &plan, int64_t S, int64_t c_in, in
   a.out_f32 = products;
   CUtensorMap map_b;
   MN_RETURN_IF(make_kmajor_map(&map_b, weights_t, bf16, c_in, c_out, O, a.n_pad));
-  const size_t smem =
-      std::max<size_t>((size_t)a.stages * a.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
+  const size_t smem = sizing.smem_bytes;
   MN_CHECK_CUDA(cudaFuncSetAttribute(conv_implicit_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int grid = std::min(a.num_tiles, kNumSMs);
+  const int grid = std::min(a.num_tiles, kNumSMs * sizing.ctas_per_sm);
   // the output map is not used in pair mode; any valid map will do
   MN_LAUNCH("conv_implicit_kernel<pairs>", st,
             conv_implicit_kernel<<<grid, kImThreads, smem, st>>>(a, map_b, map_b));
@@ -500,7 +529,8 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
     const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
     const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
-    void *targets_out, int32_t *status_dev, void *ws_ptr, size_t ws_bytes, void *stream) {
+    double pairs_per_row, int sub_hint, void *targets_out, int32_t *status_dev, void *ws_ptr,
+    size_t ws_bytes, void *stream) {
   if (!mn_implicit_supported(O, c_in, c_out, dtype)) {
     set_error("implicit forward: needs fp16/bf16, at most 32 offsets, channels multiple of 8, "
               "c_out <= 256 (got O=%lld c_in=%lld c_out=%lld dtype=%d)", (long long)O,
@@ -536,17 +566,32 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   a.N = (int)c_out;
   a.n_pad = (int)align_up((size_t)c_out, 16);
   a.k_blocks = (int)div_up(c_in, kBK);
-  // two 128-row sub-tiles per CTA tile halve the weight traffic per output row; keep one
-  // when the job would otherwise not fill the SMs
   a.n_tiles128 = (int)div_up(T, kBM);
-  // (with one accumulator set the epilogue no longer overlaps the next tile's MMAs, which
-  // only pays off when a tile has many pipeline stages)
-  const bool two_sets_fit = 2 * 2 * a.n_pad <= 512;
-  a.sub = (a.n_tiles128 >= 2 * 2 * kNumSMs && (two_sets_fit || O * a.k_blocks >= 32)) ? 2 : 1;
+  // Sub-tiles per CTA tile.  Every sub-tile of a CTA tile reuses the weight tile of a stage,
+  // at the price of a shallower ring and, past 512 / (2 * n_pad) sub-tiles, a single
+  // accumulator buffer (the epilogue then no longer overlaps the next tile's MMAs).  The
+  // automatic choice is the one that measured fastest per output width on maps with two or
+  // more pairs per row (4 sub-tiles at 64 columns, 1 at 128, 2 at 256 and at 32); sparse
+  // maps keep small CTA tiles and several CTAs per SM.  Callers that have timed the layer
+  // pass their own choice.
+  int sub = sub_hint;
+  if (sub <= 0) {
+    sub = 1;
+    if (pairs_per_row >= 2.0) sub = a.n_pad >= 256 ? 2 : a.n_pad >= 128 ? 1 : a.n_pad >= 64 ? 4 : 2;
+    while (sub > 1 && (sub * a.n_pad > 512 || a.n_tiles128 < 2 * sub * kNumSMs ||
+                       2 * (sub * kBM * kBK * 2 + a.n_pad * kBK * 2) + 4 * 8192 + 2048 > 227 * 1024))
+      sub--;
+  }
+  MN_CHECK_ARG(sub >= 1 && sub <= kMaxSub && sub * a.n_pad <= 512,
+               "implicit forward: %d sub-tiles of %d columns do not fit TMEM", sub, a.n_pad);
+  a.sub = sub;
   a.acc_bufs = 2 * a.sub * a.n_pad <= 512 ? 2 : 1;
   a.a_bytes = a.sub * kBM * kBK * 2;
   a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
-  a.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / a.stage_bytes));
+  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, 3);
+  a.stages = sizing.stages;
+  a.tmem_cols = sizing.tmem_cols;
+  a.num_offsets = (int)O;
   a.elem_is_bf16 = bf16 ? 1 : 0;
   a.num_tiles = (int)div_up(a.n_tiles128, a.sub);
   a.relu = relu ? 1 : 0;
@@ -554,11 +599,10 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   CUtensorMap map_b, map_out;
   MN_RETURN_IF(make_kmajor_map(&map_b, weights_t, bf16, c_in, c_out, O, a.n_pad));
   MN_RETURN_IF(make_kmajor_map(&map_out, targets_out, bf16, c_out, T, 0, 32));
-  const size_t smem =
-      std::max<size_t>((size_t)a.stages * a.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
+  const size_t smem = sizing.smem_bytes;
   MN_CHECK_CUDA(cudaFuncSetAttribute(conv_implicit_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int grid = std::min(a.num_tiles, kNumSMs);
+  const int grid = std::min(a.num_tiles, kNumSMs * sizing.ctas_per_sm);
   MN_LAUNCH("conv_implicit_kernel", st,
             conv_implicit_kernel<<<grid, kImThreads, smem, st>>>(a, map_b, map_out));
   return MN_OK;

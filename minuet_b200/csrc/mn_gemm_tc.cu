@@ -41,6 +41,7 @@ struct TcArgs {
   int32_t n_pad;         // c_out rounded up to 16 (UMMA N)
   int32_t c_out;
   int32_t stages;
+  int32_t tmem_cols;     // TMEM columns this CTA allocates (two accumulators)
   int32_t a_bytes;       // bytes of one A stage (16 KB)
   int32_t stage_bytes;   // A + B bytes of one stage
   int32_t elem_is_bf16;
@@ -68,7 +69,7 @@ __device__ __forceinline__ TilePos locate_tile(const GemmTable &tab, int tile) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 4)
 gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ TcArgs args,
                const __grid_constant__ CUtensorMap map_a,       // gather buffer  [rows, K]
                const __grid_constant__ CUtensorMap map_direct,  // input features [S, K]
@@ -88,7 +89,7 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = args.stages;
-  const uint32_t tmem_cols = 512;
+  const uint32_t tmem_cols = (uint32_t)args.tmem_cols;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
@@ -180,42 +181,64 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
     for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
       const TilePos pos = locate_tile(tab, tile);
       const int p = pos.problem;
+      const bool direct = tab.direct[p] != 0;
+      const int out_row = (direct ? 0 : (int)tab.a_row[p]) + pos.m0 + quarter * 32;
+      // the hit word of this lane's output row and the first product row it names are
+      // fetched while the tile's MMAs are still in flight
+      uint32_t hit_word = 0u;
+      int first_hit = -1;
+      int64_t first_row = 0;
+      if (direct && args.fused_epilogue && ep.bits != nullptr && (int64_t)out_row + lane < ep.T) {
+        const int64_t t = (int64_t)out_row + lane;
+        hit_word = __ldg(ep.bits + t) & ep.keep;
+        if (hit_word != 0u) {
+          first_hit = __ffs(hit_word) - 1;
+          first_row = ep.row_begin[first_hit] + __ldg(ep.target_masks + (int64_t)first_hit * ep.T + t);
+          const char *prow = reinterpret_cast<const char *>(ep.products + first_row * args.c_out);
+          for (int off = 0; off < args.c_out * 4; off += 128)
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(prow + off));
+        }
+      }
+      if (direct && args.fused_epilogue && ep.residual != nullptr && (int64_t)out_row + lane < ep.T) {
+        // the residual row of this lane is on its way while the MMAs run
+        const char *rrow = static_cast<const char *>(ep.residual) +
+                           ((int64_t)out_row + lane) * args.c_out * 2;
+        for (int off = 0; off < args.c_out * 2; off += 128)
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(rrow + off));
+      }
       int ok = 1;   // one lane polls the barrier, the warp follows
       if (lane == 0) ok = mbar_wait(&bar_acc_full[acc], acc_phase, abort_flag, args.status) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool direct = tab.direct[p] != 0;
-      const int out_row = (direct ? 0 : (int)tab.a_row[p]) + pos.m0 + quarter * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * args.n_pad);
       for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
         uint8_t *buf = cbuf + (chunk & 1) * 4096;
-        uint32_t r[64];
-        tmem_ld_32x32(taddr + (uint32_t)c0, *reinterpret_cast<uint32_t (*)[32]>(&r[0]));
-        if (c0 + 32 < args.n_pad) {
-          tmem_ld_32x32(taddr + (uint32_t)c0 + 32u, *reinterpret_cast<uint32_t (*)[32]>(&r[32]));
-        } else {
-#pragma unroll
-          for (int i = 32; i < 64; i++) r[i] = 0u;
-        }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (direct && args.fused_epilogue) {
-          const int64_t t = (int64_t)out_row + lane;
-          const int n = args.c_out;
-          if (t < ep.T) {
-            if (ep.bits != nullptr) {
+        bool buffer_free = false;
+        // 32 columns at a time (a 64-column register tile would cap the kernel at one
+        // CTA per SM); the two halves fill one 64-column staging tile
+        for (int half = 0; half < 2; half++) {
+          const int cb = c0 + 32 * half;
+          if (cb >= args.n_pad) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + (uint32_t)cb, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (direct && args.fused_epilogue) {
+            const int64_t t = (int64_t)out_row + lane;
+            const int n = args.c_out;
+            if (t < ep.T) {
               // the other offsets' products of this output row, named by its hit word
-              uint32_t w = __ldg(ep.bits + t) & ep.keep;
+              uint32_t w = hit_word;
               while (w != 0u) {
                 const int pr = __ffs(w) - 1;
                 w &= w - 1u;
-                const int m = __ldg(ep.target_masks + (int64_t)pr * ep.T + t);
-                if (m < 0) continue;
-                const float4 *src = reinterpret_cast<const float4 *>(
-                    ep.products + (ep.row_begin[pr] + m) * n + c0);
+                const int64_t prow = pr == first_hit
+                    ? first_row
+                    : ep.row_begin[pr] + __ldg(ep.target_masks + (int64_t)pr * ep.T + t);
+                const float4 *src = reinterpret_cast<const float4 *>(ep.products + prow * n + cb);
 #pragma unroll
-                for (int v = 0; v < 16; v++) {
-                  if (c0 + 4 * v < n) {
+                for (int v = 0; v < 8; v++) {
+                  if (cb + 4 * v < n) {
                     const float4 a = __ldg(src + v);
                     r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + a.x);
                     r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + a.y);
@@ -224,85 +247,107 @@ gemm_tc_kernel(const __grid_constant__ GemmTable tab, const __grid_constant__ Tc
                   }
                 }
               }
-            }
 #pragma unroll
-            for (int v = 0; v < 8; v++) {
-              const int c = c0 + v * 8;
-              if (c < n) {
-                float f[8];
+              for (int v = 0; v < 4; v++) {
+                const int c = cb + v * 8;
+                if (c < n) {
+                  float f[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[v * 8 + i]);
-                if (ep.scale != nullptr) {
+                  for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[v * 8 + i]);
+                  if (ep.scale != nullptr) {
+                    if (c + 8 <= n) {
+                      const float4 s0 = __ldg(reinterpret_cast<const float4 *>(ep.scale + c));
+                      const float4 s1 = __ldg(reinterpret_cast<const float4 *>(ep.scale + c) + 1);
+                      f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
+                      f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
+                    } else {
+                      for (int i = 0; i < 8 && c + i < n; i++) f[i] *= __ldg(ep.scale + c + i);
+                    }
+                  }
+                  if (ep.shift != nullptr) {
+                    if (c + 8 <= n) {
+                      const float4 s0 = __ldg(reinterpret_cast<const float4 *>(ep.shift + c));
+                      const float4 s1 = __ldg(reinterpret_cast<const float4 *>(ep.shift + c) + 1);
+                      f[0] += s0.x; f[1] += s0.y; f[2] += s0.z; f[3] += s0.w;
+                      f[4] += s1.x; f[5] += s1.y; f[6] += s1.z; f[7] += s1.w;
+                    } else {
+                      for (int i = 0; i < 8 && c + i < n; i++) f[i] += __ldg(ep.shift + c + i);
+                    }
+                  }
+                  if (ep.residual != nullptr && c + 8 <= n) {
+                    const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(
+                        static_cast<const uint8_t *>(ep.residual) + (t * n + c) * 2));
+                    const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
 #pragma unroll
-                  for (int i = 0; i < 8; i++) f[i] *= __ldg(ep.scale + c + i);
-                }
-                if (ep.shift != nullptr) {
+                    for (int i = 0; i < 8; i++)
+                      f[i] += args.elem_is_bf16 ? __uint_as_float((uint32_t)r16[i] << 16)
+                                                : __half2float(__ushort_as_half(r16[i]));
+                  } else if (ep.residual != nullptr) {
+                    const uint16_t *r16 = static_cast<const uint16_t *>(ep.residual) + t * n + c;
+                    for (int i = 0; i < 8 && c + i < n; i++)
+                      f[i] += args.elem_is_bf16 ? __uint_as_float((uint32_t)r16[i] << 16)
+                                                : __half2float(__ushort_as_half(r16[i]));
+                  }
+                  if (ep.relu) {
 #pragma unroll
-                  for (int i = 0; i < 8; i++) f[i] += __ldg(ep.shift + c + i);
-                }
-                if (ep.residual != nullptr) {
-                  const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(
-                      static_cast<const uint8_t *>(ep.residual) + (t * n + c) * 2));
-                  const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
+                    for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
+                  }
 #pragma unroll
-                  for (int i = 0; i < 8; i++)
-                    f[i] += args.elem_is_bf16 ? __uint_as_float((uint32_t)r16[i] << 16)
-                                              : __half2float(__ushort_as_half(r16[i]));
-                }
-                if (ep.relu) {
-#pragma unroll
-                  for (int i = 0; i < 8; i++) f[i] = fmaxf(f[i], 0.f);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; i++) r[v * 8 + i] = __float_as_uint(f[i]);
-              }
-            }
-          }
-        }
-        if (args.plain_store) {
-          // row pitch not a multiple of 16 bytes: no tensor map exists for this output
-          const int64_t t = (int64_t)out_row + lane;
-          if (t < args.out_rows) {
-            uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(args.out_plain) +
-                                                         t * args.c_out + c0);
-#pragma unroll
-            for (int h = 0; h < 32; h++) {
-              if (c0 + 2 * h + 1 < args.c_out) {
-                const float lo = __uint_as_float(r[2 * h]), hi = __uint_as_float(r[2 * h + 1]);
-                if (args.elem_is_bf16) {
-                  __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
-                  dst[h] = *reinterpret_cast<uint32_t *>(&pk);
-                } else {
-                  __half2 pk = __floats2half2_rn(lo, hi);
-                  dst[h] = *reinterpret_cast<uint32_t *>(&pk);
+                  for (int i = 0; i < 8; i++) r[v * 8 + i] = __float_as_uint(f[i]);
                 }
               }
             }
           }
-          continue;
-        }
-        // the store that last read this buffer (two chunks ago) must be done with it
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        __syncwarp();
+          if (args.plain_store) {
+            // row pitch not a multiple of 16 bytes: no tensor map exists for this output
+            const int64_t t = (int64_t)out_row + lane;
+            if (t < args.out_rows) {
+              uint32_t *dst = reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(args.out_plain) +
+                                                           t * args.c_out + cb);
 #pragma unroll
-        for (int v = 0; v < 8; v++) {         // 8 outputs = one 16-byte piece of the row
-          uint4 out;
-          uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
-#pragma unroll
-          for (int h = 0; h < 4; h++) {
-            const float lo = __uint_as_float(r[v * 8 + 2 * h]);
-            const float hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
-            if (args.elem_is_bf16) {
-              __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
-              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
-            } else {
-              __half2 pk = __floats2half2_rn(lo, hi);
-              o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+              for (int h = 0; h < 16; h++) {
+                if (cb + 2 * h + 1 < args.c_out) {
+                  const float lo = __uint_as_float(r[2 * h]), hi = __uint_as_float(r[2 * h + 1]);
+                  if (args.elem_is_bf16) {
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+                    dst[h] = *reinterpret_cast<uint32_t *>(&pk);
+                  } else {
+                    __half2 pk = __floats2half2_rn(lo, hi);
+                    dst[h] = *reinterpret_cast<uint32_t *>(&pk);
+                  }
+                }
+              }
             }
+            continue;
           }
-          // 128-byte swizzle: 16-byte piece v of row `lane` lives at piece v ^ (lane % 8)
-          *reinterpret_cast<uint4 *>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) = out;
+          if (!buffer_free) {
+            // the store that last read this buffer (two chunks ago) must be done with it
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            buffer_free = true;
+          }
+#pragma unroll
+          for (int v = 0; v < 4; v++) {         // 8 outputs = one 16-byte piece of the row
+            uint4 out;
+            uint32_t *o32 = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+              const float lo = __uint_as_float(r[v * 8 + 2 * h]);
+              const float hi = __uint_as_float(r[v * 8 + 2 * h + 1]);
+              if (args.elem_is_bf16) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+                o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+              } else {
+                __half2 pk = __floats2half2_rn(lo, hi);
+                o32[h] = *reinterpret_cast<uint32_t *>(&pk);
+              }
+            }
+            // 128-byte swizzle: 16-byte piece v of row `lane` lives at piece v ^ (lane % 8)
+            const int piece = half * 4 + v;
+            *reinterpret_cast<uint4 *>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = out;
+          }
         }
+        if (args.plain_store) continue;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
@@ -509,8 +554,9 @@ mn_status launch_gemm_tc_impl(const GemmTable &tab_in, const TcOperands &ops, in
   args.c_out = c_out;
   args.a_bytes = kBM * kBK * 2;
   args.stage_bytes = args.a_bytes + args.n_pad * kBK * 2;
-  // 227 KB per CTA: 1 KB alignment slack + 32 KB of epilogue tiles + the operand ring
-  args.stages = std::min(kMaxStages, std::max(2, (192 * 1024) / args.stage_bytes));
+  const TcSizing sizing = size_tc_kernel(args.stage_bytes, 2 * args.n_pad, kMaxStages, 4);
+  args.stages = sizing.stages;
+  args.tmem_cols = sizing.tmem_cols;
   args.elem_is_bf16 = bf16 ? 1 : 0;
   args.total_tiles = total_tiles;
   args.order = order;
@@ -553,11 +599,8 @@ mn_status launch_gemm_tc_impl(const GemmTable &tab_in, const TcOperands &ops, in
     MN_RETURN_IF(make_kmajor_map(&map_c_direct, out_base, bf16, c_out, out_rows, 0, 32));
   }
 
-  // at least 120 KB so that two CTAs (each allocating all 512 TMEM columns) can
-  // never share an SM
-  const size_t smem =
-      std::max<size_t>((size_t)args.stages * args.stage_bytes + 4 * 8192 + 1024, 120 * 1024);
-  const int grid = std::min(total_tiles, kNumSMs);
+  const size_t smem = sizing.smem_bytes;
+  const int grid = std::min(total_tiles, kNumSMs * sizing.ctas_per_sm);
   if (bf16) {
     MN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -3,6 +3,8 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "mn_common.cuh"
 
 namespace mn {
@@ -117,6 +119,36 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 
 
 }  // namespace tc
+
+// Shared-memory ring depth, TMEM columns and CTAs per SM of a tensor-core kernel.
+// These layers are bound by memory latency, not by the tensor pipe (a 128-row tile
+// of a 32-channel layer is 16 KB of traffic and a microsecond of dependent loads),
+// so as many CTAs as fit share an SM, each with a short ring and only the TMEM
+// columns its accumulators need.
+struct TcSizing {
+  int stages;
+  int tmem_cols;      // power of two >= 32
+  int ctas_per_sm;
+  size_t smem_bytes;  // dynamic shared memory per CTA
+};
+inline TcSizing size_tc_kernel(int stage_bytes, int acc_cols, int max_stages, int max_ctas,
+                               int extra_bytes = 0) {
+  TcSizing z{};
+  z.tmem_cols = 32;
+  while (z.tmem_cols < acc_cols) z.tmem_cols *= 2;
+  const int extra = 4 * 8192 + 1024 + extra_bytes;   // epilogue staging tiles + alignment slack
+  for (int ctas = std::min(max_ctas, 512 / z.tmem_cols); ctas >= 1; ctas--) {
+    const int budget = (227 * 1024) / ctas - 2048;   // static shared memory and reserve
+    const int stages = std::min(max_stages, (budget - extra) / stage_bytes);
+    if (stages >= 2 || ctas == 1) {
+      z.ctas_per_sm = ctas;
+      z.stages = std::max(2, ctas == 1 ? stages : std::min(stages, 4));
+      break;
+    }
+  }
+  z.smem_bytes = (size_t)z.stages * stage_bytes + extra;
+  return z;
+}
 
 // ---- pair-list forward (mn_conv_pairs.cu) -------------------------------------------
 constexpr int MN_MAX_PAIR_ROWS = 32;

@@ -17,6 +17,8 @@ GEMM_PARALLEL_LEVEL = 4
 # scatter, "implicit" = the fused output-stationary kernel, "auto" = time both the
 # first time a layer shape / map density is seen and keep the faster one
 ALGORITHM = "auto"
+# 128-row sub-tiles per CTA tile of the fused kernel (0 = chosen by the library)
+IMPLICIT_SUB_TILES = 0
 _algorithm_choice = {}
 
 
@@ -246,6 +248,7 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
         S, T, O, c_in, c_out, engine.dtype_code(weights.dtype), engine.ptr(sources),
         engine.ptr(weights), engine.ptr(nbr), engine.ptr(tile_bits), engine.ptr(order),
         engine.ptr(scale), engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
+        float(sizes_host.sum()) / max(T, 1), int(IMPLICIT_SUB_TILES),
         engine.ptr(out), engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
         engine.stream_ptr(device)), "sparse_convolution_forward_implicit")
     return out
