@@ -3,11 +3,17 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Workload: a batch of 4 outdoor-scan-like clouds of 120 000 voxels per GPU; one
-step builds, on a cold KernelMapCache, the four kernel maps
+BUILD makes, on a cold KernelMapCache, the four kernel maps
 (kernel 3^3 / 2^3) x (stride 1 / 2), including the strided target coordinates
-(floor, sort, unique).  The metric is source voxels processed per second, summed
-over the four maps (Mvoxels/s).  With N > 1 every rank owns its own batch (weak
-scaling, no collective on the data path); the time is the max over ranks.
+(floor, sort, unique); one STEP is --repeats such builds back to back (so that the
+timed region is long enough for the clock sampler).  The metric is source voxels
+processed per second, summed over the four maps (Mvoxels/s).  With N > 1 every
+rank owns its own batch (weak scaling, no collective on the data path); the time
+is the max over ranks.
+
+The same line carries the gather / GEMM / scatter sweep over channel widths
+("gms_sweep") and the sparse-UNet forward on 64 clouds ("unet") with its own
+roofline and CPU baseline.
 
 Prints ONE JSON line on rank 0.
 """
@@ -32,6 +38,7 @@ CLOUDS_PER_GPU = 4
 VOXELS_PER_CLOUD = 120_000
 METRIC = "kernel-map Mvoxels/s"
 UNIT = "Mvoxels/s"
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic_map_step_C1.txt")
 
 
 def measured_peaks():
@@ -45,7 +52,9 @@ def measured_peaks():
 # ---------------------------------------------------------------------------
 # CPU arm: the oracle restatement on the host cores
 # ---------------------------------------------------------------------------
-def oracle_step(oracle, coords, bd, offsets):
+def oracle_step(oracle, coords, bd, offsets, repeats=1):
+    for _ in range(repeats - 1):
+        oracle_step(oracle, coords, bd, offsets)
     tgt2, tbd2 = oracle.downsample(coords, 2, bd)
     out = []
     for kernel, stride in MAPS:
@@ -54,7 +63,7 @@ def oracle_step(oracle, coords, bd, offsets):
     return out
 
 
-def run_cpu(steps, warmup, coords, bd, min_seconds=0.0):
+def run_cpu(steps, warmup, coords, bd, min_seconds=0.0, repeats=1):
     # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     os.environ["OMP_NUM_THREADS"] = str(cores)
@@ -64,14 +73,14 @@ def run_cpu(steps, warmup, coords, bd, min_seconds=0.0):
     oracle.set_num_threads(cores)
     offsets = {k: generate_kernel_offsets(3, k, 1, 1).astype(np.int32) for k in (2, 3)}
     for _ in range(warmup):
-        oracle_step(oracle, coords, bd, offsets)
+        oracle_step(oracle, coords, bd, offsets, repeats)
     t0 = time.perf_counter()
     done = 0
     while done < steps or time.perf_counter() - t0 < min_seconds:
-        oracle_step(oracle, coords, bd, offsets)
+        oracle_step(oracle, coords, bd, offsets, repeats)
         done += 1
     dt = time.perf_counter() - t0
-    voxels = len(MAPS) * len(coords) * done
+    voxels = len(MAPS) * len(coords) * done * repeats
     return voxels / dt / 1e6, dt / done * 1e3, done, oracle.num_threads()
 
 
@@ -84,15 +93,18 @@ def reference_arm(args):
         return
     from minuet_b200 import synth
     coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000, n_voxels=VOXELS_PER_CLOUD)
-    value, ms, done, cores = run_cpu(args.steps, args.warmup, coords, bd)
+    # a bounded sample: at most 4 builds per step, so that the driver's K steps end in minutes
+    repeats = max(1, min(args.repeats, 4))
+    value, ms, done, cores = run_cpu(args.steps, args.warmup, coords, bd, repeats=repeats)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
         "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": round(ms, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
         "data": "synthetic",
-        "config": workload_config(len(coords)),
+        "config": workload_config(len(coords), repeats),
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{done} full steps (4 cold map builds of one 4-cloud batch)"},
+                         "sample": f"{done} steps of {repeats} builds (4 cold kernel maps each) of "
+                                   "one 4-cloud batch"},
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
@@ -177,11 +189,47 @@ def reference_cuda_arm(args):
                       "config": workload_config(S)}), flush=True)
 
 
-def workload_config(n_voxels_per_gpu):
+def workload_config(n_voxels_per_gpu, repeats=1):
     return {"workload": "C1 kernel-map build: 4 outdoor clouds x ~120k voxels per GPU, maps "
                         "(3^3,s1) (2^3,s1) (3^3,s2) (2^3,s2), cold cache, int32 coords",
-            "voxels_per_gpu": int(n_voxels_per_gpu), "maps_per_step": len(MAPS),
-            "l2": "flushed between timed steps (512 MiB write); per-step outputs ~0.5 GB > L2"}
+            "voxels_per_gpu": int(n_voxels_per_gpu), "maps_per_build": len(MAPS),
+            "builds_per_step": int(repeats),
+            "l2": "flushed between timed steps (512 MiB write); every build writes ~0.22 GB of "
+                  "masks, more than L2 holds, before the next one reads its inputs"}
+
+
+def dram_traffic(kernel):
+    """Measured DRAM bytes per build of one kernel name, from the committed table
+    (columns: kernel, launches per build, read bytes, written bytes), or None."""
+    if not os.path.exists(TRAFFIC_TABLE):
+        return None
+    with open(TRAFFIC_TABLE) as f:
+        for row in f:
+            cols = row.split()
+            if len(cols) >= 4 and cols[0] == kernel:
+                try:
+                    return float(cols[2]) + float(cols[3])
+                except ValueError:
+                    return None
+    return None
+
+
+def profile_kernels(lib, fn, reps):
+    """Per-kernel launch counts and device milliseconds (the library's own event pairs
+    around every launch, on the launching stream) over ``reps`` calls of ``fn``."""
+    import torch
+    lib.mn_profile_enable(1)
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    lib.mn_profile_enable(0)
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.mn_profile_report(buf, len(buf))
+    out = {}
+    for row in buf.value.decode().splitlines():
+        name, count, ms = row.rsplit(" ", 2)
+        out[name] = {"launches": int(count) / reps, "ms": float(ms) / reps}
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -202,7 +250,7 @@ class ClockSampler:
         os.close(fd)
         self.out = open(self.path, "w")
         self.proc = subprocess.Popen([exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader",
-                                      "-i", str(gpu_index), "-lms", "100"],
+                                      "-i", str(gpu_index), "-lms", "50"],
                                      stdout=self.out, stderr=subprocess.DEVNULL)
 
     def stop(self, windows=()):
@@ -246,28 +294,34 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
-def kernel_bytes(name, S, T_by_stride, num_clouds):
-    """Algorithmic bytes per step of one kernel name, summed over its launches.
-    S source voxels; T target voxels per kernel stride; O = k^3."""
+def kernel_bytes(name, S, T2, num_clouds):
+    """Algorithmic bytes per BUILD of one kernel name, summed over its launches.
+    S source voxels; T2 stride-2 target voxels; O = k^3 offsets per map."""
+    T_of = {1: S, 2: T2}
     total = 0
     for kernel, stride in MAPS:
-        O, T = kernel ** 3, T_by_stride[stride]
+        O, T = kernel ** 3, T_of[stride]
         mirrored = stride == 1 and kernel % 2 == 1
         if name == "emit_masks_kernel":
-            total += 4 * O * (S + T) + 4 * (S + T)          # masks written, hit words read
-        elif name == "search_kernel<bits>":
-            total += 8 * (S + T) + 4 * T + 4 * O * ((T + 1023) // 1024)   # keys read, words + counts written
-            if not mirrored:
-                total += 8 * (S + T) + 4 * S + 4 * O * ((S + 1023) // 1024)
-    if name == "pack_kernel":
-        total = (12 + 8) * S * 2                              # source keys + floored keys
+            # hit words read, both masks and the row-ordered hit words written
+            total += 4 * (S + T) + 4 * O * (S + T) + 4 * (S + T)
+        elif name == "search_kernel<bits>" and mirrored:
+            total += 8 * S + 4 * T                    # keys read once (S == T), words written
+        elif name == "search_kernel<bits,rev>" and not mirrored:
+            total += 8 * (S + T) + 4 * (S + T)        # both key arrays read, both word arrays written
+    if name == "root_keys_kernel":
+        total = 12 * S + 8 * S                        # coordinates read, packed keys written
+    elif name == "radix_sort_kernel":
+        total = 12 * S + 8 * S                        # coordinates read (floored + packed on the fly), sorted keys written
+    elif name == "unique_keys_kernel":
+        total = 8 * S + (12 + 8) * T2 + 8 * (num_clouds + 3)   # keys read, coordinates + keys written
     return total
 
 
 def gpu_arm(args):
     import torch
     import minuet_b200 as minuet
-    from minuet_b200 import _lib, synth
+    from minuet_b200 import _lib, engine, synth
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -284,6 +338,7 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
 
     lib = _lib.load()
+    R = max(1, args.repeats)
     coords, bd = synth.outdoor_batch(CLOUDS_PER_GPU, seed0=1000 + 100 * rank,
                                      n_voxels=VOXELS_PER_CLOUD)
     S = len(coords)
@@ -293,13 +348,17 @@ def gpu_arm(args):
     cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
-    def step(c, b):
+    def build(c, b):
         cache.reset()
         out = []
         for kernel, stride in MAPS:
             tc, ts, tbd = cache.get_target_coordinates(c, b, 1, stride)
             out.append(cache.get_kernel_map(c, 1, b, tc, ts, tbd, kernel, 1))
         return out
+
+    def step():
+        for _ in range(R):
+            build(d_coords, d_bd)
 
     def barrier():
         torch.cuda.synchronize()
@@ -322,27 +381,32 @@ def gpu_arm(args):
 
     sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
-        step(d_coords, d_bd)
-    T_by_stride = {1: S, 2: int(cache.get_target_coordinates(d_coords, d_bd, 1, 2)[0].shape[0])}
+        step()
+    T2 = int(cache.get_target_coordinates(d_coords, d_bd, 1, 2)[0].shape[0])
+    engine.check_status(dev)
 
     # ---- device-resident inputs ------------------------------------------------
     barrier()
     launches0 = lib.mn_launch_count()
     w0 = time.time()
-    ms_total = timed(lambda: step(d_coords, d_bd), args.steps)
+    ms_total = timed(step, args.steps)
     barrier()
     w1 = time.time()
     t_wall = w1 - w0
     launches = lib.mn_launch_count() - launches0
 
-    # ---- host buffers in, sizes/order out (end to end) ---------------------------
+    # ---- host buffers in, sizes out (end to end) ---------------------------------
     def e2e_step():
-        c = h_coords.to(dev, non_blocking=True)
-        b = h_bd.to(dev, non_blocking=True)
-        out = step(c, b)
-        # the masks stay on the GPU for the convolutions; what the host consumes
-        # per map is the size-sorted order
-        return torch.cat([o[2] for o in out]).cpu()      # one read for the four maps
+        got = None
+        for _ in range(R):
+            c = h_coords.to(dev, non_blocking=True)
+            b = h_bd.to(dev, non_blocking=True)
+            out = build(c, b)
+            # the masks stay on the GPU for the convolutions; what the host consumes per map
+            # is the per-offset sizes (they size the GEMM problems) and the status word, which
+            # every build already copies to pinned memory without a kernel of its own
+            got = [engine.host_copy(o[3]) for o in out]
+        return got
 
     for _ in range(2):
         e2e_step()
@@ -352,18 +416,20 @@ def gpu_arm(args):
     barrier()
     w3 = time.time()
     clocks = sampler.stop([(w0, w1), (w2, w3)]) if sampler is not None else None
+    engine.check_status(dev)
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e = (float(v) for v in times.cpu())
-    voxels_all = len(MAPS) * S * world      # every rank holds S voxels (same generator sizes)
+    voxels_all = len(MAPS) * S * world
     if dist is not None:
         counts = torch.tensor([len(MAPS) * S], dtype=torch.int64, device=dev)
         dist.all_reduce(counts)
         voxels_all = int(counts.item())
-    value = voxels_all * args.steps / (ms_total * 1e-3) / 1e6
-    e2e_value = voxels_all * args.steps / (ms_e2e * 1e-3) / 1e6
+    builds = args.steps * R
+    value = voxels_all * builds / (ms_total * 1e-3) / 1e6
+    e2e_value = voxels_all * builds / (ms_e2e * 1e-3) / 1e6
 
     unet = None
     if not args.no_unet:
@@ -378,63 +444,66 @@ def gpu_arm(args):
         return
 
     # ---- per-kernel times (separate, untimed pass) ---------------------------------
-    lib.mn_profile_enable(1)
-    prof_steps = 5
-    for _ in range(prof_steps):
-        flush.zero_()
-        step(d_coords, d_bd)
-    torch.cuda.synchronize()
-    lib.mn_profile_enable(0)
-    buf = ctypes.create_string_buffer(1 << 16)
-    lib.mn_profile_report(buf, len(buf))
-    kernels = {}
-    for row in buf.value.decode().splitlines():
-        name, count, ms = row.rsplit(" ", 2)
-        kernels[name] = {"launches_per_step": int(count) / prof_steps,
-                         "ms_per_step": float(ms) / prof_steps}
-    top = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
+    # The library times every launch with an event pair on the launching stream.  A pair
+    # also counts the time the stream sat idle before the launch reached the GPU, and the
+    # host needs longer to prepare a launch than these kernels run, so each group of
+    # launches is queued behind a few L2-flushing fills: the GPU is still busy with them
+    # while the host enqueues the group, and the pairs then bracket execution only.
+    def pad():
+        for _ in range(4):
+            flush.zero_()
+
+    def cold_build():
+        cache.reset()
+        for kernel, stride in MAPS:
+            pad()
+            tc, ts, tbd = cache.get_target_coordinates(d_coords, d_bd, 1, stride)
+            pad()
+            cache.get_kernel_map(d_coords, 1, d_bd, tc, ts, tbd, kernel, 1)
+
+    kernels = profile_kernels(lib, cold_build, 10)
+    top = max(kernels, key=lambda k: kernels[k]["ms"])
     peaks, peak_kind = measured_peaks()
-    top_bytes = kernel_bytes(top, S, T_by_stride, CLOUDS_PER_GPU)
-    top_ms = kernels[top]["ms_per_step"]
-    achieved = top_bytes / (top_ms * 1e-3) / 1e9 if top_bytes else None
-    stage_bytes = sum(12 * (S + T_by_stride[s]) + 4 * k ** 3 * (S + T_by_stride[s]) for k, s in MAPS)
-    stage_bytes_with_map = stage_bytes + sum(4 * k ** 3 * T_by_stride[s] for k, s in MAPS)
-    gpu_ms = sum(v["ms_per_step"] for v in kernels.values())
-    # the kernel that moves most of the step's bytes (the mask emission) next to the
-    # kernel that takes most of its time (the search, which is instruction bound)
-    byte_dominant = None
-    if "emit_masks_kernel" in kernels:
-        eb = kernel_bytes("emit_masks_kernel", S, T_by_stride, CLOUDS_PER_GPU)
-        ems = kernels["emit_masks_kernel"]["ms_per_step"]
-        byte_dominant = {"kernel": "emit_masks_kernel", "algorithmic_bytes_per_step": eb,
-                         "kernel_ms_per_step": round(ems, 4),
-                         "achieved": round(eb / (ems * 1e-3) / 1e9, 1), "unit": "GB/s",
-                         "frac": round(eb / (ems * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}
+    hbm = peaks["hbm_gbs"]
+
+    def line_of(name):
+        nbytes = kernel_bytes(name, S, T2, CLOUDS_PER_GPU)
+        ms = kernels[name]["ms"]
+        gbs = nbytes / (ms * 1e-3) / 1e9 if nbytes and ms > 0 else None
+        return {"kernel": name, "achieved": None if gbs is None else round(gbs, 1),
+                "frac": None if gbs is None else round(gbs / hbm, 4),
+                "algorithmic_bytes_per_build": nbytes, "kernel_ms_per_build": round(ms, 4),
+                "launches_per_build": kernels[name]["launches"],
+                "traffic": dram_traffic(name)}
+
+    T_of = {1: S, 2: T2}
+    stage_bytes = sum(12 * (S + T_of[s]) + 4 * k ** 3 * (S + T_of[s]) for k, s in MAPS)
+    stage_bytes_with_map = stage_bytes + sum(4 * k ** 3 * T_of[s] for k, s in MAPS)
+    gpu_ms = sum(v["ms"] for v in kernels.values())
+    ms_build = ms_total / builds
+    top_line = line_of(top)
     roofline = {
-        "bound": "hbm", "kernel": top,
-        "achieved": None if achieved is None else round(achieved, 1),
-        "peak": peaks["hbm_gbs"], "unit": "GB/s",
-        "frac": None if achieved is None else round(achieved / peaks["hbm_gbs"], 4),
-        "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured"
-        else "fallback 6650 GB/s",
-        # dram__bytes_read + dram__bytes_write of the search launches of one step under ncu
-        # (3.9 MB read per search direction, 7 directions; the hit words and tile counts they
-        # write were still in L2 when the kernels ended), profiles/search_and_emit_kernels_C1.md
-        "traffic": 27.3e6 if top.startswith("search_kernel") else None,
-        "algorithmic_bytes_per_step": top_bytes,
-        "kernel_ms_per_step": round(top_ms, 4),
-        "launches_per_step": kernels[top]["launches_per_step"],
+        "bound": "hbm", "kernel": top, "achieved": top_line["achieved"], "peak": hbm,
+        "unit": "GB/s", "frac": top_line["frac"],
+        "peak_source": ("measured (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured"
+                        else "fallback 6650 GB/s"),
+        # dram__bytes_read + dram__bytes_write of this kernel's launches of one build, from the
+        # committed ncu table; null when the table has no row for the kernel
+        "traffic": top_line["traffic"],
+        "algorithmic_bytes_per_build": top_line["algorithmic_bytes_per_build"],
+        "kernel_ms_per_build": top_line["kernel_ms_per_build"],
+        "launches_per_build": top_line["launches_per_build"],
         "whole_step": {
             "algorithmic_bytes_fused": stage_bytes,
             "algorithmic_bytes_with_kernel_map": stage_bytes_with_map,
             "gpu_busy_ms": round(gpu_ms, 4),
             "gbs_over_gpu_busy_time": round(stage_bytes / (gpu_ms * 1e-3) / 1e9, 1),
-            "gbs_over_step_time": round(stage_bytes / (ms_total / args.steps * 1e-3) / 1e9, 1),
+            "gbs_over_step_time": round(stage_bytes / (ms_build * 1e-3) / 1e9, 1),
+            "frac_over_step_time": round(stage_bytes / (ms_build * 1e-3) / 1e9 / hbm, 4),
         },
-        "byte_dominant_kernel": byte_dominant,
-        "kernels": {k: {"ms_per_step": round(v["ms_per_step"], 4),
-                        "launches_per_step": v["launches_per_step"]}
-                    for k, v in sorted(kernels.items(), key=lambda kv: -kv[1]["ms_per_step"])},
+        # the kernel that moves most of the build's bytes, next to the one that takes most time
+        "byte_dominant_kernel": line_of("emit_masks_kernel") if "emit_masks_kernel" in kernels else None,
+        "kernels": [line_of(k) for k in sorted(kernels, key=lambda k: -kernels[k]["ms"])],
     }
 
     # ---- CPU baseline on this box's host cores (bounded) ---------------------------
@@ -442,30 +511,33 @@ def gpu_arm(args):
     if world == 1 and not args.no_cpu_baseline:
         v, ms, done, cores = run_cpu(3, 1, coords, bd, min_seconds=10.0)
         cpu = {"value": round(v, 3), "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": f"{done} full steps of the same 4-cloud batch ({ms:.1f} ms/step)"}
+               "sample": f"{done} builds of the same 4-cloud batch ({ms:.1f} ms per build)"}
 
     sweep = None
-    if world == 1 and args.gms_sweep:
+    if world == 1 and not args.no_gms_sweep:
         chans = tuple(int(c) for c in args.gms_channels.split(","))
-        sweep = gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=chans)
+        sweep = gms_sweep(torch, minuet, lib, cache, d_coords, d_bd, channels=chans)
         # the same sweep on the single 50 000-voxel uniform cloud of the fp32 configuration
         u_coords = torch.from_numpy(synth.uniform_cloud()).to(dev)
         u_cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=dev)
-        sweep["uniform50k"] = gms_sweep(torch, minuet, u_cache, u_coords, None, channels=chans)
+        sweep["uniform50k"] = gms_sweep(torch, minuet, lib, u_cache, u_coords, None, channels=chans)
         sweep["uniform50k"]["map"] = "3^3 stride 1 on 50 000 uniform voxels in [0,256)^3"
 
     h2d = h_coords.numel() * 4 + h_bd.numel() * 8
-    d2h = sum((k ** 3 + 1) * 4 + k ** 3 * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8 + 32
+    # per build: sizes + status word of every map, and the stride-2 level's counts
+    d2h = sum((k ** 3 + 1) * 4 for k, _ in MAPS) + (CLOUDS_PER_GPU + 3) * 8
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-        "config": workload_config(S),
+        "config": workload_config(S, R),
         "clocks": clocks,
-        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(ms_e2e / args.steps, 4)},
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": int(h2d * R),
+                "d2h_bytes_per_step": int(d2h * R), "ms_per_step": round(ms_e2e / args.steps, 4),
+                "returns": "per-offset pair counts of the four maps and the status word"},
         "gpu_launches": int(launches),
+        "ms_per_build": round(ms_build, 4),
         "roofline": roofline,
         "cpu_baseline": cpu,
         "gms_sweep": sweep,
@@ -477,61 +549,117 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
-def gms_sweep(torch, minuet, cache, d_coords, d_bd, channels=(16, 32, 64, 128, 256), rounds=5):
-    """Gather / grouped GEMM / scatter stage times on the 3^3 stride-1 map of the
-    benchmark batch, fp16 features and weights (fp32 accumulate)."""
+def gms_sweep(torch, minuet, lib, cache, d_coords, d_bd, channels=(16, 32, 64, 128, 256), rounds=5):
+    """Gather / grouped GEMM / scatter on the 3^3 stride-1 map of the given batch, fp16
+    features and weights (fp32 accumulate), per channel width:
+
+    * the three stage kernels behind the reference's timers (cuda_time_gather / _gemm /
+      _scatter), gather and scatter at the fastest tile size among the divisors of C (what
+      the layer autotuner picks), charged with the bytes the kernel must move on THIS map
+      (rows that have a pair) and, beside it, with the fusion-agnostic stage formula;
+    * the whole layer through the two forward paths that 16-bit layers actually take (pair
+      lists, fused implicit GEMM at its best sub-tile count), against the layer's bound.
+    """
     from minuet_b200 import engine
     from minuet_b200.nn import functional as F
     peaks, _ = measured_peaks()
+    hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
     tc = cache.get_target_coordinates(d_coords, d_bd, 1, 1)
     sm, tm, order, sizes = cache.get_kernel_map(d_coords, 1, d_bd, tc[0], tc[1], tc[2], 3, 1)
     h_sizes = engine.host_copy(sizes)
     S = T = d_coords.shape[0]
     O = len(h_sizes)
     E = int(h_sizes.sum())
-    E1, O1 = E - int(h_sizes[-1]), O - 1            # centre offset takes the shortcut
+    E1, O1 = E - int(h_sizes[-1]), O - 1            # the centre offset takes the shortcut
+    centre = 1 << (O - 1)                            # its bit in the row-ordered hit words
+    s_hit = int((engine.hit_bits(sm) & ~centre).ne(0).sum())
+    t_hit = int((engine.hit_bits(tm) & ~centre).ne(0).sum())
+
+    def per_launch(names, fn):
+        got = profile_kernels(lib, fn, rounds)
+        ms = [got[n]["ms"] for n in names if n in got]
+        return sum(ms) if ms else float("nan")
+
+    def frac(value, peak):
+        f = value / peak
+        return {"frac": round(f, 3)} if f <= 1.2 else {
+            "frac": round(f, 3), "suspect": "above 1.2 of the measured peak: the charged bytes "
+                                            "overstate what the kernel moved"}
+
     out = {}
     for c in channels:
         w = torch.randn(O, c, c, device=d_coords.device).half()
         kw = dict(weights=w, source_masks=sm, target_masks=tm, kernel_map_sizes=sizes,
                   allow_shortcut_matmul=True)
-        for fn in (F.cuda_time_gather, F.cuda_time_scatter):
+        divisors = [t for t in range(1, c + 1) if c % t == 0]
+        best = {}
+        for stage, fn, kernel in (("gather", F.cuda_time_gather, "gather_kernel"),
+                                  ("scatter", F.cuda_time_scatter, "scatter_kernel")):
             fn(tile_size=1, **kw)
+            for t in divisors:
+                ms = per_launch([kernel], lambda: fn(tile_size=t, **kw))
+                if stage not in best or ms < best[stage][1]:
+                    best[stage] = (t, ms)
         F.cuda_time_gemm(**kw)
-        # kernel times from the library's own event pairs around each launch (the
-        # stage timers above also count the host's launch latency)
-        lib = engine.lib()
-        lib.mn_profile_enable(1)
-        for _ in range(rounds):
-            F.cuda_time_gather(tile_size=1, **kw)
-            F.cuda_time_gemm(**kw)
-            F.cuda_time_scatter(tile_size=1, **kw)
-        torch.cuda.synchronize()
-        lib.mn_profile_enable(0)
-        buf = ctypes.create_string_buffer(1 << 14)
-        lib.mn_profile_report(buf, len(buf))
-        per = {}
-        for row in buf.value.decode().splitlines():
-            name, count, kms = row.rsplit(" ", 2)
-            per[name] = float(kms) / int(count)
-        tg = per.get("gather_kernel", float("nan"))
-        ts = per.get("scatter_kernel", float("nan"))
-        tm_ = per.get("gemm_tc_kernel", per.get("gemm_simt_kernel", float("nan")))
-        gather_bytes = S * c * 2 + 4 * O1 * S + E1 * c * 2
-        scatter_bytes = E1 * c * 2 + 4 * O1 * T + 2 * T * c * 2
+        gemm_ms = per_launch(["gemm_tc_kernel", "gemm_simt_kernel"], lambda: F.cuda_time_gemm(**kw))
+        # bytes the stage must move on this map / the stage formula over all S (or T) rows
+        g_honest = s_hit * c * 2 + E1 * c * 2 + 4 * E1
+        g_survey = S * c * 2 + 4 * O1 * S + E1 * c * 2
+        s_honest = E1 * c * 2 + T * c * 2 + 4 * E1
+        s_survey = E1 * c * 2 + 4 * O1 * T + T * c * 2
         flops = 2.0 * E * c * c
         gemm_bytes = E * 2 * c * 2 + O * c * c * 2
-        out[str(c)] = {
-            "gather_ms": round(tg, 4), "gather_gbs": round(gather_bytes / tg / 1e6, 1),
-            "gather_frac_hbm": round(gather_bytes / tg / 1e6 / peaks["hbm_gbs"], 3),
-            "gemm_ms": round(tm_, 4), "gemm_tflops": round(flops / tm_ / 1e9, 2),
-            "gemm_frac_tensor": round(flops / tm_ / 1e9 / peaks["bf16_tflops"], 4),
-            "gemm_gbs": round(gemm_bytes / tm_ / 1e6, 1),
-            "scatter_ms": round(ts, 4), "scatter_gbs": round(scatter_bytes / ts / 1e6, 1),
-            "scatter_frac_hbm": round(scatter_bytes / ts / 1e6 / peaks["hbm_gbs"], 3),
+        tg, ts = best["gather"][1], best["scatter"][1]
+        row = {
+            "gather": {"tile_size": best["gather"][0], "ms": round(tg, 4),
+                       "bytes_on_this_map": g_honest, "gbs": round(g_honest / tg / 1e6, 1),
+                       **frac(g_honest / tg / 1e6, hbm),
+                       "bytes_stage_formula": g_survey,
+                       "gbs_stage_formula": round(g_survey / tg / 1e6, 1)},
+            "scatter": {"tile_size": best["scatter"][0], "ms": round(ts, 4),
+                        "bytes_on_this_map": s_honest, "gbs": round(s_honest / ts / 1e6, 1),
+                        **frac(s_honest / ts / 1e6, hbm),
+                        "bytes_stage_formula": s_survey,
+                        "gbs_stage_formula": round(s_survey / ts / 1e6, 1)},
+            "gemm": {"ms": round(gemm_ms, 4), "tflops": round(flops / gemm_ms / 1e9, 2),
+                     "frac_tensor": round(flops / gemm_ms / 1e9 / tensor, 4),
+                     "gbs": round(gemm_bytes / gemm_ms / 1e6, 1),
+                     "frac_hbm": round(gemm_bytes / gemm_ms / 1e6 / hbm, 3),
+                     "bound": "hbm" if c <= 32 else "tensor"},
         }
+        # whole layer, the paths 16-bit layers take
+        layer = {}
+        fw = dict(weights=w, source_masks=sm, target_masks=tm, kernel_map_order=order,
+                  kernel_map_sizes=sizes, allow_shortcut_matmul=True)
+        code = engine.dtype_code(w.dtype)
+        if lib.mn_pairs_supported(O, c, c, code):
+            F.time_forward(algorithm="explicit", **fw)
+            layer["pairs_ms"] = round(float(np.mean(
+                [F.time_forward(algorithm="explicit", **fw) for _ in range(rounds)])), 4)
+            got = profile_kernels(lib, lambda: F.time_forward(algorithm="explicit", **fw), rounds)
+            layer["pairs_kernels_ms"] = {k: round(v["ms"], 4) for k, v in got.items()}
+        if lib.mn_implicit_supported(O, c, c, code):
+            n_pad = -(-c // 16) * 16
+            for sub in (1, 2, 3, 4):
+                if sub * n_pad > 512:
+                    break
+                F.time_forward(algorithm="implicit", sub_tiles=sub, **fw)
+                ms = float(np.mean([F.time_forward(algorithm="implicit", sub_tiles=sub, **fw)
+                                    for _ in range(rounds)]))
+                if "implicit_ms" not in layer or ms < layer["implicit_ms"]:
+                    layer["implicit_ms"], layer["implicit_sub_tiles"] = round(ms, 4), sub
+        if layer:
+            best_ms = min(v for k, v in layer.items() if k in ("pairs_ms", "implicit_ms"))
+            bound_bytes = S * c * 2 + T * c * 2 + O * c * c * 2 + 4 * O * (S + T)
+            bound_ms = max(bound_bytes / hbm / 1e6, flops / tensor / 1e9)
+            layer.update(best_ms=best_ms, tflops=round(flops / best_ms / 1e9, 2),
+                         frac_tensor=round(flops / best_ms / 1e9 / tensor, 4),
+                         bound_ms=round(bound_ms, 4), frac_of_bound=round(bound_ms / best_ms, 3))
+        row["layer"] = layer
+        out[str(c)] = row
     return {"map": "3^3 stride 1 on the benchmark batch", "S": int(S), "pairs": E,
-            "pairs_without_centre": E1, "dtype": "f16", "channels": out}
+            "pairs_without_centre": E1, "source_rows_with_a_pair": s_hit,
+            "target_rows_with_a_pair": t_hit, "dtype": "f16", "channels": out}
 
 
 UNET_CLOUDS = 64          # C4: 64 outdoor clouds in total, sharded over the ranks
@@ -548,13 +676,25 @@ def _make_indoor_cloud(seed):
     return synth.indoor_cloud(seed, 200_000)
 
 
+def layer_bound(entry, hbm_gbs, tensor_tflops, elem=2):
+    """Fusion-agnostic lower bound of one convolution layer: every operand crosses HBM
+    once (features in, features out, weights, one 32-bit word per mask entry) against
+    2 E c_in c_out flops on the tensor pipe.  Returns (bytes, flops, milliseconds)."""
+    S, T, O, E = entry["S"], entry["T"], entry["O"], entry["E"]
+    ci, co = entry["c_in"], entry["c_out"]
+    nbytes = S * ci * elem + T * co * elem + O * ci * co * elem + (4 * O * (S + T) if O > 1 else 0)
+    flops = 2.0 * E * ci * co
+    return nbytes, flops, max(nbytes / hbm_gbs / 1e6, flops / tensor_tflops / 1e9)
+
+
 def unet_section(args, torch, dist, dev, rank, world, lib):
     """Sparse UNet (fp16, random weights, eval-mode BatchNorm) on 64 outdoor clouds
-    sharded by cloud over the ranks; the logits are gathered with NCCL.  Strong
-    scaling: the 64 clouds are the whole job at every N."""
+    sharded by cloud over the ranks; the per-voxel outputs are gathered on rank 0 with
+    point-to-point NCCL messages.  Strong scaling: the 64 clouds are the whole job at
+    every N."""
     import concurrent.futures
     import minuet_b200 as minuet
-    from minuet_b200 import sharding
+    from minuet_b200 import engine, sharding
     from minuet_b200.unet import SparseUNet
 
     indoor = args.unet_config == "c3"       # C3: 8 indoor scenes x 200k voxels, RGB features
@@ -580,6 +720,10 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
     h_bd = torch.from_numpy(bd).pin_memory()
     h_feats = torch.from_numpy(feats).half().pin_memory()
     d_coords, d_bd, d_feats = h_coords.to(dev), h_bd.to(dev), h_feats.to(dev)
+    # the generators make clouds of exactly per_cloud voxels, so every rank knows every
+    # rank's row count from the shard plan and the gather needs no count exchange
+    assert len(coords) == per_cloud * len(mine)
+    rows_per_rank = [per_cloud * len(s) for s in shards]
 
     torch.manual_seed(0)
     net = SparseUNet(feats.shape[1], num_classes=20).to(dev).half().eval().fuse()
@@ -591,11 +735,13 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
         with torch.no_grad():
             return net(minuet.SparseTensor(f, c, batch_dims=b))
 
-    def forward(c, b, f):
-        out = local_forward(c, b, f)
+    def forward(c, b, f, labels=False):
+        out = local_forward(c, b, f).F
+        if labels:          # class labels: one byte per voxel instead of 20 fp16 logits
+            out = out.argmax(dim=1, keepdim=True).to(torch.uint8)
         if dist is not None:
-            return sharding.gather_rows(out.F, dst=0)   # collective: every rank calls it
-        return [out.F]
+            return sharding.gather_rows(out, dst=0, counts=rows_per_rank)   # every rank calls it
+        return [out]
 
     def timed(fn, steps):
         total = 0.0
@@ -611,9 +757,25 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
             total += a.elapsed_time(b)
         return total
 
+    # per-layer tuning on this rank's shard (pair lists against the fused kernel, sub-tiles)
+    tuned = None
+    if not args.no_autotune:
+        rounds = minuet.nn.SparseConv.__NUM_TUNING_ROUNDS__
+        minuet.nn.SparseConv.__NUM_TUNING_ROUNDS__ = 3
+        try:
+            minuet.autotune(net, cache, [minuet.SparseTensor(d_feats, d_coords, batch_dims=d_bd)])
+        finally:
+            minuet.nn.SparseConv.__NUM_TUNING_ROUNDS__ = rounds
+        tuned = {}
+        for m in net.modules():
+            if isinstance(m, minuet.nn.SparseConv) and not m.is_trivial:
+                key = f"{m.tunable_config['algorithm']}/{m.tunable_config['sub_tiles']}"
+                tuned[key] = tuned.get(key, 0) + 1
+
     steps, warm = args.unet_steps, 3
     for _ in range(warm):
         forward(d_coords, d_bd, d_feats)
+    engine.check_status(dev)
     launches0 = lib.mn_launch_count()
     ms = timed(lambda: forward(d_coords, d_bd, d_feats), steps)
     launches = lib.mn_launch_count() - launches0
@@ -622,35 +784,79 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
         c = h_coords.to(dev, non_blocking=True)
         b = h_bd.to(dev, non_blocking=True)
         f = h_feats.to(dev, non_blocking=True)
-        parts = forward(c, b, f)
+        parts = forward(c, b, f, labels=True)
         if parts is not None:      # rank 0: per-voxel class labels go back to the host
-            return [p.argmax(dim=1).to(torch.uint8).cpu() for p in parts]
+            return [p.cpu() for p in parts]
         return None
 
     e2e()
     ms_e2e = timed(e2e, steps)
+    engine.check_status(dev)
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = (float(v) for v in t.cpu())
 
-    kernels = None
+    kernels = roofline = None
     if rank == 0:
-        lib.mn_profile_enable(1)
-        local_forward(d_coords, d_bd, d_feats)      # rank-local: no collective in here
+        got = profile_kernels(lib, lambda: local_forward(d_coords, d_bd, d_feats), 1)   # rank-local
+        kernels = {k: {"launches": int(v["launches"]), "ms": round(v["ms"], 4)}
+                   for k, v in sorted(got.items(), key=lambda kv: -kv[1]["ms"])}
+        # per-layer shapes and device times of one more rank-local forward
+        peaks, peak_kind = measured_peaks()
+        hbm, tensor = peaks["hbm_gbs"], peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+        engine.LAYER_LOG = []
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        local_forward(d_coords, d_bd, d_feats)
+        b.record()
         torch.cuda.synchronize()
-        lib.mn_profile_enable(0)
-        buf = ctypes.create_string_buffer(1 << 16)
-        lib.mn_profile_report(buf, len(buf))
-        kernels = {}
-        for row in buf.value.decode().splitlines():
-            name, count, kms = row.rsplit(" ", 2)
-            kernels[name] = {"launches": int(count), "ms": round(float(kms), 4)}
-        kernels = dict(sorted(kernels.items(), key=lambda kv: -kv[1]["ms"]))
+        log, engine.LAYER_LOG = engine.LAYER_LOG, None
+        local_ms = a.elapsed_time(b)
+        layers, sum_bytes, sum_flops, sum_bound, sum_meas = [], 0, 0.0, 0.0, 0.0
+        for e in log:
+            nbytes, flops, bound = layer_bound(e, hbm, tensor)
+            meas = e["events"][0].elapsed_time(e["events"][1])
+            sum_bytes += nbytes
+            sum_flops += flops
+            sum_bound += bound
+            sum_meas += meas
+            layers.append([e["S"], e["T"], e["O"], e["E"], e["c_in"], e["c_out"], e["algorithm"],
+                           round(bound, 4), round(meas, 4)])
+        # the nine kernel maps of the forward (one per stride level and kernel size)
+        map_bytes = 0
+        seen = set()
+        for e in log:
+            key = (min(e["S"], e["T"]), max(e["S"], e["T"]), e["O"])
+            if e["O"] > 1 and key not in seen:
+                seen.add(key)
+                map_bytes += 12 * (e["S"] + e["T"]) + 4 * e["O"] * (e["S"] + e["T"])
+        map_bound = map_bytes / hbm / 1e6
+        roofline = {
+            "bound": "per layer max(bytes / HBM, flops / tensor), summed; kernel maps at HBM",
+            "peak_hbm_gbs": hbm, "peak_tensor_tflops": tensor,
+            "peak_source": peak_kind + (" (sustained bf16 figure: the layers run inside a long step)"
+                                        if "bf16_tflops_sustained" in peaks else ""),
+            "layer_columns": ["S", "T", "O", "E", "c_in", "c_out", "algorithm", "bound_ms",
+                              "measured_ms"],
+            "layers": layers,
+            "sum_layer_bytes": int(sum_bytes), "sum_layer_flops": sum_flops,
+            "sum_layer_bound_ms": round(sum_bound, 3), "sum_layer_measured_ms": round(sum_meas, 3),
+            "kernel_maps": len(seen), "kernel_map_bytes": int(map_bytes),
+            "kernel_map_bound_ms": round(map_bound, 3),
+            "forward_ms_rank0_shard": round(local_ms, 3),
+            "frac": round((sum_bound + map_bound) / local_ms, 4),
+            "achieved_tflops": round(sum_flops / local_ms / 1e9, 2),
+        }
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = unet_cpu_baseline(torch, feats.shape[1], clouds[0], feats[:len(clouds[0])])
     if dist is not None:
         dist.barrier()
     if rank != 0:
         return None
+    out_bytes = sum(rows_per_rank)
     return {
         "metric": "sparse-UNet fp16 clouds/sec", "value": round(n_clouds * steps / (ms * 1e-3), 2),
         "unit": "clouds/s", "scaling": "strong", "ms_per_step": round(ms / steps, 3),
@@ -659,36 +865,73 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
                                 if indoor else
                                 "C4: UNet (stem 32, encoder 32/64/128/256, decoder mirror, 20 "
                                 "classes) on 64 outdoor clouds x 120k voxels, 4-channel fp16 "
-                                "features") + ", clouds sharded over the GPUs, NCCL gather of "
-                               "the logits",
+                                "features") + ", clouds sharded over the GPUs; rank 0 receives "
+                               "every rank's fp16 logits (device-resident leg) or uint8 class "
+                               "labels (end-to-end leg) as point-to-point NCCL messages",
                    "clouds_total": n_clouds, "clouds_on_rank0": len(mine),
-                   "voxels_on_rank0": int(len(coords))},
+                   "voxels_on_rank0": int(len(coords)), "autotuned_layers": tuned},
         "e2e": {"value": round(n_clouds * steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "ms_per_step": round(ms_e2e / steps, 3),
                 "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_bd.numel() * 8 + h_feats.numel() * 2),
-                "d2h_bytes_per_step": int(n_clouds * per_cloud)},
+                "d2h_bytes_per_step": int(out_bytes),
+                "returns": "one uint8 class label per voxel of all clouds, on rank 0's host"},
         "gpu_launches": int(launches),
+        "library_launches_per_forward": int(launches / max(steps, 1)),
+        "blocking_host_reads_per_forward": 4,
+        "roofline": roofline,
+        "cpu_baseline": cpu,
         "library_kernel_ms_rank0_one_step": kernels,
     }
+
+
+def unet_cpu_baseline(torch, in_channels, cloud, feats):
+    """The same network, layer by layer, through the CPU restatement (kernel maps and
+    convolutions in C++/OpenMP with fp64 accumulation, BatchNorm/ReLU/concat in numpy)
+    on ONE cloud of the batch."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    import oracle
+    from oracle.net import OracleNet
+    from minuet_b200.unet import SparseUNet
+    oracle.build()
+    oracle.set_num_threads(cores)
+    torch.manual_seed(0)
+    net = SparseUNet(in_channels, num_classes=20).half().eval()
+    f0 = torch.from_numpy(feats).half().float().numpy()
+    c0 = np.ascontiguousarray(cloud.astype(np.int32))
+    t0 = time.perf_counter()
+    done = 0
+    while done < 1 or time.perf_counter() - t0 < 10.0:
+        OracleNet(oracle, round_to=torch.float16).forward(net, (f0, c0, 1, None))
+        done += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(done / dt, 4), "unit": "clouds/s", "cores": oracle.num_threads(),
+            "kind": "port",
+            "sample": f"{done} forward passes of one {len(c0)}-voxel cloud of the batch "
+                      f"({dt / done:.2f} s each), cold kernel maps every pass"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-unet", action="store_true",
                     help="skip the secondary end-to-end UNet measurement")
     ap.add_argument("--unet-steps", type=int, default=5)
+    ap.add_argument("--no-autotune", action="store_true",
+                    help="UNet layers keep the cost-model choice instead of being timed")
     ap.add_argument("--unet-clouds", type=int, default=UNET_CLOUDS,
                     help="clouds in the UNet job (64 = the benchmark configuration)")
     ap.add_argument("--gms-channels", default="16,32,64,128,256")
     ap.add_argument("--unet-config", default="c4", choices=["c3", "c4"],
                     help="c4: 64 outdoor clouds (default); c3: 8 indoor scenes with RGB features")
-    ap.add_argument("--gms-sweep", action="store_true",
-                    help="also time gather / grouped GEMM / scatter for C in 16..256 (fp16)")
+    ap.add_argument("--no-gms-sweep", action="store_true",
+                    help="skip the gather / grouped GEMM / scatter sweep over C in 16..256 (fp16)")
+    ap.add_argument("--repeats", type=int, default=32,
+                    help="cold builds of the four maps per timed step")
     args = ap.parse_args()
     if args.impl == "reference-cuda":
         reference_cuda_arm(args)

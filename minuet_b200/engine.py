@@ -21,6 +21,18 @@ _DTYPE_CODE = {torch.float32: _lib.MN_F32, torch.float16: _lib.MN_F16,
                torch.bfloat16: _lib.MN_BF16}
 
 
+def event_pair_begin(device):
+    """Two timing events, the first recorded now on the current stream (per-layer
+    times for LAYER_LOG)."""
+    pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    pair[0].record(torch.cuda.current_stream(device))
+    return pair
+
+
+def event_pair_end(pair, device):
+    pair[1].record(torch.cuda.current_stream(device))
+
+
 def lib():
     return _lib.load()
 

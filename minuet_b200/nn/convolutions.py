@@ -263,7 +263,11 @@ class SparseConv(Module):
     matrix product and needs no kernel map cache.
     """
 
-    __AVAILABLE_THRESHOLD__ = [-1, *list(np.linspace(0, 2, num=50)), None]
+    # Bucket thresholds only decide how the reference pads its cuBLAS batches; here the
+    # grouped GEMM takes every offset at its own size, so the key stays in the config
+    # (files written by the reference load) and only these few values are ever timed.
+    __AVAILABLE_THRESHOLD__ = [-1, 0.0, 0.5, None]
+    __AVAILABLE_SUB_TILES__ = [1, 2, 3, 4]
     __NUM_TUNING_ROUNDS__ = 10
 
     def __init__(self, ndim: int, in_channels: int, out_channels: int, kernel_size,
@@ -286,10 +290,16 @@ class SparseConv(Module):
             self.register_parameter('bias', None)
         self.reset_parameters()
         self._kernel_map_cache: Optional[KernelMapCache] = None
+        # threshold / tile sizes: the reference's keys (minuet/nn/convolutions.py:277-281);
+        # algorithm ("auto", "explicit", "implicit") and sub_tiles (row sub-tiles per tile
+        # of the fused kernel, 0 = automatic) are the knobs that matter on this library
         self._tunable_config = {'threshold': -1,
                                 'gather_tile_size': min(in_channels, 1),
-                                'scatter_tile_size': min(out_channels, 1)}
+                                'scatter_tile_size': min(out_channels, 1),
+                                'algorithm': 'auto',
+                                'sub_tiles': 0}
         self._tuning_data = None
+        self._tuning_maps = None
 
     def reset_parameters(self):
         """Uniform init in ``+-1/sqrt(fan * K^D)`` with ``fan`` the input channels
@@ -353,14 +363,35 @@ class SparseConv(Module):
                 best = mean
                 self._tunable_config[config_key] = value
 
+    def _time_algorithm(self, algorithm: str, sub_tiles: int) -> float:
+        """Mean milliseconds of a whole forward pass over the recorded maps (after one
+        untimed pass, which builds whatever the algorithm derives from the map once:
+        pair lists, neighbour tables)."""
+        kw = dict(allow_shortcut_matmul=self._allow_shortcut_matmul, algorithm=algorithm,
+                  sub_tiles=sub_tiles)
+        for sm, tm, order, sz in self._tuning_maps:
+            F.time_forward(self.kernel, sm, tm, order, sz, **kw)
+        times = [F.time_forward(self.kernel, sm, tm, order, sz,
+                                allow_shortcut_matmul=self._allow_shortcut_matmul,
+                                algorithm=algorithm, sub_tiles=sub_tiles,
+                                gather_tile_size=self._tunable_config['gather_tile_size'],
+                                scatter_tile_size=self._tunable_config['scatter_tile_size'],
+                                threshold=self._tunable_config['threshold'])
+                 for _ in range(self.__NUM_TUNING_ROUNDS__)
+                 for sm, tm, order, sz in self._tuning_maps]
+        return float(np.mean(times))
+
     @contextlib.contextmanager
     def autotune(self, free_buffers: bool = True):
         """Record the kernel maps this layer sees inside the ``with`` block, then
-        pick ``threshold``, ``gather_tile_size`` and ``scatter_tile_size`` by
-        timing each candidate for ``__NUM_TUNING_ROUNDS__`` rounds
-        (minuet/nn/convolutions.py:337-444)."""
+        time the candidates for ``__NUM_TUNING_ROUNDS__`` rounds each and keep the
+        fastest (minuet/nn/convolutions.py:337-444): for fp32 layers (gather - grouped
+        GEMM - scatter) ``threshold``, ``gather_tile_size`` and ``scatter_tile_size`` as
+        the reference does; for fp16/bf16 layers ``algorithm`` (pair lists against the
+        fused kernel) and the fused kernel's ``sub_tiles``."""
         try:
             self._tuning_data = list()
+            self._tuning_maps = list()
             if free_buffers:
                 F.cuda_free_buffers()
             yield
@@ -368,18 +399,37 @@ class SparseConv(Module):
                 F.cuda_free_buffers()
             if self.is_trivial or not self._tuning_data:
                 return
-            self._sweep(F.cuda_time_gemm, self.__AVAILABLE_THRESHOLD__, 'threshold', 'threshold',
-                        stop_on_error=True)
-            threshold = self._tunable_config['threshold']
-            divisors = lambda c: [t for t in range(1, c + 1) if c % t == 0]
-            self._sweep(F.cuda_time_gather, divisors(self.in_channels), 'tile_size',
-                        'gather_tile_size', threshold=threshold)
-            self._sweep(F.cuda_time_scatter, divisors(self.out_channels), 'tile_size',
-                        'scatter_tile_size', threshold=threshold)
+            lib = engine.lib()
+            code = engine.dtype_code(self.kernel.dtype)
+            volume = self.kernel.shape[0]
+            pairs_ok = self.kernel.dtype != torch.float32 and bool(lib.mn_pairs_supported(
+                volume, self.in_channels, self.out_channels, code))
+            if not pairs_ok:
+                self._sweep(F.cuda_time_gemm, self.__AVAILABLE_THRESHOLD__, 'threshold',
+                            'threshold', stop_on_error=True)
+                threshold = self._tunable_config['threshold']
+                divisors = lambda c: [t for t in range(1, c + 1) if c % t == 0]
+                self._sweep(F.cuda_time_gather, divisors(self.in_channels), 'tile_size',
+                            'gather_tile_size', threshold=threshold)
+                self._sweep(F.cuda_time_scatter, divisors(self.out_channels), 'tile_size',
+                            'scatter_tile_size', threshold=threshold)
+            if lib.mn_implicit_supported(volume, self.in_channels, self.out_channels, code):
+                n_pad = -(-self.out_channels // 16) * 16
+                best, choice = self._time_algorithm('explicit', 0), ('explicit', 0)
+                for sub in self.__AVAILABLE_SUB_TILES__:
+                    if sub * n_pad > 512:
+                        break
+                    ms = self._time_algorithm('implicit', sub)
+                    if ms < best:
+                        best, choice = ms, ('implicit', sub)
+                self._tunable_config['algorithm'], self._tunable_config['sub_tiles'] = choice
+            else:
+                self._tunable_config['algorithm'] = 'explicit'
             if free_buffers:
                 F.cuda_free_buffers()
         finally:
             self._tuning_data = None
+            self._tuning_maps = None
 
     # -- forward ------------------------------------------------------------------
     def _lookup(self, inputs: SparseTensor):
@@ -397,6 +447,7 @@ class SparseConv(Module):
             kernel_dilation=self.dilation, transposed=self.transposed)
         if self._tuning_data is not None:
             self._tuning_data.append((source_masks, target_masks, sizes))
+            self._tuning_maps.append((source_masks, target_masks, order, sizes))
         return coordinates, stride, batch_dims, source_masks, target_masks, order, sizes
 
     def forward(self, inputs: SparseTensor) -> SparseTensor:
@@ -415,7 +466,9 @@ class SparseConv(Module):
                 gather_tile_size=self._tunable_config["gather_tile_size"],
                 scatter_tile_size=self._tunable_config["scatter_tile_size"],
                 allow_shortcut_matmul=self._allow_shortcut_matmul,
-                threshold=self._tunable_config["threshold"])
+                threshold=self._tunable_config["threshold"],
+                algorithm=self._tunable_config.get("algorithm"),
+                sub_tiles=self._tunable_config.get("sub_tiles"))
         if self.bias is not None:
             out += self.bias
         return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
@@ -445,7 +498,8 @@ class SparseConv(Module):
             scatter_tile_size=self._tunable_config["scatter_tile_size"],
             allow_shortcut_matmul=self._allow_shortcut_matmul,
             threshold=self._tunable_config["threshold"], scale=scale, shift=shift,
-            residual=residual, relu=relu)
+            residual=residual, relu=relu, algorithm=self._tunable_config.get("algorithm"),
+            sub_tiles=self._tunable_config.get("sub_tiles"))
         return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
 
 

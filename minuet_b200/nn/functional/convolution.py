@@ -2,7 +2,7 @@
 (mirror of minuet/nn/functional/convolution.py)."""
 __all__ = ['cuda_time_gather', 'cuda_time_scatter', 'sparse_convolution_forward',
            'sparse_convolution_forward_fused', 'apply_epilogue', 'cuda_time_gemm',
-           'set_gemm_parallel_level', 'dense_forward']
+           'set_gemm_parallel_level', 'dense_forward', 'time_forward', 'estimate_ms']
 
 import math
 from typing import Optional
@@ -13,13 +13,15 @@ import torch
 from minuet_b200 import _lib, engine
 
 GEMM_PARALLEL_LEVEL = 4
-# Which forward algorithm fp16/bf16 layers use: "explicit" = gather - grouped GEMM -
-# scatter, "implicit" = the fused output-stationary kernel, "auto" = time both the
-# first time a layer shape / map density is seen and keep the faster one
+# Which forward algorithm fp16/bf16 layers use when the call does not say:
+# "explicit" = pair lists (or gather - grouped GEMM - scatter where pair lists do not
+# apply), "implicit" = the fused output-stationary kernel, "auto" = a cost estimate
+# from the map's pair and tile counts (no timing ever runs inside a forward pass; the
+# layer autotuner times both and passes its choice with every call)
 ALGORITHM = "auto"
-# 128-row sub-tiles per CTA tile of the fused kernel (0 = chosen by the library)
+# 128-row sub-tiles per CTA tile of the fused kernel when the call does not say
+# (0 = chosen by the library)
 IMPLICIT_SUB_TILES = 0
-_algorithm_choice = {}
 
 
 def set_gemm_parallel_level(level: int):
@@ -75,7 +77,9 @@ def sparse_convolution_forward(sources: torch.Tensor,
                                scatter_tile_size: int,
                                allow_shortcut_matmul: bool = False,
                                parallel: Optional[int] = None,
-                               threshold: Optional[float] = 0) -> torch.Tensor:
+                               threshold: Optional[float] = 0,
+                               algorithm: Optional[str] = None,
+                               sub_tiles: Optional[int] = None) -> torch.Tensor:
     """``out[t] = sum_k sum_{(s, t) in map[k]} sources[s] @ weights[order[k]]``
     (minuet/nn/functional/convolution.py:110-155).
 
@@ -84,8 +88,11 @@ def sparse_convolution_forward(sources: torch.Tensor,
     accepted and do not change the result: the grouped GEMM needs neither side
     streams nor equal-size buckets.  ``*_tile_size`` is the number of channels
     one thread moves per row; 1 (the untuned default) picks 16-byte accesses.
-    fp16/bf16 layers run either gather - grouped GEMM - scatter or the fused
-    implicit-GEMM kernel, whichever ``ALGORITHM`` selects.
+    fp16/bf16 layers run either the pair-list forward or the fused implicit-GEMM
+    kernel: ``algorithm`` ("explicit" / "implicit"; default: the module-level
+    ``ALGORITHM``) and ``sub_tiles`` (row sub-tiles per tile of the fused kernel,
+    0 = automatic) are this library's additions to the reference signature and are
+    what the layer autotuner tunes.
     """
     del parallel
     engine.require_cuda(sources)
@@ -96,7 +103,8 @@ def sparse_convolution_forward(sources: torch.Tensor,
     if sources.shape[0] != S:
         raise RuntimeError(f"sources has {sources.shape[0]} rows but the masks describe {S}")
     return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
-                    scatter_tile_size, allow_shortcut_matmul, threshold)
+                    scatter_tile_size, allow_shortcut_matmul, threshold, algorithm=algorithm,
+                    sub_tiles=sub_tiles)
 
 
 def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tensor,
@@ -110,7 +118,9 @@ def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tenso
                                      scale: Optional[torch.Tensor] = None,
                                      shift: Optional[torch.Tensor] = None,
                                      residual: Optional[torch.Tensor] = None,
-                                     relu: bool = False) -> torch.Tensor:
+                                     relu: bool = False,
+                                     algorithm: Optional[str] = None,
+                                     sub_tiles: Optional[int] = None) -> torch.Tensor:
     """Sparse convolution with a fused epilogue (no counterpart in the reference,
     whose models apply BatchNorm, the residual add and ReLU as separate passes
     over the feature matrix):
@@ -134,7 +144,7 @@ def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tenso
         raise RuntimeError("residual must be [N_out, C_out] in the feature dtype")
     return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
                     scatter_tile_size, allow_shortcut_matmul, threshold, _f32(scale), _f32(shift),
-                    res, relu)
+                    res, relu, algorithm=algorithm, sub_tiles=sub_tiles)
 
 
 def apply_epilogue(features: torch.Tensor, scale=None, shift=None, residual=None,
@@ -214,6 +224,11 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
     if features.dtype in (torch.float16, torch.bfloat16) and features.dtype == weight.dtype and \
             lib.mn_dense_supported(c_in, c_out, engine.dtype_code(features.dtype)):
         device = features.device
+        entry = None
+        if engine.LAYER_LOG is not None:
+            entry = {"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in, "c_out": c_out,
+                     "algorithm": "dense", "events": engine.event_pair_begin(device)}
+            engine.LAYER_LOG.append(entry)
         out = torch.empty((rows, c_out), dtype=features.dtype, device=device)
         ws = engine.workspace(lib.mn_dense_workspace_bytes(c_in, c_out), device)
         res = None if residual is None else residual.contiguous()
@@ -222,9 +237,8 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
             engine.ptr(weight), engine.ptr(_f32(scale)), engine.ptr(_f32(shift)), engine.ptr(res),
             int(bool(relu)), engine.ptr(out), engine.ptr(engine.status_word(device)),
             engine.ptr(ws), ws.numel(), engine.stream_ptr(device)), "dense_forward")
-        if engine.LAYER_LOG is not None:
-            engine.LAYER_LOG.append({"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in,
-                                     "c_out": c_out, "algorithm": "dense"})
+        if entry is not None:
+            engine.event_pair_end(entry["events"], device)
         return out
     out = torch.mm(features, weight)
     if scale is not None or shift is not None or residual is not None or relu:
@@ -236,7 +250,7 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
 
 
 def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes_host, out,
-                      scale=None, shift=None, residual=None, relu=False):
+                      scale=None, shift=None, residual=None, relu=False, sub_tiles=None):
     O, S = source_masks.shape
     T = target_masks.shape[1]
     c_in, c_out = weights.shape[1], weights.shape[2]
@@ -248,49 +262,56 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
         S, T, O, c_in, c_out, engine.dtype_code(weights.dtype), engine.ptr(sources),
         engine.ptr(weights), engine.ptr(nbr), engine.ptr(tile_bits), engine.ptr(order),
         engine.ptr(scale), engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
-        float(sizes_host.sum()) / max(T, 1), int(IMPLICIT_SUB_TILES),
+        float(sizes_host.sum()) / max(T, 1),
+        int(IMPLICIT_SUB_TILES if sub_tiles is None else sub_tiles),
         engine.ptr(out), engine.ptr(engine.status_word(device)), engine.ptr(ws), ws.numel(),
         engine.stream_ptr(device)), "sparse_convolution_forward_implicit")
     return out
 
 
-def _time_ms(fn, reps=3):
-    best = float("inf")
-    for _ in range(reps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        b.synchronize()
-        best = min(best, a.elapsed_time(b))
-    return best
+def estimate_ms(algorithm: str, S, T, O, c_in, c_out, pairs, shortcut: bool) -> float:
+    """Rough cost of one 16-bit forward pass, from fits to measured layers of the
+    benchmark network on a B200.  Pair lists move every non-centre pair row three
+    times (16-bit read, fp32 product written and read back) at about 2.7 TB/s; the
+    fused kernel pays about 3.5 ns per (128-row tile, offset, 64-channel block)
+    whether or not the offset has pairs in the tile.  Only the ORDER of the two
+    estimates matters."""
+    if algorithm == "implicit":
+        return 0.05 + 3.5e-6 * math.ceil(T / 128) * O * math.ceil(c_in / 64) * \
+            (0.7 + 0.3 * c_out / 128)
+    rest = pairs - (min(S, T) if shortcut else 0)
+    return 0.05 + (rest * (8.0 * c_out + 2.0 * c_in) + 2.0 * (S * c_in + T * c_out)) / 2.7e9
 
 
-def _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit) -> str:
-    """'explicit' or 'implicit' for this layer shape and map density; with
-    ``ALGORITHM == "auto"`` both are timed once per (offsets, channels, dtype,
-    ~log2 targets, ~log2 pairs per target) and the faster one is kept."""
+def _pick_algorithm(weights, sm, tm, sizes_host, allow_shortcut_matmul, algorithm) -> str:
+    """'explicit' or 'implicit' for this call: the caller's choice when it is
+    supported, else the module-level ``ALGORITHM``, else the cheaper estimate."""
     O, T = tm.shape
+    S = sm.shape[1]
     c_in, c_out = weights.shape[1], weights.shape[2]
-    if ALGORITHM == "explicit" or T == 0 or not engine.lib().mn_implicit_supported(
-            O, c_in, c_out, engine.dtype_code(weights.dtype)):
+    if algorithm in (None, "auto"):
+        algorithm = ALGORITHM
+    if algorithm not in ("auto", "explicit", "implicit"):
+        raise ValueError(f"unknown sparse convolution algorithm {algorithm!r}")
+    code = engine.dtype_code(weights.dtype)
+    if algorithm == "explicit" or T == 0 or not engine.lib().mn_implicit_supported(
+            O, c_in, c_out, code):
         return "explicit"
-    if ALGORITHM == "implicit":
+    if algorithm == "implicit":
         return "implicit"
+    if not engine.lib().mn_pairs_supported(O, c_in, c_out, code) or engine.hit_bits(tm) is None:
+        return "implicit"      # the explicit path would gather and scatter through HBM
     pairs = float(sizes_host.sum())
-    key = (O, c_in, c_out, weights.dtype, round(math.log2(T)),
-           round(2 * math.log2(max(pairs, 1.0) / T)))
-    choice = _algorithm_choice.get(key)
-    if choice is None:
-        run_explicit()
-        run_implicit()
-        choice = "implicit" if _time_ms(run_implicit) < _time_ms(run_explicit) else "explicit"
-        _algorithm_choice[key] = choice
-    return choice
+    shortcut = bool(allow_shortcut_matmul) and O > 0 and int(sizes_host[-1]) == S == T
+    if estimate_ms("implicit", S, T, O, c_in, c_out, pairs, shortcut) < \
+            estimate_ms("explicit", S, T, O, c_in, c_out, pairs, shortcut):
+        return "implicit"
+    return "explicit"
 
 
 def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scatter_tile_size,
-             allow_shortcut_matmul, threshold, scale=None, shift=None, residual=None, relu=False):
+             allow_shortcut_matmul, threshold, scale=None, shift=None, residual=None, relu=False,
+             algorithm=None, sub_tiles=None):
     T = tm.shape[1]
     c_out = weights.shape[2]
     out = torch.empty((T, c_out), dtype=weights.dtype, device=sources.device)
@@ -313,16 +334,40 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
 
     def run_implicit():
         return _implicit_forward(sources, weights, sm, tm, order, sizes_host, out, scale, shift,
-                                 residual, relu)
+                                 residual, relu, sub_tiles)
 
-    algorithm = _pick_algorithm(weights, sm, tm, sizes_host, run_explicit, run_implicit)
-    if engine.LAYER_LOG is not None:
-        engine.LAYER_LOG.append({"S": sm.shape[1], "T": T, "O": sm.shape[0],
-                                 "E": int(sizes_host.sum()), "c_in": weights.shape[1],
-                                 "c_out": c_out, "algorithm": algorithm})
-    if algorithm == "implicit":
-        return run_implicit()
-    return run_explicit()
+    choice = _pick_algorithm(weights, sm, tm, sizes_host, allow_shortcut_matmul, algorithm)
+    log = engine.LAYER_LOG
+    if log is not None:
+        entry = {"S": sm.shape[1], "T": T, "O": sm.shape[0], "E": int(sizes_host.sum()),
+                 "c_in": weights.shape[1], "c_out": c_out, "algorithm": choice,
+                 "events": engine.event_pair_begin(sources.device)}
+        log.append(entry)
+    result = run_implicit() if choice == "implicit" else run_explicit()
+    if log is not None:
+        engine.event_pair_end(entry["events"], sources.device)
+    return result
+
+
+def time_forward(weights, source_masks, target_masks, kernel_map_order, kernel_map_sizes,
+                 allow_shortcut_matmul: bool = False, algorithm: str = "explicit",
+                 sub_tiles: int = 0, gather_tile_size: int = 1, scatter_tile_size: int = 1,
+                 threshold: Optional[float] = -1) -> float:
+    """Milliseconds of one whole forward pass with the given algorithm on buffers whose
+    contents do not matter (what the layer autotuner compares)."""
+    engine.require_cuda(weights, source_masks, target_masks)
+    weights = weights.detach().contiguous()
+    sm, tm, order = _i32(source_masks), _i32(target_masks), _i32(kernel_map_order)
+    S, T, O, c_in, c_out, sizes_host = _prepare(weights, sm, tm, kernel_map_sizes)
+    sources = torch.zeros((S, c_in), dtype=weights.dtype, device=weights.device)
+    stream = torch.cuda.current_stream(weights.device)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record(stream)
+    _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scatter_tile_size,
+             allow_shortcut_matmul, threshold, algorithm=algorithm, sub_tiles=sub_tiles)
+    end.record(stream)
+    end.synchronize()
+    return begin.elapsed_time(end)
 
 
 def _time_stage(stage, weights, source_masks, target_masks, kernel_map_sizes, tile_size,

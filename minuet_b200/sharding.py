@@ -37,32 +37,41 @@ def take_clouds(coords: np.ndarray, batch_dims: np.ndarray, features: Optional[n
     return np.ascontiguousarray(coords[index]), bounds, feats
 
 
-def gather_rows(local: torch.Tensor, dst: int = 0, group=None) -> Optional[List[torch.Tensor]]:
+def gather_rows(local: torch.Tensor, dst: int = 0, group=None,
+                counts: Optional[Sequence[int]] = None) -> Optional[List[torch.Tensor]]:
     """Gather a different number of rows from every rank onto ``dst``.
 
-    Row counts travel with one all_gather; the rows travel as one padded
-    ``[max_rows, C]`` block per rank (all_gather_into_tensor on NCCL, gather on
-    gloo).  Returns the list of per-rank tensors on ``dst`` and None elsewhere.
+    Every other rank sends exactly its rows to ``dst`` (one point-to-point message
+    each, posted as one batch); nothing is padded and nothing travels to the ranks
+    that do not need it.  ``counts`` are the row counts of all ranks when the caller
+    knows them (for example from the shard plan); without them one small all_gather
+    and one host read establish them.  Returns the list of per-rank tensors on
+    ``dst`` (its own entry is ``local`` itself) and None elsewhere.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    count = torch.tensor([local.shape[0]], dtype=torch.int64, device=local.device)
-    counts = torch.empty(world, dtype=torch.int64, device=local.device)
-    dist.all_gather_into_tensor(counts, count, group=group)
-    counts = counts.cpu().tolist()
-    width = local.shape[1]
-    padded = torch.zeros((max(counts), width), dtype=local.dtype, device=local.device)
-    padded[:local.shape[0]] = local
-    if local.is_cuda:
-        out = torch.empty((world, max(counts), width), dtype=local.dtype, device=local.device)
-        dist.all_gather_into_tensor(out.view(-1, width), padded, group=group)
-        blocks = list(out.unbind(0))
-    else:
-        blocks = [torch.empty_like(padded) for _ in range(world)] if rank == dst else None
-        dist.gather(padded, blocks, dst=dst, group=group)
+    local = local.contiguous()
+    if counts is None:
+        count = torch.tensor([local.shape[0]], dtype=torch.int64, device=local.device)
+        every = torch.empty(world, dtype=torch.int64, device=local.device)
+        dist.all_gather_into_tensor(every, count, group=group)
+        counts = every.cpu().tolist()
+    if int(counts[rank]) != local.shape[0]:
+        raise ValueError(f"rank {rank} holds {local.shape[0]} rows, the plan says {counts[rank]}")
     if rank != dst:
+        if local.shape[0] > 0:
+            for work in dist.batch_isend_irecv([dist.P2POp(dist.isend, local, dst, group)]):
+                work.wait()
         return None
-    return [b[:n] for b, n in zip(blocks, counts)]
+    parts = [local if r == dst else
+             torch.empty((int(counts[r]),) + tuple(local.shape[1:]), dtype=local.dtype,
+                         device=local.device) for r in range(world)]
+    ops = [dist.P2POp(dist.irecv, parts[r], r, group) for r in range(world)
+           if r != dst and int(counts[r]) > 0]
+    if ops:
+        for work in dist.batch_isend_irecv(ops):
+            work.wait()
+    return parts
 
 
 def reassemble(per_rank: Sequence[torch.Tensor], shards: Sequence[Sequence[int]],

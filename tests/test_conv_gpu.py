@@ -198,8 +198,26 @@ def test_stage_timers_and_autotune(oracle_lib):
         conv.__class__.__NUM_TUNING_ROUNDS__ = 10
     cfg = conv.tunable_config
     assert 16 % cfg["gather_tile_size"] == 0 and 16 % cfg["scatter_tile_size"] == 0
+    # a 16-bit layer: the tuner decided between pair lists and the fused kernel
+    assert cfg["algorithm"] in ("explicit", "implicit") and 0 <= cfg["sub_tiles"] <= 4
     cache.reset()
     assert_close(conv(inp).F, want, torch.float16)
+    # every tunable value gives the same function
+    for algorithm, sub in (("explicit", 0), ("implicit", 1), ("implicit", 3), ("auto", 0)):
+        conv.tunable_config.update(algorithm=algorithm, sub_tiles=sub)
+        assert_close(conv(inp).F, want, torch.float16)
+    # an fp32 layer tunes the reference's three keys on the gather - GEMM - scatter path
+    conv32, cache32, inp32, _, want32 = run_layer(oracle_lib, src, None, 8, 8, 3, 1, torch.float32)
+    conv32.__class__.__NUM_TUNING_ROUNDS__ = 1
+    try:
+        minuet.autotune(conv32, cache32, inp32)
+    finally:
+        conv32.__class__.__NUM_TUNING_ROUNDS__ = 10
+    cfg = conv32.tunable_config
+    assert 8 % cfg["gather_tile_size"] == 0 and 8 % cfg["scatter_tile_size"] == 0
+    assert cfg["threshold"] in conv32.__AVAILABLE_THRESHOLD__ and cfg["algorithm"] == "explicit"
+    cache32.reset()
+    assert_close(conv32(inp32).F, want32, torch.float32)
 
 
 def test_neighbor_table_matches_kernel_map(oracle_lib):

@@ -139,7 +139,13 @@ def test_module_surface_and_tunable_config(tmp_path):
                                                                     transposed=True))
     conv = net[0]
     assert conv.kernel.shape == (27, 4, 8) and conv.bias is None
-    assert conv.tunable_config == {'threshold': -1, 'gather_tile_size': 1, 'scatter_tile_size': 1}
+    assert conv.tunable_config == {'threshold': -1, 'gather_tile_size': 1, 'scatter_tile_size': 1,
+                                   'algorithm': 'auto', 'sub_tiles': 0}
+    # a configuration file written by the reference (three keys) still loads
+    minuet.load_tunable_config(conv, {'threshold': 0.5, 'gather_tile_size': 2,
+                                      'scatter_tile_size': 4})
+    assert conv.tunable_config['algorithm'] == 'auto' and conv.tunable_config['threshold'] == 0.5
+    conv.tunable_config.update(threshold=-1, gather_tile_size=1, scatter_tile_size=1)
     assert set(conv.state_dict()) == {"kernel"}
     bound = 1 / np.sqrt(4 * 27)
     assert float(conv.kernel.abs().max()) <= bound

@@ -50,7 +50,11 @@ def _worker(rank, world, port, sizes, result_path):
         mine = [torch.arange(starts[c], starts[c + 1], dtype=torch.float32) for c in shards[rank]]
         local = (torch.cat(mine) if mine else torch.zeros(0))[:, None].repeat(1, 3)
         gathered = sharding.gather_rows(local, dst=0)
+        # row counts known from the shard plan: same result, no count exchange
+        planned = [sum(sizes[c] for c in shard) for shard in shards]
+        again = sharding.gather_rows(local, dst=0, counts=planned)
         if rank == 0:
+            assert all(torch.equal(a, b) for a, b in zip(gathered, again))
             full = sharding.reassemble(gathered, shards, sizes)
             torch.save(full, result_path)
         else:
