@@ -89,7 +89,7 @@ typedef struct {
 /* Version of this interface; mn_version() returns the value the library was
  * built with.  A binding should refuse a library whose version differs from the
  * header it was written against: argument lists change between versions. */
-#define MN_ABI_VERSION 9
+#define MN_ABI_VERSION 10
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -313,10 +313,19 @@ mn_status mn_build_neighbor_table(const int32_t *source_masks, const int32_t *ta
 size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out);
 mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
-    const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
-    const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
-    double pairs_per_row, int sub_tiles, void *targets_out, int32_t *status_dev, void *ws,
-    size_t ws_bytes, void *stream);
+    const void *sources, const void *weights, const void *weights_t, const int32_t *nbr,
+    const uint32_t *tile_bits, const int32_t *order, const float *scale, const float *shift,
+    const void *residual, int relu, double pairs_per_row, int sub_tiles, void *targets_out,
+    int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
+
+/* weights_t_out[o, n, k] = weights[o, k, n]: the K-major weight layout the tensor-core
+ * kernels read.  The three 16-bit forward entry points (implicit, pairs, dense) take
+ * it as `weights_t`; with weights_t == NULL they transpose `weights` into their
+ * workspace on every call, which is what a caller whose weights change between calls
+ * wants.  No reference counterpart (the reference permutes its weights on every call,
+ * sparse_convolution.cu:526-553). */
+mn_status mn_transpose_weights(const void *weights, int64_t O, int64_t c_in, int64_t c_out,
+                               mn_dtype dtype, void *weights_t_out, void *stream);
 
 /* ---- Pair-list forward (sparse kernel maps) and dense forward ------------------ */
 /* Same result as mn_sparse_convolution_forward followed by mn_apply_epilogue, for
@@ -341,11 +350,11 @@ size_t mn_pairs_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t S,
                                 int64_t c_in, int64_t c_out, int allow_shortcut);
 mn_status mn_sparse_convolution_forward_pairs(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
-    const void *sources, const void *weights, const int32_t *target_masks,
-    const uint32_t *target_bits, const int32_t *pair_src, const int32_t *order,
-    const int32_t *sizes_host, int allow_shortcut, const float *scale, const float *shift,
-    const void *residual, int relu, void *targets_out, int32_t *status_dev, void *ws,
-    size_t ws_bytes, void *stream);
+    const void *sources, const void *weights, const void *weights_t,
+    const int32_t *target_masks, const uint32_t *target_bits, const int32_t *pair_src,
+    const int32_t *order, const int32_t *sizes_host, int allow_shortcut, const float *scale,
+    const float *shift, const void *residual, int relu, void *targets_out, int32_t *status_dev,
+    void *ws, size_t ws_bytes, void *stream);
 
 /* out = relu?((features @ weights) * scale + shift + residual) on the tensor cores:
  * the 1x1x1 convolution, for which the reference calls torch.mm
@@ -354,9 +363,10 @@ mn_status mn_sparse_convolution_forward_pairs(
 int mn_dense_supported(int64_t c_in, int64_t c_out, mn_dtype dtype);
 size_t mn_dense_workspace_bytes(int64_t c_in, int64_t c_out);
 mn_status mn_dense_forward(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype dtype,
-                           const void *features, const void *weights, const float *scale,
-                           const float *shift, const void *residual, int relu, void *out,
-                           int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
+                           const void *features, const void *weights, const void *weights_t,
+                           const float *scale, const float *shift, const void *residual, int relu,
+                           void *out, int32_t *status_dev, void *ws, size_t ws_bytes,
+                           void *stream);
 
 /* In place: features[t, c] = relu?(features[t, c] * scale[c] + shift[c] + residual[t, c]);
  * scale / shift (fp32 [channels]) and residual ([rows, channels], feature dtype)

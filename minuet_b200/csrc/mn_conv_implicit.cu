@@ -527,7 +527,8 @@ extern "C" size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c
 
 extern "C" mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
-    const void *sources, const void *weights, const int32_t *nbr, const uint32_t *tile_bits,
+    const void *sources, const void *weights, const void *weights_t_in, const int32_t *nbr,
+    const uint32_t *tile_bits,
     const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
     double pairs_per_row, int sub_hint, void *targets_out, int32_t *status_dev, void *ws_ptr,
     size_t ws_bytes, void *stream) {
@@ -539,7 +540,7 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   }
   MN_CHECK_ARG(S >= 0 && T >= 0 && T < (1ll << 31) && S < (1ll << 31), "implicit forward: bad sizes");
   if (T == 0) return MN_OK;
-  MN_CHECK_ARG(weights != nullptr && nbr != nullptr && tile_bits != nullptr &&
+  MN_CHECK_ARG((weights != nullptr || weights_t_in != nullptr) && nbr != nullptr && tile_bits != nullptr &&
                    targets_out != nullptr && status_dev != nullptr && (S == 0 || sources != nullptr),
                "implicit forward: null pointer");
   MN_CHECK_ARG(((reinterpret_cast<uintptr_t>(sources) | reinterpret_cast<uintptr_t>(targets_out) |
@@ -548,9 +549,13 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == MN_BF16;
   Workspace ws(ws_ptr, ws_bytes);
-  char *weights_t = ws.take<char>(align_up((size_t)O * c_in * c_out * 2, 1024));
-  MN_CHECK_WS(ws);
-  MN_RETURN_IF(launch_transpose_weights(weights, weights_t, (int)O, (int)c_in, (int)c_out, bf16, st));
+  const void *weights_t = weights_t_in;
+  if (weights_t == nullptr) {
+    char *mine = ws.take<char>(align_up((size_t)O * c_in * c_out * 2, 1024));
+    MN_CHECK_WS(ws);
+    MN_RETURN_IF(launch_transpose_weights(weights, mine, (int)O, (int)c_in, (int)c_out, bf16, st));
+    weights_t = mine;
+  }
 
   ImArgs a{};
   a.in = static_cast<const uint8_t *>(sources);

@@ -184,11 +184,11 @@ extern "C" size_t mn_pairs_workspace_bytes(const int32_t *sizes_host, int64_t O,
 
 extern "C" mn_status mn_sparse_convolution_forward_pairs(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
-    const void *sources, const void *weights, const int32_t *target_masks,
-    const uint32_t *target_bits, const int32_t *pair_src, const int32_t *order,
-    const int32_t *sizes_host, int allow_shortcut, const float *scale, const float *shift,
-    const void *residual, int relu, void *targets_out, int32_t *status_dev, void *ws_ptr,
-    size_t ws_bytes, void *stream) {
+    const void *sources, const void *weights, const void *weights_t_in,
+    const int32_t *target_masks, const uint32_t *target_bits, const int32_t *pair_src,
+    const int32_t *order, const int32_t *sizes_host, int allow_shortcut, const float *scale,
+    const float *shift, const void *residual, int relu, void *targets_out, int32_t *status_dev,
+    void *ws_ptr, size_t ws_bytes, void *stream) {
   if (!mn_pairs_supported(O, c_in, c_out, dtype)) {
     set_error("pair-list forward: needs fp16/bf16, at most 32 offsets, channels multiple of 8, "
               "c_out <= 256 (got O=%lld c_in=%lld c_out=%lld dtype=%d)", (long long)O,
@@ -201,18 +201,23 @@ extern "C" mn_status mn_sparse_convolution_forward_pairs(
     MN_CHECK_ARG(sizes_host[p] >= 0 && sizes_host[p] <= std::min(S, T),
                  "pair-list forward: size[%lld] = %d is outside [0, min(S, T)]", (long long)p, sizes_host[p]);
   if (T == 0) return MN_OK;
-  MN_CHECK_ARG(weights != nullptr && target_masks != nullptr && target_bits != nullptr &&
-                   targets_out != nullptr && status_dev != nullptr && (S == 0 || sources != nullptr),
-               "pair-list forward: null pointer");
+  MN_CHECK_ARG((weights != nullptr || weights_t_in != nullptr) && target_masks != nullptr &&
+                   target_bits != nullptr && targets_out != nullptr && status_dev != nullptr &&
+                   (S == 0 || sources != nullptr), "pair-list forward: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == MN_BF16;
   const PairPlan plan = make_pair_plan(sizes_host, O, S, T, allow_shortcut);
   MN_CHECK_ARG(plan.total_rows == 0 || pair_src != nullptr, "pair-list forward: null pair list");
   Workspace ws(ws_ptr, ws_bytes);
   float *products = ws.take<float>((size_t)std::max<int64_t>(plan.total_rows, 1) * c_out);
-  char *weights_t = ws.take<char>(align_up((size_t)O * c_in * c_out * 2, 1024));
+  const void *weights_t = weights_t_in;
+  if (weights_t == nullptr) {
+    char *mine = ws.take<char>(align_up((size_t)O * c_in * c_out * 2, 1024));
+    MN_CHECK_WS(ws);
+    MN_RETURN_IF(launch_transpose_weights(weights, mine, (int)O, (int)c_in, (int)c_out, bf16, st));
+    weights_t = mine;
+  }
   MN_CHECK_WS(ws);
-  MN_RETURN_IF(launch_transpose_weights(weights, weights_t, (int)O, (int)c_in, (int)c_out, bf16, st));
 
   // step 1: products of the mask rows that go through the buffer
   if (plan.total_rows > 0)
@@ -260,7 +265,8 @@ extern "C" size_t mn_dense_workspace_bytes(int64_t c_in, int64_t c_out) {
 }
 
 extern "C" mn_status mn_dense_forward(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype dtype,
-                                      const void *features, const void *weights, const float *scale,
+                                      const void *features, const void *weights,
+                                      const void *weights_t_in, const float *scale,
                                       const float *shift, const void *residual, int relu,
                                       void *out, int32_t *status_dev, void *ws_ptr, size_t ws_bytes,
                                       void *stream) {
@@ -271,17 +277,30 @@ extern "C" mn_status mn_dense_forward(int64_t rows, int64_t c_in, int64_t c_out,
   }
   MN_CHECK_ARG(rows >= 0 && rows < (1ll << 31), "dense forward: bad row count");
   if (rows == 0) return MN_OK;
-  MN_CHECK_ARG(features != nullptr && weights != nullptr && out != nullptr && status_dev != nullptr,
-               "dense forward: null pointer");
+  MN_CHECK_ARG(features != nullptr && (weights != nullptr || weights_t_in != nullptr) &&
+                   out != nullptr && status_dev != nullptr, "dense forward: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == MN_BF16;
   Workspace ws(ws_ptr, ws_bytes);
-  char *weights_t = ws.take<char>(align_up((size_t)c_in * c_out * 2, 1024));
-  MN_CHECK_WS(ws);
-  MN_RETURN_IF(launch_transpose_weights(weights, weights_t, 1, (int)c_in, (int)c_out, bf16, st));
+  const void *weights_t = weights_t_in;
+  if (weights_t == nullptr) {
+    char *mine = ws.take<char>(align_up((size_t)c_in * c_out * 2, 1024));
+    MN_CHECK_WS(ws);
+    MN_RETURN_IF(launch_transpose_weights(weights, mine, 1, (int)c_in, (int)c_out, bf16, st));
+    weights_t = mine;
+  }
   PairEpilogue ep{};
   ep.scale = scale; ep.shift = shift; ep.residual = residual; ep.relu = relu ? 1 : 0;
   ep.T = rows;
   return launch_centre_gemm(rows, c_in, c_out, bf16, features, weights_t, 1, 0, nullptr, ep, out,
                             status_dev, st);
+}
+
+extern "C" mn_status mn_transpose_weights(const void *weights, int64_t O, int64_t c_in, int64_t c_out,
+                                          mn_dtype dtype, void *weights_t_out, void *stream) {
+  MN_CHECK_ARG(dtype == MN_F16 || dtype == MN_BF16, "transpose weights: fp16/bf16 only");
+  MN_CHECK_ARG(O >= 1 && c_in >= 1 && c_out >= 1 && weights != nullptr && weights_t_out != nullptr,
+               "transpose weights: bad arguments");
+  return launch_transpose_weights(weights, weights_t_out, (int)O, (int)c_in, (int)c_out,
+                                  dtype == MN_BF16, static_cast<cudaStream_t>(stream));
 }

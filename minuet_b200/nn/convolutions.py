@@ -300,16 +300,35 @@ class SparseConv(Module):
                                 'sub_tiles': 0}
         self._tuning_data = None
         self._tuning_maps = None
+        self._frozen_kernel_t = None
 
     def reset_parameters(self):
         """Uniform init in ``+-1/sqrt(fan * K^D)`` with ``fan`` the input channels
         (output channels when transposed), minuet/nn/convolutions.py:311-319."""
         fan = self.out_channels if self.transposed else self.in_channels
         bound = 1.0 / math.sqrt(fan * self.kernel.shape[0])
+        self._frozen_kernel_t = None
         with torch.no_grad():
             self.kernel.uniform_(-bound, bound)
             if self.bias is not None:
                 self.bias.uniform_(-bound, bound)
+
+    def freeze_weights(self, frozen: bool = True):
+        """Inference preparation: keep the kernel in the layout the tensor-core kernels
+        read, so that forward passes stop transposing it on every call.  The copy is
+        taken NOW; call again (or ``freeze_weights(False)``) after changing the kernel.
+        Moving or casting the module, ``train()`` and ``reset_parameters`` drop it."""
+        self._frozen_kernel_t = F.transpose_weights(self.kernel) if frozen else None
+        return self
+
+    def train(self, mode: bool = True):
+        if mode:
+            self._frozen_kernel_t = None
+        return super().train(mode)
+
+    def _apply(self, fn, *args, **kwargs):
+        self._frozen_kernel_t = None
+        return super()._apply(fn, *args, **kwargs)
 
     def set_kernel_map_cache(self, cache: KernelMapCache):
         self._kernel_map_cache = cache
@@ -455,7 +474,7 @@ class SparseConv(Module):
         if self.is_trivial:
             bias = None if self.bias is None else self.bias.detach().float()
             out = F.dense_forward(features, self.kernel.view(self.in_channels, self.out_channels),
-                                  shift=bias)
+                                  shift=bias, weights_t=self._frozen_kernel_t)
             return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         else:
             coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
@@ -468,7 +487,8 @@ class SparseConv(Module):
                 allow_shortcut_matmul=self._allow_shortcut_matmul,
                 threshold=self._tunable_config["threshold"],
                 algorithm=self._tunable_config.get("algorithm"),
-                sub_tiles=self._tunable_config.get("sub_tiles"))
+                sub_tiles=self._tunable_config.get("sub_tiles"),
+                weights_t=self._frozen_kernel_t)
         if self.bias is not None:
             out += self.bias
         return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
@@ -487,7 +507,7 @@ class SparseConv(Module):
         features = inputs.F
         if self.is_trivial:
             out = F.dense_forward(features, self.kernel.view(self.in_channels, self.out_channels),
-                                  scale, shift, residual, relu)
+                                  scale, shift, residual, relu, weights_t=self._frozen_kernel_t)
             return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
             self._lookup(inputs)
@@ -499,7 +519,7 @@ class SparseConv(Module):
             allow_shortcut_matmul=self._allow_shortcut_matmul,
             threshold=self._tunable_config["threshold"], scale=scale, shift=shift,
             residual=residual, relu=relu, algorithm=self._tunable_config.get("algorithm"),
-            sub_tiles=self._tunable_config.get("sub_tiles"))
+            sub_tiles=self._tunable_config.get("sub_tiles"), weights_t=self._frozen_kernel_t)
         return SparseTensor(out, coordinates, stride=stride, batch_dims=batch_dims)
 
 

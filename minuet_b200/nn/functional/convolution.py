@@ -2,7 +2,8 @@
 (mirror of minuet/nn/functional/convolution.py)."""
 __all__ = ['cuda_time_gather', 'cuda_time_scatter', 'sparse_convolution_forward',
            'sparse_convolution_forward_fused', 'apply_epilogue', 'cuda_time_gemm',
-           'set_gemm_parallel_level', 'dense_forward', 'time_forward', 'estimate_ms']
+           'set_gemm_parallel_level', 'dense_forward', 'time_forward', 'estimate_ms',
+           'transpose_weights']
 
 import math
 from typing import Optional
@@ -79,7 +80,8 @@ def sparse_convolution_forward(sources: torch.Tensor,
                                parallel: Optional[int] = None,
                                threshold: Optional[float] = 0,
                                algorithm: Optional[str] = None,
-                               sub_tiles: Optional[int] = None) -> torch.Tensor:
+                               sub_tiles: Optional[int] = None,
+                               weights_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t] = sum_k sum_{(s, t) in map[k]} sources[s] @ weights[order[k]]``
     (minuet/nn/functional/convolution.py:110-155).
 
@@ -92,7 +94,9 @@ def sparse_convolution_forward(sources: torch.Tensor,
     kernel: ``algorithm`` ("explicit" / "implicit"; default: the module-level
     ``ALGORITHM``) and ``sub_tiles`` (row sub-tiles per tile of the fused kernel,
     0 = automatic) are this library's additions to the reference signature and are
-    what the layer autotuner tunes.
+    what the layer autotuner tunes; ``weights_t`` is :func:`transpose_weights` of
+    ``weights`` for callers whose weights do not change between calls (without it the
+    16-bit paths transpose the weights on every call).
     """
     del parallel
     engine.require_cuda(sources)
@@ -104,7 +108,7 @@ def sparse_convolution_forward(sources: torch.Tensor,
         raise RuntimeError(f"sources has {sources.shape[0]} rows but the masks describe {S}")
     return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
                     scatter_tile_size, allow_shortcut_matmul, threshold, algorithm=algorithm,
-                    sub_tiles=sub_tiles)
+                    sub_tiles=sub_tiles, weights_t=weights_t)
 
 
 def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tensor,
@@ -120,7 +124,8 @@ def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tenso
                                      residual: Optional[torch.Tensor] = None,
                                      relu: bool = False,
                                      algorithm: Optional[str] = None,
-                                     sub_tiles: Optional[int] = None) -> torch.Tensor:
+                                     sub_tiles: Optional[int] = None,
+                                     weights_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sparse convolution with a fused epilogue (no counterpart in the reference,
     whose models apply BatchNorm, the residual add and ReLU as separate passes
     over the feature matrix):
@@ -144,7 +149,7 @@ def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tenso
         raise RuntimeError("residual must be [N_out, C_out] in the feature dtype")
     return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
                     scatter_tile_size, allow_shortcut_matmul, threshold, _f32(scale), _f32(shift),
-                    res, relu, algorithm=algorithm, sub_tiles=sub_tiles)
+                    res, relu, algorithm=algorithm, sub_tiles=sub_tiles, weights_t=weights_t)
 
 
 def apply_epilogue(features: torch.Tensor, scale=None, shift=None, residual=None,
@@ -183,7 +188,7 @@ def _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_t
 
 
 def _pairs_forward(sources, weights, sm, tm, order, sizes_host, out, allow_shortcut_matmul,
-                   scale=None, shift=None, residual=None, relu=False) -> bool:
+                   scale=None, shift=None, residual=None, relu=False, weights_t=None) -> bool:
     """Pair-list forward (16-bit, kernel maps that carry hit words).  Returns False,
     without touching ``out``, when this layer cannot take it."""
     O, S = sm.shape
@@ -201,7 +206,8 @@ def _pairs_forward(sources, weights, sm, tm, order, sizes_host, out, allow_short
     ws = engine.workspace(lib.mn_pairs_workspace_bytes(engine.np_ptr(sizes_host), O, S, T, c_in,
                                                        c_out, shortcut), device)
     _lib.check(lib.mn_sparse_convolution_forward_pairs(
-        S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights), engine.ptr(tm),
+        S, T, O, c_in, c_out, code, engine.ptr(sources), engine.ptr(weights),
+        engine.ptr(weights_t), engine.ptr(tm),
         engine.ptr(engine.hit_bits(tm)), engine.ptr(pair_src), engine.ptr(order),
         engine.np_ptr(sizes_host), shortcut, engine.ptr(scale), engine.ptr(shift),
         engine.ptr(residual), int(bool(relu)), engine.ptr(out),
@@ -210,7 +216,24 @@ def _pairs_forward(sources, weights, sm, tm, order, sizes_host, out, allow_short
     return True
 
 
-def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=False):
+def transpose_weights(weights: torch.Tensor) -> Optional[torch.Tensor]:
+    """``weights [O, c_in, c_out]`` (or ``[c_in, c_out]``) as ``[O, c_out, c_in]``, the
+    layout the tensor-core kernels read; None for dtypes those kernels do not take."""
+    if weights.dtype not in (torch.float16, torch.bfloat16) or not weights.is_cuda:
+        return None
+    w = weights.detach().contiguous()
+    if w.ndim == 2:
+        w = w.unsqueeze(0)
+    O, c_in, c_out = w.shape
+    out = torch.empty((O, c_out, c_in), dtype=w.dtype, device=w.device)
+    _lib.check(engine.lib().mn_transpose_weights(
+        engine.ptr(w), O, c_in, c_out, engine.dtype_code(w.dtype), engine.ptr(out),
+        engine.stream_ptr(w.device)), "transpose_weights")
+    return out
+
+
+def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=False,
+                  weights_t=None):
     """``relu?((features @ weight) * scale + shift + residual)`` for a 1x1x1
     convolution: the tensor-core GEMM of this library for fp16/bf16 (c_in a multiple
     of 8, c_out even, at most 256), a plain product plus the epilogue pass otherwise
@@ -234,7 +257,8 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
         res = None if residual is None else residual.contiguous()
         _lib.check(lib.mn_dense_forward(
             rows, c_in, c_out, engine.dtype_code(features.dtype), engine.ptr(features),
-            engine.ptr(weight), engine.ptr(_f32(scale)), engine.ptr(_f32(shift)), engine.ptr(res),
+            engine.ptr(weight), engine.ptr(weights_t), engine.ptr(_f32(scale)),
+            engine.ptr(_f32(shift)), engine.ptr(res),
             int(bool(relu)), engine.ptr(out), engine.ptr(engine.status_word(device)),
             engine.ptr(ws), ws.numel(), engine.stream_ptr(device)), "dense_forward")
         if entry is not None:
@@ -250,7 +274,8 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
 
 
 def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes_host, out,
-                      scale=None, shift=None, residual=None, relu=False, sub_tiles=None):
+                      scale=None, shift=None, residual=None, relu=False, sub_tiles=None,
+                      weights_t=None):
     O, S = source_masks.shape
     T = target_masks.shape[1]
     c_in, c_out = weights.shape[1], weights.shape[2]
@@ -260,7 +285,8 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
     ws = engine.workspace(lib.mn_implicit_workspace_bytes(O, c_in, c_out), device)
     _lib.check(lib.mn_sparse_convolution_forward_implicit(
         S, T, O, c_in, c_out, engine.dtype_code(weights.dtype), engine.ptr(sources),
-        engine.ptr(weights), engine.ptr(nbr), engine.ptr(tile_bits), engine.ptr(order),
+        engine.ptr(weights), engine.ptr(weights_t), engine.ptr(nbr), engine.ptr(tile_bits),
+        engine.ptr(order),
         engine.ptr(scale), engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
         float(sizes_host.sum()) / max(T, 1),
         int(IMPLICIT_SUB_TILES if sub_tiles is None else sub_tiles),
@@ -311,7 +337,7 @@ def _pick_algorithm(weights, sm, tm, sizes_host, allow_shortcut_matmul, algorith
 
 def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scatter_tile_size,
              allow_shortcut_matmul, threshold, scale=None, shift=None, residual=None, relu=False,
-             algorithm=None, sub_tiles=None):
+             algorithm=None, sub_tiles=None, weights_t=None):
     T = tm.shape[1]
     c_out = weights.shape[2]
     out = torch.empty((T, c_out), dtype=weights.dtype, device=sources.device)
@@ -321,7 +347,7 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
         # sparse maps with hit words: pair lists, fp32 products, one rounding
         if weights.dtype != torch.float32 and _pairs_forward(
                 sources, weights, sm, tm, order, sizes_host, out, allow_shortcut_matmul, scale,
-                shift, residual, relu):
+                shift, residual, relu, weights_t):
             return out
         _explicit_forward(sources, weights, sm, tm, order, sizes_host, out, gather_tile_size,
                           scatter_tile_size, allow_shortcut_matmul, threshold)
@@ -334,7 +360,7 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
 
     def run_implicit():
         return _implicit_forward(sources, weights, sm, tm, order, sizes_host, out, scale, shift,
-                                 residual, relu, sub_tiles)
+                                 residual, relu, sub_tiles, weights_t)
 
     choice = _pick_algorithm(weights, sm, tm, sizes_host, allow_shortcut_matmul, algorithm)
     log = engine.LAYER_LOG

@@ -95,13 +95,16 @@ class SparseUNet(nn.Module):
         """Fold every eval-mode BatchNorm into a per-channel scale/shift and run it,
         the residual add and the ReLU as convolution epilogues.  Call after
         ``eval()`` and after the final dtype/device of the model is set; ``train()``
-        switches back to the unfused modules."""
+        switches back to the unfused modules.  The convolution kernels are also frozen
+        in the layout the tensor-core kernels read (SparseConv.freeze_weights)."""
         for m in self.modules():
             if isinstance(m, ConvBlock):
                 m.folded = fold_batchnorm(m[1])
             elif isinstance(m, ResidualBlock):
                 proj = None if m.project is None else fold_batchnorm(m.project[1])
                 m.folded = (fold_batchnorm(m.body[1]), fold_batchnorm(m.body[4]), proj)
+            elif isinstance(m, SparseConv) and m.kernel.is_cuda:
+                m.freeze_weights()      # the weights of a fused model no longer change
         return self
 
     def forward(self, x: SparseTensor) -> SparseTensor:

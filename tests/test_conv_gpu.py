@@ -220,6 +220,36 @@ def test_stage_timers_and_autotune(oracle_lib):
     assert_close(conv32(inp32).F, want32, torch.float32)
 
 
+@pytest.mark.parametrize("algorithm", ["explicit", "implicit"])
+def test_frozen_weights_give_the_same_bits(oracle_lib, algorithm):
+    """freeze_weights() only removes the per-call transpose: identical output bits, and a
+    kernel changed afterwards is picked up by freezing again (or by un-freezing)."""
+    rng = np.random.default_rng(21)
+    src, sbd = synth.random_small_batch(rng, 2, 3000, 20)
+    conv, cache, inp, out, want = run_layer(oracle_lib, src, sbd, 32, 64, 3, 1, torch.float16)
+    conv.tunable_config.update(algorithm=algorithm)
+    base = conv(inp).F.clone()
+    conv.freeze_weights()
+    assert conv._frozen_kernel_t.shape == (27, 64, 32)
+    assert torch.equal(conv(inp).F, base)
+    with torch.no_grad():
+        conv.kernel.mul_(2.0)
+    assert torch.equal(conv(inp).F, base)                    # still the frozen copy
+    conv.freeze_weights()
+    doubled = conv(inp).F
+    conv.freeze_weights(False)
+    assert torch.equal(conv(inp).F, doubled)
+    assert_close(doubled, 2.0 * want, torch.float16)
+    conv.freeze_weights()
+    conv.half()                                               # moving / casting drops the copy
+    assert conv._frozen_kernel_t is None
+    # 1x1x1 convolution
+    head = minuet.nn.SparseConv3d(32, 20, 1, dtype=torch.float16, device=DEV)
+    y = head(inp).F.clone()
+    head.freeze_weights()
+    assert torch.equal(head(inp).F, y)
+
+
 def test_neighbor_table_matches_kernel_map(oracle_lib):
     """mn_build_neighbor_table turns masks back into the (mask-row ordered) kernel
     map and marks, per 128-target tile, the offsets that have any pair."""
