@@ -89,7 +89,7 @@ typedef struct {
 /* Version of this interface; mn_version() returns the value the library was
  * built with.  A binding should refuse a library whose version differs from the
  * header it was written against: argument lists change between versions. */
-#define MN_ABI_VERSION 10
+#define MN_ABI_VERSION 12
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -157,6 +157,17 @@ mn_status mn_arg_sort_coordinates(const int32_t *coords, int64_t n, int ndim,
                                   const mn_keyspec *spec, int64_t *index_out,
                                   int32_t *status_dev, void *ws, size_t ws_bytes,
                                   void *stream);
+
+/* The same permutation without a packed key: one stable radix sort per dimension, last
+ * dimension first, then one on the cloud (the reference's fallback for boxes whose
+ * flattened range exceeds 64 bits and its enable_flattening = False path,
+ * arg_sort_coodrinates.cu:333-359, 454-468).  Any int32 coordinates; needs no bounding
+ * box and no key layout.  ctrl: the caller's control block (MN_CTRL_WORDS words);
+ * workspace: mn_map_workspace_bytes(n, n, 1). */
+mn_status mn_arg_sort_coordinates_by_dimension(const int32_t *coords, int64_t n, int ndim,
+                                               const int64_t *batch_dims, int64_t num_clouds,
+                                               int64_t *index_out, int32_t *ctrl, void *ws,
+                                               size_t ws_bytes, void *stream);
 
 /* _C.cuda_unique_coordinates / _C.cuda_multi_unique_coordinates
  * (csrc/minuet/torch/cuda_unique_coordinates.cu:8-81) on SORTED coordinates:
@@ -367,6 +378,25 @@ mn_status mn_dense_forward(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype d
                            const float *scale, const float *shift, const void *residual, int relu,
                            void *out, int32_t *status_dev, void *ws, size_t ws_bytes,
                            void *stream);
+
+/* The same product for every dtype and shape (fp32, channels that are not a multiple
+ * of 8, c_out above 256) on the FFMA grouped-GEMM kernel, followed by the in-place
+ * epilogue pass when one is asked for.  fp32 must not go through TF32 tensor cores:
+ * their 10-bit mantissa breaks the 1e-5 bound.  Needs no workspace. */
+mn_status mn_dense_forward_simt(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype dtype,
+                                const void *features, const void *weights, const float *scale,
+                                const float *shift, const void *residual, int relu, void *out,
+                                void *stream);
+
+/* Per-voxel mean of point features for voxelisation (the reference's
+ * minuet/nn/functional/voxelize.py:10-35 stops at the unique coordinates).
+ * sorted_index [n]: the arg-sort of the floored points; run_ids [n] (the first n entries
+ * of the unique op's index array): voxel of sorted row i, non-decreasing.
+ * means_out[u, :] = mean over the points of voxel u, summed in fp32 in sorted order
+ * (deterministic, no atomics).  features / means_out: [n, channels] / [U, channels]. */
+mn_status mn_voxel_mean(const void *features, int64_t n, int64_t channels, mn_dtype dtype,
+                        const int64_t *sorted_index, const int64_t *run_ids, void *means_out,
+                        void *stream);
 
 /* In place: features[t, c] = relu?(features[t, c] * scale[c] + shift[c] + residual[t, c]);
  * scale / shift (fp32 [channels]) and residual ([rows, channels], feature dtype)

@@ -15,7 +15,7 @@ MN_F32, MN_F16, MN_BF16 = 0, 1, 2
 MN_MAX_NDIM = 4
 MN_MAX_OFFSETS = 128
 MN_CTRL_WORDS = 1024
-ABI_VERSION = 10         # must equal MN_ABI_VERSION of the header the library was built from
+ABI_VERSION = 12         # must equal MN_ABI_VERSION of the header the library was built from
 
 c_i32p = ctypes.c_void_p
 c_ptr = ctypes.c_void_p
@@ -101,6 +101,11 @@ PROTOTYPES = {
                                                     c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr,
                                                     c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_dense_supported": (c_int, [c_i64, c_i64, c_int]),
+    "mn_arg_sort_coordinates_by_dimension": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_i64, c_ptr, c_ptr,
+                                                     c_ptr, c_size, c_ptr]),
+    "mn_voxel_mean": (c_int, [c_ptr, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
+    "mn_dense_forward_simt": (c_int, [c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                                      c_int, c_ptr, c_ptr]),
     "mn_dense_workspace_bytes": (c_size, [c_i64, c_i64]),
     "mn_dense_forward": (c_int, [c_i64, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                  c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),

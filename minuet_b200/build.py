@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libminuet_b200.so")
 SOURCES = ["mn_api.cu", "mn_map_keys.cu", "mn_map_sort.cu", "mn_map_query.cu", "mn_gms.cu",
-           "mn_gemm_tc.cu", "mn_conv_implicit.cu", "mn_conv_pairs.cu"]
+           "mn_gemm_tc.cu", "mn_conv_implicit.cu", "mn_conv_pairs.cu", "mn_voxel.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 

@@ -27,27 +27,37 @@ struct ProfEntry {
   cudaEvent_t begin, end;
 };
 std::atomic<long long> g_launches{0};
-bool g_profiling = false;
+std::atomic<bool> g_profiling{false};
 std::mutex g_prof_mutex;
-std::vector<ProfEntry> g_prof;
+std::vector<ProfEntry> g_prof;   // completed (begin, end) pairs only
 }  // namespace
 
-LaunchScope::LaunchScope(const char *name, cudaStream_t st) : st_(st), slot_(-1) {
+// The scope owns its two events and hands the finished pair to the record under the
+// lock, so a report that clears the record while a launch is in flight on another
+// thread cannot leave a scope pointing at a slot that no longer exists.
+LaunchScope::LaunchScope(const char *name, cudaStream_t st)
+    : st_(st), name_(name), begin_(nullptr), end_(nullptr) {
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  if (!g_profiling) return;
-  std::lock_guard<std::mutex> lock(g_prof_mutex);
-  if ((int)g_prof.size() >= kMaxProfiled) return;
-  ProfEntry e{name, nullptr, nullptr};
-  if (cudaEventCreate(&e.begin) != cudaSuccess || cudaEventCreate(&e.end) != cudaSuccess) return;
-  cudaEventRecord(e.begin, st);
-  slot_ = (int)g_prof.size();
-  g_prof.push_back(e);
+  if (!g_profiling.load(std::memory_order_relaxed)) return;
+  if (cudaEventCreate(&begin_) != cudaSuccess) { begin_ = nullptr; return; }
+  if (cudaEventCreate(&end_) != cudaSuccess) {
+    cudaEventDestroy(begin_);
+    begin_ = end_ = nullptr;
+    return;
+  }
+  cudaEventRecord(begin_, st);
 }
 
 LaunchScope::~LaunchScope() {
-  if (slot_ < 0) return;
+  if (begin_ == nullptr) return;
+  cudaEventRecord(end_, st_);
   std::lock_guard<std::mutex> lock(g_prof_mutex);
-  cudaEventRecord(g_prof[slot_].end, st_);
+  if ((int)g_prof.size() < kMaxProfiled) {
+    g_prof.push_back(ProfEntry{name_, begin_, end_});
+  } else {
+    cudaEventDestroy(begin_);
+    cudaEventDestroy(end_);
+  }
 }
 
 }  // namespace mn
@@ -57,8 +67,7 @@ using namespace mn;
 extern "C" long long mn_launch_count(void) { return g_launches.load(); }
 
 extern "C" void mn_profile_enable(int on) {
-  std::lock_guard<std::mutex> lock(g_prof_mutex);
-  g_profiling = on != 0;
+  g_profiling.store(on != 0);
 }
 
 // Waits for the recorded events and writes one line per distinct kernel name:

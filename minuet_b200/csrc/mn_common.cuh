@@ -64,7 +64,8 @@ struct LaunchScope {
   LaunchScope(const char *name, cudaStream_t st);
   ~LaunchScope();
   cudaStream_t st_;
-  int slot_;
+  const char *name_;
+  cudaEvent_t begin_, end_;   // both null unless this launch is being timed
 };
 
 #define MN_LAUNCH(name, st, ...)                  \

@@ -631,6 +631,53 @@ extern "C" mn_status mn_apply_epilogue(void *features, int64_t rows, int64_t cha
   return MN_ERR_BAD_ARG;
 }
 
+extern "C" mn_status mn_dense_forward_simt(int64_t rows, int64_t c_in, int64_t c_out, mn_dtype dtype,
+                                           const void *features, const void *weights,
+                                           const float *scale, const float *shift,
+                                           const void *residual, int relu, void *out,
+                                           void *stream) {
+  MN_CHECK_ARG(rows >= 0 && rows < (1ll << 31) && c_in >= 1 && c_out >= 1,
+               "dense forward (FFMA): bad shape rows=%lld c_in=%lld c_out=%lld", (long long)rows,
+               (long long)c_in, (long long)c_out);
+  MN_CHECK_ARG(dtype == MN_F32 || dtype == MN_F16 || dtype == MN_BF16,
+               "dense forward (FFMA): unknown dtype %d", (int)dtype);
+  if (rows == 0) return MN_OK;
+  MN_CHECK_ARG(features != nullptr && weights != nullptr && out != nullptr,
+               "dense forward (FFMA): null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GemmTable tab{};
+  tab.num_problems = 1;
+  tab.rows[0] = (int32_t)rows;
+  tab.weight_row[0] = 0;
+  tab.a[0] = features;
+  tab.c[0] = out;
+  tab.direct[0] = 1;
+  tab.tile_rows = kGemmTM;
+  tab.tile_prefix[0] = 0;
+  tab.tile_prefix[1] = (int)div_up(rows, kGemmTM);
+  const dim3 grid(tab.tile_prefix[1], (unsigned)div_up(c_out, kGemmTN));
+  {
+    LaunchScope scope("gemm_simt_kernel", st);
+    switch (dtype) {
+      case MN_F32:
+        gemm_simt_kernel<float><<<grid, 256, 0, st>>>(tab, static_cast<const float *>(weights), nullptr,
+                                                      (int)c_in, (int)c_out);
+        break;
+      case MN_F16:
+        gemm_simt_kernel<__half><<<grid, 256, 0, st>>>(tab, static_cast<const __half *>(weights),
+                                                       nullptr, (int)c_in, (int)c_out);
+        break;
+      default:
+        gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+            tab, static_cast<const __nv_bfloat16 *>(weights), nullptr, (int)c_in, (int)c_out);
+        break;
+    }
+  }
+  MN_CHECK_LAUNCH();
+  if (scale == nullptr && shift == nullptr && residual == nullptr && !relu) return MN_OK;
+  return mn_apply_epilogue(out, rows, c_out, dtype, scale, shift, residual, relu, stream);
+}
+
 extern "C" mn_status mn_plan_buckets(const int32_t *sizes, int64_t O, int has_threshold,
                                      double threshold, int64_t *buckets_out, int64_t *cumsum_out,
                                      int64_t *num_buckets_out) {

@@ -247,6 +247,31 @@ __global__ void widen_index_kernel(const int32_t *__restrict__ in, int64_t n,
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz) out[i] = in[i];
 }
 
+// Keys of one LSD pass of the dimension-by-dimension sort: the coordinate of
+// dimension `dim` (dim >= 0; sign bit flipped, so that unsigned order is signed
+// order) or the cloud (dim < 0) of the row that currently sits at position i.
+__global__ void dimension_keys_kernel(const int32_t *__restrict__ coords, int64_t n, int ndim, int dim,
+                                      const int32_t *__restrict__ perm,
+                                      const int64_t *__restrict__ batch_dims, int num_clouds,
+                                      uint64_t *__restrict__ keys) {
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz) {
+    const int64_t row = perm != nullptr ? perm[i] : i;
+    uint64_t k;
+    if (dim >= 0) {
+      k = (uint64_t)((uint32_t)__ldg(coords + row * ndim + dim) ^ 0x80000000u);
+    } else {
+      int lo = 0, hi = num_clouds;   // last cloud whose first row is <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(batch_dims + mid) <= row) lo = mid; else hi = mid;
+      }
+      k = (uint64_t)lo;
+    }
+    keys[i] = k;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // unique: count -> scan -> compact
 // ---------------------------------------------------------------------------
@@ -658,6 +683,48 @@ extern "C" mn_status mn_arg_sort_coordinates(const int32_t *coords, int64_t n, i
                                  *spec, &source, status_dev, nullptr, ws, &in_tmp, st));
   const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, 256));
   MN_LAUNCH("widen_index_kernel", st, widen_index_kernel<<<blocks, 256, 0, st>>>(in_tmp ? vals_tmp : vals, n, index_out));
+  return MN_OK;
+}
+
+extern "C" mn_status mn_arg_sort_coordinates_by_dimension(
+    const int32_t *coords, int64_t n, int ndim, const int64_t *batch_dims, int64_t num_clouds,
+    int64_t *index_out, int32_t *ctrl, void *ws_ptr, size_t ws_bytes, void *stream) {
+  MN_CHECK_ARG(n >= 0 && n < (1ll << 31) && ndim >= 1 && ndim <= MN_MAX_NDIM,
+               "arg_sort_by_dimension: bad n/ndim");
+  if (n == 0) return MN_OK;
+  MN_CHECK_ARG(coords != nullptr && index_out != nullptr && ctrl != nullptr,
+               "arg_sort_by_dimension: null pointer");
+  if (batch_dims == nullptr) num_clouds = 1;
+  MN_CHECK_ARG(num_clouds >= 1 && num_clouds < (1ll << 31), "arg_sort_by_dimension: bad num_clouds");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace ws(ws_ptr, ws_bytes);
+  uint64_t *keys[2] = {ws.take<uint64_t>(n), ws.take<uint64_t>(n)};
+  int32_t *vals[2] = {ws.take<int32_t>(n), ws.take<int32_t>(n)};
+  MN_CHECK_WS(ws);
+  const size_t fixed = ws.used;
+  const mn_keyspec no_spec{};
+  const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(n, 256));
+  int cur = 0;            // vals[cur] holds the current permutation (after the first pass)
+  bool first = true;
+  // least significant key first: last dimension ... dimension 0, then the cloud
+  for (int dim = ndim - 1; dim >= (num_clouds > 1 ? -1 : 0); dim--) {
+    int bits = 32;
+    if (dim < 0) {
+      bits = 1;
+      while ((1ll << bits) < num_clouds) bits++;
+    }
+    MN_LAUNCH("dimension_keys_kernel", st,
+              dimension_keys_kernel<<<blocks, 256, 0, st>>>(coords, n, ndim, dim,
+                                                            first ? nullptr : vals[cur], batch_dims,
+                                                            (int)num_clouds, keys[cur]));
+    Workspace sub(static_cast<char *>(ws_ptr) + fixed, ws_bytes - fixed);
+    bool in_tmp = false;
+    MN_RETURN_IF(launch_radix_sort(keys[cur], keys[cur ^ 1], vals[cur], vals[cur ^ 1], first, n, 0,
+                                   bits, no_spec, nullptr, ctrl, nullptr, sub, &in_tmp, st));
+    if (in_tmp) cur ^= 1;
+    first = false;
+  }
+  MN_LAUNCH("widen_index_kernel", st, widen_index_kernel<<<blocks, 256, 0, st>>>(vals[cur], n, index_out));
   return MN_OK;
 }
 

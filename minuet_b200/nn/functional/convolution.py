@@ -236,7 +236,7 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
                   weights_t=None):
     """``relu?((features @ weight) * scale + shift + residual)`` for a 1x1x1
     convolution: the tensor-core GEMM of this library for fp16/bf16 (c_in a multiple
-    of 8, c_out even, at most 256), a plain product plus the epilogue pass otherwise
+    of 8, c_out even, at most 256), its FFMA GEMM plus the epilogue pass otherwise
     (fp32 must not go through TF32: its 10-bit mantissa would break the 1e-5 bound)."""
     engine.require_cuda(features)
     features = features.contiguous()
@@ -264,12 +264,25 @@ def dense_forward(features, weight, scale=None, shift=None, residual=None, relu=
         if entry is not None:
             engine.event_pair_end(entry["events"], device)
         return out
-    out = torch.mm(features, weight)
-    if scale is not None or shift is not None or residual is not None or relu:
-        apply_epilogue(out, scale, shift, residual, relu)
+    if features.dtype != weight.dtype or features.dtype not in (torch.float32, torch.float16,
+                                                                  torch.bfloat16):
+        raise RuntimeError(f"features ({features.dtype}) and weight ({weight.dtype}) must share "
+                           "one of float32, float16, bfloat16")
+    # fp32 and the shapes the tensor-core kernel does not take: the FFMA grouped-GEMM kernel
+    device = features.device
+    entry = None
     if engine.LAYER_LOG is not None:
-        engine.LAYER_LOG.append({"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in,
-                                 "c_out": c_out, "algorithm": "mm"})
+        entry = {"S": rows, "T": rows, "O": 1, "E": rows, "c_in": c_in, "c_out": c_out,
+                 "algorithm": "dense-ffma", "events": engine.event_pair_begin(device)}
+        engine.LAYER_LOG.append(entry)
+    out = torch.empty((rows, c_out), dtype=features.dtype, device=device)
+    res = None if residual is None else residual.contiguous()
+    _lib.check(lib.mn_dense_forward_simt(
+        rows, c_in, c_out, engine.dtype_code(features.dtype), engine.ptr(features),
+        engine.ptr(weight), engine.ptr(_f32(scale)), engine.ptr(_f32(shift)), engine.ptr(res),
+        int(bool(relu)), engine.ptr(out), engine.stream_ptr(device)), "dense_forward_simt")
+    if entry is not None:
+        engine.event_pair_end(entry["events"], device)
     return out
 
 

@@ -20,11 +20,12 @@ def arg_sort_coordinates(coordinates: torch.Tensor,
     Same contract as ``minuet.nn.functional.arg_sort_coordinates``
     (minuet/nn/functional/indexing.py:14-56): the result is int32 for a single
     cloud, ``batch_dims.dtype`` for a batch, or ``dtype`` when given.
-    ``enable_flattening`` is accepted for compatibility; coordinates are always
-    packed into one key, and a bounding box that does not fit 63 bits raises
-    NotImplementedError instead of falling back to D sort passes.
+    With ``enable_flattening`` (the default) the coordinates are packed into one
+    64-bit key and sorted once; without it, or when the bounding box needs more than
+    63 key bits, one stable radix sort runs per dimension and one on the cloud, as in
+    the reference's fallback (arg_sort_coodrinates.cu:333-359).  Same permutation
+    either way.
     """
-    del enable_flattening
     engine.require_cuda(coordinates, batch_dims)
     if coordinates.ndim != 2:
         raise RuntimeError(f"coordinates must be a 2-D tensor but found {coordinates.ndim}-D")
@@ -34,8 +35,20 @@ def arg_sort_coordinates(coordinates: torch.Tensor,
     nb = 1 if bd is None else bd.numel() - 1
     out_dtype = dtype or (torch.int32 if batch_dims is None else batch_dims.dtype)
     index = torch.empty(n, dtype=torch.int64, device=coords.device)
-    if n > 0:
-        spec = engine.make_keyspec([coords], ndim, nb, 0)
+    spec = None
+    if n > 0 and enable_flattening:
+        try:
+            spec = engine.make_keyspec([coords], ndim, nb, 0)
+        except NotImplementedError:
+            spec = None        # the box is wider than one key: sort dimension by dimension
+    if n > 0 and spec is None:
+        lib = engine.lib()
+        ws = engine.workspace(lib.mn_map_workspace_bytes(n, n, 1), coords.device)
+        _lib.check(lib.mn_arg_sort_coordinates_by_dimension(
+            engine.ptr(coords), n, ndim, engine.ptr(bd), nb, engine.ptr(index),
+            engine.ptr(engine.control_block(coords.device)), engine.ptr(ws), ws.numel(),
+            engine.stream_ptr(coords.device)), "arg_sort_coordinates_by_dimension")
+    elif n > 0:
         lib = engine.lib()
         ws = engine.workspace(lib.mn_map_workspace_bytes(n, n, 1), coords.device)
         _lib.check(lib.mn_arg_sort_coordinates(

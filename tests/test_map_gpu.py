@@ -55,10 +55,31 @@ def test_arg_sort_empty_and_int64_coords(oracle_lib):
     assert np.array_equal(got, oracle_lib.arg_sort(coords.astype(np.int32)))
 
 
-def test_arg_sort_rejects_unpackable_range():
-    coords = np.array([[-2**30, -2**30, -2**30], [2**30, 2**30, 2**30]], np.int32)
-    with pytest.raises(NotImplementedError):
-        F.arg_sort_coordinates(dev(coords))
+def test_arg_sort_of_a_box_wider_than_one_key(oracle_lib):
+    """A bounding box of 3 x 31 bits does not fit a 63-bit key: the sort then runs
+    dimension by dimension (the reference's fallback) and gives the same permutation."""
+    rng = np.random.default_rng(5)
+    coords = rng.integers(-2**30, 2**30, size=(50_000, 3)).astype(np.int32)
+    coords[:2] = [[-2**30, -2**30, -2**30], [2**30 - 1, 2**30 - 1, 2**30 - 1]]
+    coords[100:2000] = coords[2100:4000]                # duplicates: stability shows
+    got = host(F.arg_sort_coordinates(dev(coords)))
+    assert np.array_equal(got, oracle_lib.arg_sort(coords))
+    bd = np.array([0, 20_000, 20_000, 50_000], np.int64)
+    got = host(F.arg_sort_coordinates(dev(coords), batch_dims=dev(bd)))
+    assert np.array_equal(got, oracle_lib.arg_sort(coords, bd))
+
+
+@pytest.mark.parametrize("ndim", [1, 3, 4])
+def test_arg_sort_without_flattening_is_the_same_permutation(oracle_lib, ndim):
+    rng = np.random.default_rng(6 + ndim)
+    coords = rng.integers(-40, 40, size=(30_011, ndim)).astype(np.int32)
+    bd = np.array([0, 9000, 30_011], np.int64)
+    for b in (None, bd):
+        flat = F.arg_sort_coordinates(dev(coords), batch_dims=None if b is None else dev(b))
+        by_dim = F.arg_sort_coordinates(dev(coords), batch_dims=None if b is None else dev(b),
+                                        enable_flattening=False)
+        assert torch.equal(flat, by_dim)
+        assert np.array_equal(host(by_dim), oracle_lib.arg_sort(coords, b))
 
 
 # ---------------------------------------------------------------------------
@@ -338,6 +359,34 @@ def test_voxelize_with_inverse():
     assert np.array_equal(back, np.floor(pts / np.float32(0.25)).astype(np.int32))
     # every point of cloud g lands in a voxel of cloud g
     assert (host(inv)[:8000] < len(want[0])).all() and (host(inv)[8000:] >= len(want[0])).all()
+
+
+@pytest.mark.parametrize("dtype,channels", [(torch.float32, 5), (torch.float16, 64), (torch.bfloat16, 3),
+                                            (torch.float32, 300)])
+def test_voxelize_averages_point_features(dtype, channels):
+    """voxel_features[u] = mean of the features of the points that fall into voxel u
+    (numpy: float64 sums over the inverse indices)."""
+    rng = np.random.default_rng(23)
+    pts = rng.uniform(-2.0, 2.0, size=(30_000, 3)).astype(np.float32)
+    bd = np.array([0, 11_000, 30_000], np.int64)
+    feats = torch.as_tensor(rng.standard_normal((len(pts), channels)).astype(np.float32)).to(dtype)
+    vox, vbd, inv, vf = F.voxelize(dev(pts), 0.2, batch_dims=dev(bd), return_inverse=True,
+                                   features=feats.to(DEV))
+    assert vf.dtype == dtype and vf.shape == (vox.shape[0], channels)
+    inv_h = host(inv)
+    f64 = feats.double().numpy()
+    sums = np.zeros((vox.shape[0], channels))
+    np.add.at(sums, inv_h, f64)
+    want = sums / np.bincount(inv_h, minlength=vox.shape[0])[:, None]
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dtype]
+    np.testing.assert_allclose(vf.double().cpu().numpy(), want, rtol=tol, atol=tol)
+    # without inverse indices the features still come last; same values
+    vox2, vbd2, vf2 = F.voxelize(dev(pts), 0.2, batch_dims=dev(bd), features=feats.to(DEV))
+    assert torch.equal(vox2, vox) and torch.equal(vf2, vf)
+    # single points per voxel are copied through unchanged
+    lone = np.arange(200, dtype=np.float32)[:, None].repeat(3, 1) * 2.0
+    v3, _, f3 = F.voxelize(dev(lone), 1.0, features=feats[:200].to(DEV))
+    assert torch.equal(f3, feats[:200].to(DEV))
 
 
 def test_int64_coordinates_through_a_layer(oracle_lib):

@@ -75,3 +75,32 @@ def test_static_unique_rejects_more_rows_than_its_scratch_holds():
         st = lib.mn_unique_coordinates_static(None, MAX_ROWS + 1, 3, None, 1, None, _ptr(idx), None)
     assert st == _lib.MN_ERR_BAD_ARG
     assert str(MAX_ROWS) in _lib.last_error()
+
+
+@pytest.mark.gpu
+def test_static_unique_allocates_nothing_and_takes_the_largest_size():
+    """The call leaves torch's allocator and the device's free memory untouched, and the
+    largest accepted size (exactly the scratch capacity) runs and counts correctly."""
+    lib = _lib.load()
+    with torch.cuda.device(DEV):
+        n = MAX_ROWS
+        # sorted rows with every value repeated four times: n / 4 distinct coordinates
+        base = torch.arange(n, dtype=torch.int32, device=DEV) // 4
+        coords = torch.stack([base >> 16, (base >> 8) & 255, base & 255], dim=1).contiguous()
+        uniq = torch.empty((n, 3), dtype=torch.int32, device=DEV)
+        idx = torch.empty(n + 1, dtype=torch.int64, device=DEV)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+        # one warm call first: it looks up the scratch array's address for this device
+        _lib.check(lib.mn_unique_coordinates_static(_ptr(coords), 1000, 3, None, 1, _ptr(uniq),
+                                                    _ptr(idx), stream))
+        torch.cuda.synchronize()
+        held, reserved = torch.cuda.memory_allocated(DEV), torch.cuda.memory_reserved(DEV)
+        free_before = torch.cuda.mem_get_info(DEV)[0]
+        _lib.check(lib.mn_unique_coordinates_static(_ptr(coords), n, 3, None, 1, _ptr(uniq),
+                                                    _ptr(idx), stream))
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated(DEV) == held
+        assert torch.cuda.memory_reserved(DEV) == reserved
+        assert torch.cuda.mem_get_info(DEV)[0] == free_before
+        assert int(idx[n]) == n // 4
+        assert torch.equal(uniq[:n // 4], coords[::4])
