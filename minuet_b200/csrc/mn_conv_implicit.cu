@@ -6,13 +6,13 @@
 // crosses HBM four times.  Here one persistent kernel owns 128 consecutive TARGET
 // rows at a time and accumulates ALL kernel offsets of that tile in one TMEM
 // accumulator:
-//   warps 0..3  producers: thread r fetches, for every active offset and k-block,
-//               the 128-byte slice of the source row that feeds target row r
-//               (cp.async straight into the 128-byte-swizzled A tile, zeros where
-//               the kernel map has no entry); thread 0 also starts the TMA load
-//               of the offset's transposed weight tile
-//   warp 4      allocates TMEM and issues tcgen05.mma over (offset, k-block)
-//   warps 5..8  epilogue: TMEM -> registers -> optional per-channel scale/shift
+//   warps 0..7  producers: warp w fetches, for every active offset and k-block, the
+//               128-byte slices of the source rows that feed target rows 16w..16w+15
+//               (cp.async straight into the 128-byte-swizzled A tile, eight lanes per
+//               row, zeros where the kernel map has no entry); thread 0 also starts
+//               the TMA load of the offset's transposed weight tile
+//   warp 8      allocates TMEM and issues tcgen05.mma over (offset, k-block)
+//   warps 9..12 epilogue: TMEM -> registers -> optional per-channel scale/shift
 //               (folded BatchNorm or bias), residual add, ReLU -> swizzled shared
 //               tile -> TMA store of the output rows
 // so that features are read once per pair (mostly from L2), outputs are written
@@ -30,7 +30,11 @@ namespace {
 
 using namespace tc;
 
-constexpr int kImThreads = 288;        // warps 0..3 producers, warp 4 MMA issuer, warps 5..8 epilogue
+constexpr int kProdWarps = 8;          // producer warps: warp w owns 128 / kProdWarps rows of a sub-tile
+constexpr int kProdRows = 128 / kProdWarps;
+constexpr int kMmaWarp = kProdWarps;   // then the MMA issuer, then four epilogue warps
+constexpr int kImThreads = (kProdWarps + 5) * 32;
+constexpr int kImCtas = kProdWarps > 4 ? 2 : 3;   // CTAs per SM the register file allows
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
@@ -85,7 +89,7 @@ __device__ __forceinline__ float elem_to_f32(uint16_t v) {
   return __half2float(__ushort_as_half(v));
 }
 
-__global__ void __launch_bounds__(kImThreads, 3)
+__global__ void __launch_bounds__(kImThreads, kImCtas)
 conv_implicit_kernel(const __grid_constant__ ImArgs args,
                      const __grid_constant__ CUtensorMap map_b,     // weights^T [O, N, K]
                      const __grid_constant__ CUtensorMap map_out) { // output    [T, N]
@@ -103,14 +107,14 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) {
-      mbar_init(&bar_full[s], kBM + 1);   // 128 producer lanes + the weight tile's expect_tx
+      mbar_init(&bar_full[s], kProdWarps * 32 + 1);   // every producer lane + the weight tile's expect_tx
       mbar_init(&bar_empty[s], 1);
     }
     for (int a = 0; a < 2; a++) { mbar_init(&bar_acc_full[a], 1); mbar_init(&bar_acc_empty[a], 4); }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&s_tmem_base)), "r"(tmem_cols)
                  : "memory");
@@ -122,17 +126,18 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
   const uint32_t tmem_base = s_tmem_base;
   volatile int *abort_flag = &s_abort;
 
-  if (warp < 4) {
+  if (warp < kProdWarps) {
     // ------------------------------ producers ---------------------------------
-    // Four warps feed the ring; warp w owns rows 32w .. 32w+31 of every 128-row sub-tile
-    // and lane l holds the source row of row 32w + l (one coalesced load from the
+    // Eight warps feed the ring; warp w owns rows 16w .. 16w+15 of every 128-row sub-tile
+    // and lane l holds the source row of row 16w + (l & 15) (one coalesced load from the
     // neighbour table per offset, the next offset's requested before the current one is
     // copied).  Per stage eight lanes copy one row: a warp-wide cp.async reads four whole
     // 128-byte lines (16 bytes of 32 different lines would cost a tag lookup per lane),
     // zero fill where the kernel map has no source.  Each lane's arrival on the stage
     // barrier fires when its copies have landed.  All sub-tiles of a CTA tile share every
-    // weight tile.  (One producer warp instead of four halves the kernel's speed: the
-    // copies of a stage are then issued by a single warp, and issue rate bounds it.)
+    // weight tile.  A stage is a serial chain per CTA (about 120 cycles per cp.async a
+    // thread issues): four producer warps with eight copies each were 5-18 % slower, a
+    // single producer warp 2.5x slower.
     const int sub = args.sub;
     const uint32_t b_bytes = (uint32_t)(args.stage_bytes - args.a_bytes);
     const int chunk = lane & 7;
@@ -151,7 +156,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       auto fetch = [&](int pp, int (&dst)[kMaxSub]) {
 #pragma unroll
         for (int h = 0; h < kMaxSub; h++) {
-          const int64_t t = ((int64_t)tile * sub + h) * kBM + warp * 32 + lane;
+          const int64_t t = ((int64_t)tile * sub + h) * kBM + warp * kProdRows + (lane & (kProdRows - 1));
           dst[h] = (pp >= 0 && h < sub && t < args.T) ? __ldg(args.nbr + (int64_t)pp * args.T + t) : -1;
         }
       };
@@ -177,10 +182,10 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           for (int h = 0; h < kMaxSub; h++) {
             if (h < sub) {
 #pragma unroll
-              for (int i = 0; i < 8; i++) {
+              for (int i = 0; i < kProdRows / 4; i++) {
                 const int owner = 4 * i + (lane >> 3);           // lane that holds this row's index
                 const int s_idx = __shfl_sync(0xffffffffu, src[h], owner);
-                const int rr = warp * 32 + owner;                 // row inside the sub-tile
+                const int rr = warp * kProdRows + owner;           // row inside the sub-tile
                 const uint32_t dst = smem_u32(sa) + (uint32_t)(h * kBM + rr) * 128u +
                                      (uint32_t)((chunk ^ (rr & 7)) << 4);
                 const bool valid = s_idx >= 0 && kcol < args.K;
@@ -201,7 +206,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this lane is in flight at exit
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       const uint32_t fmt = args.elem_is_bf16 ? 1u : 0u;
@@ -245,7 +250,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quarter = warp & 3;
-    uint8_t *cbuf = stage_base + (size_t)stages * args.stage_bytes + (size_t)(warp - 5) * 8192;
+    uint8_t *cbuf = stage_base + (size_t)stages * args.stage_bytes + (size_t)(warp - kMmaWarp - 1) * 8192;
     int acc = 0, chunk = 0;
     uint32_t acc_phase = 0;
     const int n = args.N;
@@ -374,7 +379,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
     for (int i = 0; i < 2000; i++) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(tmem_cols)
@@ -454,7 +459,7 @@ mn_status launch_pair_products(const PairPlan &plan, int64_t S, int64_t c_in, in
   a.acc_bufs = 2;
   a.a_bytes = kBM * kBK * 2;
   a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
-  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, 3);
+  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, kImCtas);
   a.stages = sizing.stages;
   a.tmem_cols = sizing.tmem_cols;
   a.num_offsets = 1;
@@ -576,13 +581,13 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   // at the price of a shallower ring and, past 512 / (2 * n_pad) sub-tiles, a single
   // accumulator buffer (the epilogue then no longer overlaps the next tile's MMAs).  The
   // automatic choice is the one that measured fastest per output width on maps with two or
-  // more pairs per row (4 sub-tiles at 64 columns, 1 at 128, 2 at 256 and at 32); sparse
+  // more pairs per row (4 sub-tiles at 64 and 128 columns, 2 at 256 and at 32); sparse
   // maps keep small CTA tiles and several CTAs per SM.  Callers that have timed the layer
   // pass their own choice.
   int sub = sub_hint;
   if (sub <= 0) {
     sub = 1;
-    if (pairs_per_row >= 2.0) sub = a.n_pad >= 256 ? 2 : a.n_pad >= 128 ? 1 : a.n_pad >= 64 ? 4 : 2;
+    if (pairs_per_row >= 2.0) sub = a.n_pad >= 256 ? 2 : a.n_pad >= 64 ? 4 : 2;
     while (sub > 1 && (sub * a.n_pad > 512 || a.n_tiles128 < 2 * sub * kNumSMs ||
                        2 * (sub * kBM * kBK * 2 + a.n_pad * kBK * 2) + 4 * 8192 + 2048 > 227 * 1024))
       sub--;
@@ -593,7 +598,7 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   a.acc_bufs = 2 * a.sub * a.n_pad <= 512 ? 2 : 1;
   a.a_bytes = a.sub * kBM * kBK * 2;
   a.stage_bytes = a.a_bytes + a.n_pad * kBK * 2;
-  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, 3);
+  const TcSizing sizing = size_tc_kernel(a.stage_bytes, a.acc_bufs * a.sub * a.n_pad, kMaxStages, kImCtas);
   a.stages = sizing.stages;
   a.tmem_cols = sizing.tmem_cols;
   a.num_offsets = (int)O;
