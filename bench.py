@@ -877,7 +877,7 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
                 "returns": "one uint8 class label per voxel of all clouds, on rank 0's host"},
         "gpu_launches": int(launches),
         "library_launches_per_forward": int(launches / max(steps, 1)),
-        "blocking_host_reads_per_forward": 4,
+        "blocking_host_reads_per_forward": 4,   # one unique count per stride level, all in SparseUNet.plan
         "roofline": roofline,
         "cpu_baseline": cpu,
         "library_kernel_ms_rank0_one_step": kernels,

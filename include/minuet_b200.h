@@ -89,7 +89,7 @@ typedef struct {
 /* Version of this interface; mn_version() returns the value the library was
  * built with.  A binding should refuse a library whose version differs from the
  * header it was written against: argument lists change between versions. */
-#define MN_ABI_VERSION 12
+#define MN_ABI_VERSION 13
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -310,13 +310,21 @@ int mn_implicit_supported(int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype
  * source row feeding target t under mask row p, or -1; tile_bits_out uint32
  * [ceil(T/128)] has bit p set when any target of that 128-row tile has a
  * source under mask row p.  sizes_host: HOST sizes of the mask rows. */
-size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O);
+size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t T);
+/* With perm_out (int32 [T]) the rows of the table are a permutation of the targets:
+ * perm_out[r] is the target row at table position r, chosen so that targets with the
+ * same set of offsets (equal hit words, target_bits as written by mn_build_kernel_map)
+ * sit in the same 128-row tiles and tiles can skip the offsets none of their rows has.
+ * nbr_out and tile_bits_out are then in table order; the forward pass takes perm and
+ * writes every output row at its own place.  perm_out NULL: table order = target order
+ * (target_bits and ctrl are then not read). */
 mn_status mn_build_neighbor_table(const int32_t *source_masks, const int32_t *target_masks,
                                   const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
-                                  int32_t *nbr_out, uint32_t *tile_bits_out, void *ws,
-                                  size_t ws_bytes, void *stream);
+                                  const uint32_t *target_bits, int32_t *nbr_out,
+                                  uint32_t *tile_bits_out, int32_t *perm_out, int32_t *ctrl,
+                                  void *ws, size_t ws_bytes, void *stream);
 
-/* out[t] = epilogue(sum_p sources[nbr[p, t]] @ weights[order ? order[p] : p]) with
+/* out[perm ? perm[r] : r] = epilogue(sum_p sources[nbr[p, r]] @ weights[order ? order[p] : p]) with
  * epilogue(v) = relu?(v * scale[c] + shift[c] + residual[t, c]); scale, shift
  * (fp32 [c_out]) and residual ([T, c_out], feature dtype) may each be NULL.
  * sub_tiles: 128-row sub-tiles per CTA tile (1..4; they share every weight tile);
@@ -325,7 +333,7 @@ size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c_out);
 mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
     const void *sources, const void *weights, const void *weights_t, const int32_t *nbr,
-    const uint32_t *tile_bits, const int32_t *order, const float *scale, const float *shift,
+    const uint32_t *tile_bits, const int32_t *perm, const int32_t *order, const float *scale, const float *shift,
     const void *residual, int relu, double pairs_per_row, int sub_tiles, void *targets_out,
     int32_t *status_dev, void *ws, size_t ws_bytes, void *stream);
 

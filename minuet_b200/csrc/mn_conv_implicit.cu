@@ -64,6 +64,8 @@ struct ImArgs {
   int32_t pair_rows;                            // mask rows in pair_tile_prefix
   int32_t pair_tile_prefix[MN_MAX_PAIR_ROWS + 1];
   float *out_f32;                               // [T, N]
+  const int32_t *perm;   // [T] or NULL: tile row r is target row perm[r] (nbr is in tile-row order)
+  uint8_t *out16;        // [T, N] 16-bit output, addressed row by row when perm is given
 };
 
 // mask row that owns 128-row tile `tile` of the product buffer
@@ -145,11 +147,14 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < args.num_tiles; tile += gridDim.x) {
-      uint32_t rest = 0u;
+      uint32_t rest = 0u, hb[kMaxSub];   // offsets of the CTA tile and of each sub-tile
 #pragma unroll
-      for (int h = 0; h < kMaxSub; h++)
+      for (int h = 0; h < kMaxSub; h++) {
+        hb[h] = 0u;
         if (h < sub && tile * sub + h < args.n_tiles128)
-          rest |= args.pair_mode ? 1u : __ldg(args.tile_bits + tile * sub + h);
+          hb[h] = args.pair_mode ? 1u : __ldg(args.tile_bits + tile * sub + h);
+        rest |= hb[h];
+      }
       const int pair_row = args.pair_mode ? pair_row_of_tile(args, tile) : 0;
       int p = rest != 0u ? __ffs(rest) - 1 : -1;
       int src[kMaxSub], src_next[kMaxSub];
@@ -157,7 +162,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
 #pragma unroll
         for (int h = 0; h < kMaxSub; h++) {
           const int64_t t = ((int64_t)tile * sub + h) * kBM + warp * kProdRows + (lane & (kProdRows - 1));
-          dst[h] = (pp >= 0 && h < sub && t < args.T) ? __ldg(args.nbr + (int64_t)pp * args.T + t) : -1;
+          // a sub-tile without offset pp has no table block: its rows are zero rows
+          dst[h] = (pp >= 0 && ((hb[h] >> pp) & 1u) && t < args.T) ? __ldg(args.nbr + (int64_t)pp * args.T + t) : -1;
         }
       };
       fetch(p, src);
@@ -258,10 +264,12 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       if (args.residual != nullptr) {
         // the residual rows of this lane are on their way while the MMAs run
         for (int h = 0; h < args.sub; h++) {
-          const int64_t rrow = (int64_t)(tile * args.sub + h) * kBM + quarter * 32 + lane;
-          if (rrow < args.T)
+          int64_t rrow = (int64_t)(tile * args.sub + h) * kBM + quarter * 32 + lane;
+          if (rrow < args.T) {
+            if (args.perm != nullptr) rrow = __ldg(args.perm + rrow);
             for (int off = 0; off < n * 2; off += 128)
               asm volatile("prefetch.global.L1 [%0];" ::"l"(args.residual + rrow * n * 2 + off));
+          }
         }
       }
       int ok = 1;
@@ -278,6 +286,8 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
       const int out_row = (tile * args.sub + h) * kBM + quarter * 32;
       if ((int64_t)out_row >= args.T) break;
       const int64_t row = (int64_t)out_row + lane;
+      // row of the output (and of the residual) this lane's accumulator row belongs to
+      const int64_t grow = (args.perm != nullptr && row < args.T) ? (int64_t)__ldg(args.perm + row) : row;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                              (uint32_t)((acc * args.sub + h) * args.n_pad);
       for (int c0 = 0; c0 < args.n_pad; c0 += 64, chunk++) {
@@ -303,7 +313,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
             continue;
           }
           if (!buffer_free) {
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (args.perm == nullptr && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
             buffer_free = true;
           }
@@ -327,7 +337,7 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
                 f[4] += s1.x; f[5] += s1.y; f[6] += s1.z; f[7] += s1.w;
               }
               if (args.residual != nullptr && row < args.T) {
-                const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(args.residual + (row * n + c) * 2));
+                const uint4 rv = __ldg(reinterpret_cast<const uint4 *>(args.residual + (grow * n + c) * 2));
                 const uint16_t *r16 = reinterpret_cast<const uint16_t *>(&rv);
 #pragma unroll
                 for (int i = 0; i < 8; i++)
@@ -355,6 +365,23 @@ conv_implicit_kernel(const __grid_constant__ ImArgs args,
           }
         }
         if (args.out_f32 != nullptr) continue;
+        if (args.perm != nullptr) {
+          // permuted rows: eight lanes store one row's 128 bytes of this chunk, four rows
+          // per instruction, each row at its own place in the output
+          __syncwarp();
+          const int piece = lane & 7;
+          const int col = c0 + piece * 8;
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int rl = 4 * i + (lane >> 3);
+            const int64_t drow = __shfl_sync(0xffffffffu, grow, rl);
+            const uint4 v = *reinterpret_cast<const uint4 *>(buf + rl * 128 + ((piece ^ (rl & 7)) << 4));
+            if ((int64_t)out_row + rl < args.T && col < n)
+              *reinterpret_cast<uint4 *>(args.out16 + (drow * n + col) * 2) = v;
+          }
+          __syncwarp();
+          continue;
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
@@ -404,24 +431,46 @@ rank_to_source_kernel(const int32_t *__restrict__ source_masks, int64_t S, int O
   }
 }
 
-// nbr[p, t] = source row feeding target t under mask row p (or -1); bit p of
-// tile_bits[t / 128] is set when any row of that 128-row tile has such a source
+// nbr[p, r] = source row feeding target perm[r] (perm == NULL: target r) under mask row p
+// (or -1); bit p of tile_bits[r / 128] is set when any row of that 128-row tile has such a
+// source.  With the targets' hit words (`bits`) only the (tile, p) blocks whose bit is set
+// are written, and a row looks its source up only for the offsets of its own word: the rest
+// of the table is never read by the forward pass, which checks tile_bits first.
 __global__ void __launch_bounds__(128)
 neighbor_table_kernel(const int32_t *__restrict__ target_masks, int64_t T, int O,
                       const __grid_constant__ CumSizes cs,
-                      const int32_t *__restrict__ src_of_rank, int32_t *__restrict__ nbr,
+                      const int32_t *__restrict__ src_of_rank, const int32_t *__restrict__ perm,
+                      const uint32_t *__restrict__ bits, int32_t *__restrict__ nbr,
                       uint32_t *__restrict__ tile_bits) {
   __shared__ uint32_t s_bits;
   if (threadIdx.x == 0) s_bits = 0u;
   __syncthreads();
-  const int64_t t = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  const int64_t r = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  const int64_t t = (r < T && perm != nullptr) ? (int64_t)__ldg(perm + r) : r;
+  if (bits != nullptr) {
+    const uint32_t mine = r < T ? __ldg(bits + t) : 0u;
+    const uint32_t warp_or = __reduce_or_sync(0xffffffffu, mine);
+    if ((threadIdx.x & 31) == 0 && warp_or != 0u) atomicOr(&s_bits, warp_or);
+    __syncthreads();
+    const uint32_t tile = s_bits;
+    if (threadIdx.x == 0) tile_bits[blockIdx.x] = tile;
+    if (r >= T) return;
+    for (uint32_t rest = tile; rest != 0u; rest &= rest - 1u) {
+      const int p = __ffs(rest) - 1;
+      int v = -1;
+      if ((mine >> p) & 1u)
+        v = __ldg(src_of_rank + cs.cum[p] + __ldg(target_masks + (int64_t)p * T + t));
+      nbr[(int64_t)p * T + r] = v;
+    }
+    return;
+  }
   uint32_t mine = 0u;
   for (int p = 0; p < O; p++) {
     int v = -1;
-    if (t < T) {
+    if (r < T) {
       const int m = __ldg(target_masks + (int64_t)p * T + t);
       if (m >= 0) v = __ldg(src_of_rank + cs.cum[p] + m);
-      nbr[(int64_t)p * T + t] = v;
+      nbr[(int64_t)p * T + r] = v;
     }
     mine |= (v >= 0 ? 1u : 0u) << p;
   }
@@ -429,6 +478,15 @@ neighbor_table_kernel(const int32_t *__restrict__ target_masks, int64_t T, int O
   if ((threadIdx.x & 31) == 0 && mine != 0u) atomicOr(&s_bits, mine);
   __syncthreads();
   if (threadIdx.x == 0) tile_bits[blockIdx.x] = s_bits;
+}
+
+// sort keys of the row permutation: the row's hit word (rows with the same set of
+// offsets become neighbours, so whole tiles can skip the offsets none of their rows has)
+__global__ void hit_word_keys_kernel(const uint32_t *__restrict__ bits, int64_t n,
+                                     uint64_t *__restrict__ keys) {
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz)
+    keys[i] = (uint64_t)__ldg(bits + i);
 }
 
 }  // namespace
@@ -490,22 +548,29 @@ extern "C" int mn_implicit_supported(int64_t O, int64_t c_in, int64_t c_out, mn_
          c_out >= 8 && c_out % 8 == 0 && c_out <= 256;
 }
 
-extern "C" size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O) {
+extern "C" size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O, int64_t T) {
   int64_t e = 0;
   for (int64_t p = 0; p < O; p++) e += sizes_host[p];
-  return align_up((size_t)std::max<int64_t>(e, 1) * sizeof(int32_t), 256) + 256;
+  const size_t n = (size_t)std::max<int64_t>(T, 1);
+  const size_t sort = 2 * align_up(n * 8, 256) + 2 * align_up(n * 4, 256) + radix_sort_workspace_bytes(T);
+  return align_up((size_t)std::max<int64_t>(e, 1) * sizeof(int32_t), 256) + sort + 1024;
 }
 
 extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
                                              const int32_t *target_masks,
                                              const int32_t *sizes_host, int64_t O, int64_t S,
-                                             int64_t T, int32_t *nbr_out, uint32_t *tile_bits_out,
-                                             void *ws_ptr, size_t ws_bytes, void *stream) {
+                                             int64_t T, const uint32_t *target_bits,
+                                             int32_t *nbr_out, uint32_t *tile_bits_out,
+                                             int32_t *perm_out, int32_t *ctrl, void *ws_ptr,
+                                             size_t ws_bytes, void *stream) {
   MN_CHECK_ARG(O >= 1 && O <= 32, "neighbor table: %lld offsets (supported: 1..32)", (long long)O);
-  MN_CHECK_ARG(S >= 0 && T >= 0 && sizes_host != nullptr, "neighbor table: bad arguments");
+  MN_CHECK_ARG(S >= 0 && T >= 0 && T < (1ll << 31) && sizes_host != nullptr,
+               "neighbor table: bad arguments");
   if (T == 0) return MN_OK;
   MN_CHECK_ARG(source_masks != nullptr && target_masks != nullptr && nbr_out != nullptr &&
                    tile_bits_out != nullptr, "neighbor table: null pointer");
+  MN_CHECK_ARG(perm_out == nullptr || (target_bits != nullptr && ctrl != nullptr),
+               "neighbor table: a row permutation needs the targets' hit words and a control block");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CumSizes cs{};
   for (int64_t p = 0; p < O; p++) {
@@ -515,6 +580,21 @@ extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
   Workspace ws(ws_ptr, ws_bytes);
   int32_t *src_of_rank = ws.take<int32_t>((size_t)std::max<int64_t>(cs.cum[O], 1));
   MN_CHECK_WS(ws);
+  if (perm_out != nullptr) {
+    // stable sort of the rows by hit word: perm[r] = target row at position r
+    uint64_t *keys = ws.take<uint64_t>(T), *keys_tmp = ws.take<uint64_t>(T);
+    int32_t *vals = ws.take<int32_t>(T), *vals_tmp = ws.take<int32_t>(T);
+    MN_CHECK_WS(ws);
+    const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(T, 256));
+    MN_LAUNCH("hit_word_keys_kernel", st,
+              hit_word_keys_kernel<<<blocks, 256, 0, st>>>(target_bits, T, keys));
+    const mn_keyspec no_spec{};
+    bool in_tmp = false;
+    MN_RETURN_IF(launch_radix_sort(keys, keys_tmp, vals, vals_tmp, true, T, 0, (int)O, no_spec,
+                                   nullptr, ctrl, nullptr, ws, &in_tmp, st));
+    MN_CHECK_CUDA(cudaMemcpyAsync(perm_out, in_tmp ? vals_tmp : vals, (size_t)T * sizeof(int32_t),
+                                  cudaMemcpyDeviceToDevice, st));
+  }
   if (S > 0) {
     const dim3 grid((unsigned)std::min<int64_t>(kNumSMs * 4, div_up(S, 256)), (unsigned)O);
     MN_LAUNCH("rank_to_source_kernel", st,
@@ -522,7 +602,7 @@ extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
   }
   MN_LAUNCH("neighbor_table_kernel", st,
             neighbor_table_kernel<<<(unsigned)div_up(T, 128), 128, 0, st>>>(
-                target_masks, T, (int)O, cs, src_of_rank, nbr_out, tile_bits_out));
+                target_masks, T, (int)O, cs, src_of_rank, perm_out, target_bits, nbr_out, tile_bits_out));
   return MN_OK;
 }
 
@@ -533,7 +613,7 @@ extern "C" size_t mn_implicit_workspace_bytes(int64_t O, int64_t c_in, int64_t c
 extern "C" mn_status mn_sparse_convolution_forward_implicit(
     int64_t S, int64_t T, int64_t O, int64_t c_in, int64_t c_out, mn_dtype dtype,
     const void *sources, const void *weights, const void *weights_t_in, const int32_t *nbr,
-    const uint32_t *tile_bits,
+    const uint32_t *tile_bits, const int32_t *perm,
     const int32_t *order, const float *scale, const float *shift, const void *residual, int relu,
     double pairs_per_row, int sub_hint, void *targets_out, int32_t *status_dev, void *ws_ptr,
     size_t ws_bytes, void *stream) {
@@ -570,6 +650,8 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   a.scale = scale;
   a.shift = shift;
   a.residual = static_cast<const uint8_t *>(residual);
+  a.perm = perm;
+  a.out16 = static_cast<uint8_t *>(targets_out);
   a.status = status_dev;
   a.T = T;
   a.K = (int)c_in;

@@ -328,23 +328,28 @@ _neighbor_tables = {}
 
 
 def neighbor_table(source_masks: torch.Tensor, target_masks: torch.Tensor,
-                   sizes_host: np.ndarray):
-    """``(nbr [O, T] int32, tile_bits [ceil(T/128)] int32)`` of the kernel map that
-    the two mask tensors describe; built on first use and kept for as long as the
-    masks live (a transposed convolution passes the same masks swapped and gets
-    its own table)."""
-    key = (id(source_masks), id(target_masks))
+                   sizes_host: np.ndarray, reorder: bool = True):
+    """``(nbr [O, T] int32, tile_bits [ceil(T/128)] int32, perm [T] int32 or None)`` of
+    the kernel map that the two mask tensors describe; built on first use and kept for
+    as long as the masks live (a transposed convolution passes the same masks swapped
+    and gets its own table).  With ``reorder`` and a map that carries hit words, the
+    table's rows are the targets sorted by hit word (``perm[r]`` = target at position
+    ``r``), so that 128-row tiles skip the offsets none of their rows has."""
+    bits = hit_bits(target_masks) if reorder else None
+    key = (id(source_masks), id(target_masks), bits is not None)
     hit = _neighbor_tables.get(key)
     if hit is not None and hit[0]() is source_masks and hit[1]() is target_masks:
-        return hit[2], hit[3]
+        return hit[2], hit[3], hit[4]
     O, S = source_masks.shape
     T = target_masks.shape[1]
     device = source_masks.device
     nbr = torch.empty((O, T), dtype=torch.int32, device=device)
     tile_bits = torch.empty((T + 127) // 128, dtype=torch.int32, device=device)
-    ws = workspace(lib().mn_neighbor_table_workspace_bytes(np_ptr(sizes_host), O), device)
+    perm = torch.empty(T, dtype=torch.int32, device=device) if bits is not None else None
+    ws = workspace(lib().mn_neighbor_table_workspace_bytes(np_ptr(sizes_host), O, T), device)
     _lib.check(lib().mn_build_neighbor_table(ptr(source_masks), ptr(target_masks),
-                                             np_ptr(sizes_host), O, S, T, ptr(nbr), ptr(tile_bits),
+                                             np_ptr(sizes_host), O, S, T, ptr(bits), ptr(nbr),
+                                             ptr(tile_bits), ptr(perm), ptr(control_block(device)),
                                              ptr(ws), ws.numel(), stream_ptr(device)),
                "build_neighbor_table")
 
@@ -352,8 +357,8 @@ def neighbor_table(source_masks: torch.Tensor, target_masks: torch.Tensor,
         _neighbor_tables.pop(k, None)
 
     _neighbor_tables[key] = (weakref.ref(source_masks, drop), weakref.ref(target_masks, drop),
-                             nbr, tile_bits)
-    return nbr, tile_bits
+                             nbr, tile_bits, perm)
+    return nbr, tile_bits, perm
 
 
 # ---------------------------------------------------------------------------

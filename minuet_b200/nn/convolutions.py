@@ -451,6 +451,28 @@ class SparseConv(Module):
             self._tuning_maps = None
 
     # -- forward ------------------------------------------------------------------
+    def prepare(self, coordinates: torch.Tensor, stride, batch_dims: Optional[torch.Tensor]):
+        """Build (or find in the cache) the output coordinates and the kernel map this
+        layer needs for inputs at ``coordinates`` / ``stride``, without running it, and
+        return ``(coordinates, stride, batch_dims)`` of its output.  A model that calls
+        this for all its layers before the first convolution has every blocking read
+        and every kernel-map build behind it when the feature kernels start, and its
+        forward pass then runs without a host wait (see ``SparseUNet.plan``)."""
+        if self.is_trivial:
+            return coordinates, stride, batch_dims
+        cache = self._kernel_map_cache
+        if cache is None:
+            raise ValueError("Kernel map cache must be specified")
+        out_c, out_s, out_bd = cache.get_target_coordinates(
+            source_coordinates=coordinates, source_batch_dims=batch_dims, source_stride=stride,
+            kernel_stride=self.stride, transposed=self.transposed)
+        cache.get_kernel_map(
+            source_coordinates=coordinates, source_stride=stride, source_batch_dims=batch_dims,
+            target_coordinates=out_c, target_stride=out_s, target_batch_dims=out_bd,
+            kernel_size=self.kernel_size, kernel_dilation=self.dilation,
+            transposed=self.transposed)
+        return out_c, out_s, out_bd
+
     def _lookup(self, inputs: SparseTensor):
         """Output coordinates and the kernel map of this layer for ``inputs``."""
         cache = self._kernel_map_cache

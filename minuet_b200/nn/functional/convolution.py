@@ -23,6 +23,10 @@ ALGORITHM = "auto"
 # 128-row sub-tiles per CTA tile of the fused kernel when the call does not say
 # (0 = chosen by the library)
 IMPLICIT_SUB_TILES = 0
+# The fused kernel walks the targets sorted by hit word (rows with the same set of
+# offsets share tiles, and tiles skip the offsets they do not have); False keeps the
+# targets' own order
+REORDER_ROWS = True
 
 
 def set_gemm_parallel_level(level: int):
@@ -293,13 +297,14 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
     T = target_masks.shape[1]
     c_in, c_out = weights.shape[1], weights.shape[2]
     device = sources.device
-    nbr, tile_bits = engine.neighbor_table(source_masks, target_masks, sizes_host)
+    nbr, tile_bits, perm = engine.neighbor_table(source_masks, target_masks, sizes_host,
+                                                 reorder=REORDER_ROWS)
     lib = engine.lib()
     ws = engine.workspace(lib.mn_implicit_workspace_bytes(O, c_in, c_out), device)
     _lib.check(lib.mn_sparse_convolution_forward_implicit(
         S, T, O, c_in, c_out, engine.dtype_code(weights.dtype), engine.ptr(sources),
         engine.ptr(weights), engine.ptr(weights_t), engine.ptr(nbr), engine.ptr(tile_bits),
-        engine.ptr(order),
+        engine.ptr(perm), engine.ptr(order),
         engine.ptr(scale), engine.ptr(shift), engine.ptr(residual), int(bool(relu)),
         float(sizes_host.sum()) / max(T, 1),
         int(IMPLICIT_SUB_TILES if sub_tiles is None else sub_tiles),
@@ -311,12 +316,15 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
 def estimate_ms(algorithm: str, S, T, O, c_in, c_out, pairs, shortcut: bool) -> float:
     """Rough cost of one 16-bit forward pass, from fits to measured layers of the
     benchmark network on a B200.  Pair lists move every non-centre pair row three
-    times (16-bit read, fp32 product written and read back) at about 2.7 TB/s; the
-    fused kernel pays about 3.5 ns per (128-row tile, offset, 64-channel block)
-    whether or not the offset has pairs in the tile.  Only the ORDER of the two
-    estimates matters."""
+    times (16-bit read, fp32 product written and read back) at about 2.7 TB/s.  The
+    fused kernel pays about 3.3 ns per (128-row tile, offset present in the tile,
+    64-channel block) plus 10 ns per tile; with the rows sorted by hit word a tile of a
+    map with E/T pairs per row holds about 1 + 2.2 (E/T - 1) of the O offsets.  Only
+    the ORDER of the two estimates matters."""
     if algorithm == "implicit":
-        return 0.05 + 3.5e-6 * math.ceil(T / 128) * O * math.ceil(c_in / 64) * \
+        tiles = math.ceil(T / 128)
+        present = min(float(O), 1.0 + 2.2 * max(pairs / max(T, 1) - 1.0, 0.0)) if REORDER_ROWS else O
+        return 0.03 + 1.0e-5 * tiles + 3.3e-6 * tiles * present * math.ceil(c_in / 64) * \
             (0.7 + 0.3 * c_out / 128)
     rest = pairs - (min(S, T) if shortcut else 0)
     return 0.05 + (rest * (8.0 * c_out + 2.0 * c_in) + 2.0 * (S * c_in + T * c_out)) / 2.7e9

@@ -107,7 +107,20 @@ class SparseUNet(nn.Module):
                 m.freeze_weights()      # the weights of a fused model no longer change
         return self
 
+    def plan(self, x: SparseTensor):
+        """Coordinates of every stride level and all nine kernel maps of the network,
+        built up front: the four blocking reads (one unique count per level) and the
+        copies of the per-offset pair counts are then over before the first feature
+        kernel is queued, and the forward pass below runs without a host wait."""
+        c, s, bd = x.C, x.stride, x.batch_dims
+        self.stem[0].prepare(c, s, bd)
+        for down, enc in zip(self.down, self.enc):
+            c, s, bd = down[0].prepare(c, s, bd)
+            enc[0].body[0].prepare(c, s, bd)
+
     def forward(self, x: SparseTensor) -> SparseTensor:
+        if x.F.is_cuda and self.stem[0]._kernel_map_cache is not None:
+            self.plan(x)
         x = self.stem(x)
         skips = []
         for down, enc in zip(self.down, self.enc):

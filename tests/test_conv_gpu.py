@@ -250,6 +250,50 @@ def test_frozen_weights_give_the_same_bits(oracle_lib, algorithm):
     assert torch.equal(head(inp).F, y)
 
 
+def test_neighbor_table_sorted_by_hit_word(oracle_lib):
+    """Kernel maps from the fused build carry hit words: the table's rows are then the
+    targets in stable order of their hit word, nbr / tile_bits are in that order, and the
+    fused forward gives the same function with and without the reordering."""
+    from minuet_b200 import engine
+    from minuet_b200.nn.functional import convolution as conv_mod
+    rng = np.random.default_rng(31)
+    src, sbd = synth.random_small_batch(rng, 2, 6000, 30)
+    conv, cache, inp, out, want = run_layer(oracle_lib, src, sbd, 32, 32, 3, 1, torch.float16)
+    sm, tm, order, sizes = cache.get_kernel_map(inp.C, 1, inp.batch_dims, inp.C, 1, inp.batch_dims, 3, 1)
+    hs = engine.host_copy(sizes)
+    nbr, tile_bits, perm = engine.neighbor_table(sm, tm, hs)
+    nat, nat_bits, none = engine.neighbor_table(sm, tm, hs, reorder=False)
+    assert none is None and perm is not None
+    words = engine.hit_bits(tm).cpu().numpy().astype(np.uint32)
+    p = perm.cpu().numpy()
+    assert np.array_equal(np.sort(p), np.arange(len(src)))
+    assert np.array_equal(p, np.argsort(words, kind="stable"))
+    # only the (tile, offset) blocks whose tile bit is set are written; the others have no pair
+    got, ref, tb = nbr.cpu().numpy(), nat.cpu().numpy()[:, p], tile_bits.cpu().numpy()
+    for tile in range(len(tb)):
+        rows = slice(tile * 128, (tile + 1) * 128)
+        for o in range(27):
+            if (int(tb[tile]) >> o) & 1:
+                assert np.array_equal(got[o, rows], ref[o, rows])
+            else:
+                assert (ref[o, rows] == -1).all()
+    # fewer (tile, offset) stages than in the targets' own order
+    count = lambda b: int(sum(bin(int(v) & 0xffffffff).count("1") for v in b.cpu().numpy()))
+    assert count(tile_bits) < count(nat_bits)
+    conv.tunable_config.update(algorithm="implicit")
+    scale = torch.rand(32, device=DEV) + 0.5
+    res = torch.randn(len(src), 32, device=DEV).half()
+    outs = []
+    for flag in (True, False):
+        conv_mod.REORDER_ROWS = flag
+        try:
+            outs.append(conv.forward_fused(inp, scale=scale, residual=res, relu=True).F)
+        finally:
+            conv_mod.REORDER_ROWS = True
+    assert torch.equal(outs[0], outs[1])      # same sums in the same order, other rows per tile
+    assert_close(conv(inp).F, want, torch.float16)
+
+
 def test_neighbor_table_matches_kernel_map(oracle_lib):
     """mn_build_neighbor_table turns masks back into the (mask-row ordered) kernel
     map and marks, per 128-target tile, the offsets that have any pair."""
@@ -261,7 +305,8 @@ def test_neighbor_table_matches_kernel_map(oracle_lib):
         off = generate_kernel_offsets(3, kernel, 1, 1).astype(np.int32)
         m = oracle_lib.build_kernel_map(s_, t_, off, sb, tb)
         sm, tm = dev(m["source_masks"]), dev(m["target_masks"])
-        nbr, bits = engine.neighbor_table(sm, tm, m["sorted_sizes"])
+        nbr, bits, perm = engine.neighbor_table(sm, tm, m["sorted_sizes"])
+        assert perm is None          # masks that did not come with hit words keep their order
         want = m["kernel_map"][m["order"]]
         assert np.array_equal(nbr.cpu().numpy(), want)
         T = len(t_)
