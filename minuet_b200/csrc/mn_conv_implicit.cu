@@ -480,13 +480,17 @@ neighbor_table_kernel(const int32_t *__restrict__ target_masks, int64_t T, int O
   if (threadIdx.x == 0) tile_bits[blockIdx.x] = s_bits;
 }
 
-// sort keys of the row permutation: the row's hit word (rows with the same set of
-// offsets become neighbours, so whole tiles can skip the offsets none of their rows has)
-__global__ void hit_word_keys_kernel(const uint32_t *__restrict__ bits, int64_t n,
+// sort keys of the row permutation: the row's hit word with its bits reversed (rows with
+// the same set of offsets become neighbours, so whole tiles can skip the offsets none of
+// their rows has).  Mask rows are in ascending size order, so the reversal makes the RARE
+// offsets the most significant key bits: the few rows that have a rare offset end up
+// together instead of sprinkling it over many tiles (15 against 20 offsets per tile on a
+// map with 9 pairs per row).
+__global__ void hit_word_keys_kernel(const uint32_t *__restrict__ bits, int64_t n, int num_offsets,
                                      uint64_t *__restrict__ keys) {
   const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gsz)
-    keys[i] = (uint64_t)__ldg(bits + i);
+    keys[i] = (uint64_t)(__brev(__ldg(bits + i)) >> (32 - num_offsets));
 }
 
 }  // namespace
@@ -587,7 +591,7 @@ extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
     MN_CHECK_WS(ws);
     const int blocks = (int)std::min<int64_t>(kNumSMs * 8, div_up(T, 256));
     MN_LAUNCH("hit_word_keys_kernel", st,
-              hit_word_keys_kernel<<<blocks, 256, 0, st>>>(target_bits, T, keys));
+              hit_word_keys_kernel<<<blocks, 256, 0, st>>>(target_bits, T, (int)O, keys));
     const mn_keyspec no_spec{};
     bool in_tmp = false;
     MN_RETURN_IF(launch_radix_sort(keys, keys_tmp, vals, vals_tmp, true, T, 0, (int)O, no_spec,
@@ -663,13 +667,13 @@ extern "C" mn_status mn_sparse_convolution_forward_implicit(
   // at the price of a shallower ring and, past 512 / (2 * n_pad) sub-tiles, a single
   // accumulator buffer (the epilogue then no longer overlaps the next tile's MMAs).  The
   // automatic choice is the one that measured fastest per output width on maps with two or
-  // more pairs per row (4 sub-tiles at 64 and 128 columns, 2 at 256 and at 32); sparse
+  // more pairs per row (1 sub-tile at 64 columns, 2 at 32, 128 and 256); sparse
   // maps keep small CTA tiles and several CTAs per SM.  Callers that have timed the layer
   // pass their own choice.
   int sub = sub_hint;
   if (sub <= 0) {
     sub = 1;
-    if (pairs_per_row >= 2.0) sub = a.n_pad >= 256 ? 2 : a.n_pad >= 64 ? 4 : 2;
+    if (pairs_per_row >= 2.0) sub = a.n_pad >= 128 ? 2 : a.n_pad >= 64 ? 1 : 2;
     while (sub > 1 && (sub * a.n_pad > 512 || a.n_tiles128 < 2 * sub * kNumSMs ||
                        2 * (sub * kBM * kBK * 2 + a.n_pad * kBK * 2) + 4 * 8192 + 2048 > 227 * 1024))
       sub--;
