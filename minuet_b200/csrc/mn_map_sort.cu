@@ -613,7 +613,9 @@ mn_status launch_radix_sort(uint64_t *keys, uint64_t *keys_tmp, int32_t *vals, i
   static thread_local int grid_cache[kMaxDevices] = {0};
   int coresident = 0;
   MN_RETURN_IF(coop_grid_1024(radix_sort_kernel, kRsSmemBytes, grid_cache, &coresident));
-  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, kRsChunk)));
+  // every SM gets a block as soon as there are 2048 keys for it: the passes are latency
+  // bound (two grid barriers each), so smaller chunks per block shorten them
+  const int grid = (int)std::min<int64_t>(coresident, std::max<int64_t>(1, div_up(n, kRsChunk / 4)));
   SortArgs a{};
   a.keys[0] = keys; a.keys[1] = keys_tmp;
   a.vals[0] = vals; a.vals[1] = vals_tmp;
