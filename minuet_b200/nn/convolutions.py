@@ -421,8 +421,12 @@ class SparseConv(Module):
             lib = engine.lib()
             code = engine.dtype_code(self.kernel.dtype)
             volume = self.kernel.shape[0]
+            # 16-bit layers with few input channels run zero-padded to a multiple of 8
+            c_in = self.in_channels
+            if self.kernel.dtype != torch.float32 and self.out_channels % 8 == 0:
+                c_in = -(-c_in // 8) * 8
             pairs_ok = self.kernel.dtype != torch.float32 and bool(lib.mn_pairs_supported(
-                volume, self.in_channels, self.out_channels, code))
+                volume, c_in, self.out_channels, code))
             if not pairs_ok:
                 self._sweep(F.cuda_time_gemm, self.__AVAILABLE_THRESHOLD__, 'threshold',
                             'threshold', stop_on_error=True)
@@ -432,7 +436,7 @@ class SparseConv(Module):
                             'gather_tile_size', threshold=threshold)
                 self._sweep(F.cuda_time_scatter, divisors(self.out_channels), 'tile_size',
                             'scatter_tile_size', threshold=threshold)
-            if lib.mn_implicit_supported(volume, self.in_channels, self.out_channels, code):
+            if lib.mn_implicit_supported(volume, c_in, self.out_channels, code):
                 n_pad = -(-self.out_channels // 16) * 16
                 best, choice = self._time_algorithm('explicit', 0), ('explicit', 0)
                 for sub in self.__AVAILABLE_SUB_TILES__:

@@ -361,6 +361,13 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
              algorithm=None, sub_tiles=None, weights_t=None):
     T = tm.shape[1]
     c_out = weights.shape[2]
+    if weights.dtype != torch.float32 and weights.shape[1] % 8 != 0 and c_out % 8 == 0:
+        # few input channels (a network's first layer): zero channels up to a multiple of 8
+        # put the layer on the tensor-core paths instead of gather - FFMA GEMM - scatter
+        pad = -weights.shape[1] % 8
+        sources = torch.nn.functional.pad(sources, (0, pad))
+        weights = torch.nn.functional.pad(weights, (0, 0, 0, pad))
+        weights_t = None
     out = torch.empty((T, c_out), dtype=weights.dtype, device=sources.device)
     has_epilogue = scale is not None or shift is not None or residual is not None or relu
 
