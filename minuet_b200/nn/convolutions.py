@@ -497,6 +497,13 @@ class SparseConv(Module):
 
     def forward(self, inputs: SparseTensor) -> SparseTensor:
         features = inputs.F
+        if self.is_trivial and torch.is_grad_enabled() and (
+                features.requires_grad or self.kernel.requires_grad):
+            # training: the plain product, differentiated by autograd
+            out = features @ self.kernel.view(self.in_channels, self.out_channels)
+            if self.bias is not None:
+                out = out + self.bias
+            return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         if self.is_trivial:
             bias = None if self.bias is None else self.bias.detach().float()
             out = F.dense_forward(features, self.kernel.view(self.in_channels, self.out_channels),

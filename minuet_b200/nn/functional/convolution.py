@@ -104,6 +104,11 @@ def sparse_convolution_forward(sources: torch.Tensor,
     """
     del parallel
     engine.require_cuda(sources)
+    if torch.is_grad_enabled() and (sources.requires_grad or weights.requires_grad):
+        return _SparseConvolution.apply(sources, weights, source_masks, target_masks,
+                                        kernel_map_order, kernel_map_sizes, gather_tile_size,
+                                        scatter_tile_size, allow_shortcut_matmul, threshold,
+                                        algorithm, sub_tiles)
     sources = sources.contiguous()
     weights = weights.contiguous()
     sm, tm, order = _i32(source_masks), _i32(target_masks), _i32(kernel_map_order)
@@ -113,6 +118,63 @@ def sparse_convolution_forward(sources: torch.Tensor,
     return _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size,
                     scatter_tile_size, allow_shortcut_matmul, threshold, algorithm=algorithm,
                     sub_tiles=sub_tiles, weights_t=weights_t)
+
+
+class _SparseConvolution(torch.autograd.Function):
+    """Differentiable sparse convolution (the reference has no backward pass).
+
+    With pairs ``(s, t)`` under offset ``k``: ``out[t] += x[s] W[k]``, hence
+    ``dx[s] += dout[t] W[k]^T`` -- the same convolution with the two masks swapped and
+    every weight matrix transposed, run by the same kernels -- and
+    ``dW[k] = sum over the pairs of x[s]^T dout[t]``, computed per offset from the pair
+    rows in rank order (index selection and one fp32 product per offset; written for
+    correctness, not tuned)."""
+
+    @staticmethod
+    def forward(ctx, sources, weights, source_masks, target_masks, order, sizes, gather_tile,
+                scatter_tile, shortcut, threshold, algorithm, sub_tiles):
+        x = sources.detach().contiguous()
+        w = weights.detach().contiguous()
+        sm, tm, od = _i32(source_masks), _i32(target_masks), _i32(order)
+        S, T, O, c_in, c_out, sizes_host = _prepare(w, sm, tm, sizes, x)
+        if x.shape[0] != S:
+            raise RuntimeError(f"sources has {x.shape[0]} rows but the masks describe {S}")
+        ctx.save_for_backward(x, w, sm, tm, od if od is not None else torch.empty(0), sizes)
+        ctx.has_order = od is not None
+        ctx.args = (gather_tile, scatter_tile, shortcut, threshold, algorithm, sub_tiles)
+        return _forward(x, w, sm, tm, od, sizes_host, gather_tile, scatter_tile, shortcut,
+                        threshold, algorithm=algorithm, sub_tiles=sub_tiles)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, w, sm, tm, od, sizes = ctx.saved_tensors
+        od = od if ctx.has_order else None
+        gather_tile, scatter_tile, shortcut, threshold, algorithm, sub_tiles = ctx.args
+        grad_out = grad_out.contiguous()
+        O = sm.shape[0]
+        sizes_host = engine.host_copy(sizes, np.int32)
+        grad_x = grad_w = None
+        if ctx.needs_input_grad[0]:
+            grad_x = _forward(grad_out, w.transpose(1, 2).contiguous(), tm, sm, od, sizes_host,
+                              scatter_tile, gather_tile, shortcut, threshold, algorithm=algorithm,
+                              sub_tiles=sub_tiles)
+        if ctx.needs_input_grad[1]:
+            grad_w = torch.zeros_like(w, dtype=torch.float32)
+            for p in range(O):
+                n = int(sizes_host[p])
+                if n == 0:
+                    continue
+                k = p if od is None else int(od[p])
+                s_rows = torch.nonzero(sm[p] >= 0).squeeze(1)
+                t_rows = torch.nonzero(tm[p] >= 0).squeeze(1)
+                # pair r of this mask row is (source with rank r, target with rank r)
+                s_by_rank = torch.empty(n, dtype=torch.int64, device=x.device)
+                t_by_rank = torch.empty(n, dtype=torch.int64, device=x.device)
+                s_by_rank[sm[p, s_rows].long()] = s_rows
+                t_by_rank[tm[p, t_rows].long()] = t_rows
+                grad_w[k] = x[s_by_rank].float().t() @ grad_out[t_by_rank].float()
+            grad_w = grad_w.to(w.dtype)
+        return (grad_x, grad_w) + (None,) * 10
 
 
 def sparse_convolution_forward_fused(sources: torch.Tensor, weights: torch.Tensor,

@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+    config.addinivalue_line("markers", "needs_grad: the test differentiates through the layers")
 
 
 def pytest_collection_modifyitems(config, items):
@@ -34,3 +35,15 @@ def mn_lib():
     from minuet_b200 import build, _lib
     build.build()
     return _lib.load()
+
+
+@pytest.fixture(autouse=True)
+def _no_grad_unless_asked(request):
+    """The parity tests are inference tests: they run without autograd, as the benchmark
+    does.  Tests marked ``needs_grad`` differentiate through the layers."""
+    import torch
+    if "needs_grad" in request.keywords:
+        yield
+    else:
+        with torch.no_grad():
+            yield

@@ -250,6 +250,65 @@ def test_frozen_weights_give_the_same_bits(oracle_lib, algorithm):
     assert torch.equal(head(inp).F, y)
 
 
+@pytest.mark.needs_grad
+@pytest.mark.parametrize("stride,kernel", [(1, 3), (2, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_backward_matches_autograd_of_the_pairwise_sum(oracle_lib, stride, kernel, dtype):
+    """Gradients of a layer (and of the transposed layer that shares its map) against
+    autograd on the same function written with torch index operations over the oracle's
+    kernel map, in float64."""
+    rng = np.random.default_rng(41)
+    src, sbd = synth.random_small_batch(rng, 2, 1500, 16)
+    c_in, c_out = 8, 16
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    conv = minuet.nn.SparseConv3d(c_in, c_out, kernel, stride=stride, bias=True, dtype=dtype, device=DEV)
+    back = minuet.nn.SparseConv(3, c_out, c_in, kernel, stride=stride, transposed=True, dtype=dtype,
+                                device=DEV)
+    minuet.set_kernel_map_cache(conv, cache)
+    minuet.set_kernel_map_cache(back, cache)
+    x = torch.as_tensor(rng.standard_normal((len(src), c_in)), device=DEV).to(dtype).requires_grad_()
+    inp = minuet.SparseTensor(x, dev(src), batch_dims=dev(sbd))
+    mid = conv(inp)
+    out = back(mid) if stride > 1 else mid
+    g = torch.as_tensor(rng.standard_normal(tuple(out.F.shape)), device=DEV).to(dtype)
+    (out.F * g).sum().backward()
+
+    # the same function with torch ops, float64
+    off = generate_kernel_offsets(3, kernel, 1, 1).astype(np.int32)
+    tgt, tbd = (src, sbd) if stride == 1 else oracle_lib.downsample(src, stride, sbd)
+    km = oracle_lib.build_kernel_map(src, tgt, off, sbd, tbd)["kernel_map"]    # [O, T] -> source row
+    x64 = x.detach().double().requires_grad_()
+    w64 = conv.kernel.detach().double().requires_grad_()
+    b64 = conv.bias.detach().double().requires_grad_()
+    wb64 = back.kernel.detach().double().requires_grad_()
+    y = torch.zeros((len(tgt), c_out), dtype=torch.float64, device=DEV)
+    z = torch.zeros((len(src), c_in), dtype=torch.float64, device=DEV)
+    pairs = []
+    for o in range(len(off)):
+        t_rows = torch.as_tensor(np.nonzero(km[o] >= 0)[0], device=DEV)
+        s_rows = torch.as_tensor(km[o][km[o] >= 0].astype(np.int64), device=DEV)
+        pairs.append((s_rows, t_rows))
+        y = y.index_add(0, t_rows, x64[s_rows] @ w64[o])
+    y = y + b64
+    if stride > 1:
+        for o, (s_rows, t_rows) in enumerate(pairs):       # transposed: coarse -> fine
+            z = z.index_add(0, s_rows, y[t_rows] @ wb64[o])
+        ref = z
+    else:
+        ref = y
+    (ref * g.double()).sum().backward()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    def close(got, want):
+        scale = float(want.abs().max()) + 1e-12
+        assert float((got.double() - want).abs().max()) <= tol * scale
+    close(out.F.detach(), ref.detach())
+    close(x.grad, x64.grad)
+    close(conv.kernel.grad, w64.grad)
+    close(conv.bias.grad, b64.grad)
+    if stride > 1:
+        close(back.kernel.grad, wb64.grad)
+
+
 def test_neighbor_table_sorted_by_hit_word(oracle_lib):
     """Kernel maps from the fused build carry hit words: the table's rows are then the
     targets in stable order of their hit word, nbr / tile_bits are in that order, and the

@@ -178,3 +178,31 @@ def test_status_word_is_reported_on_the_forward_path():
     engine.status_word(DEV).fill_(engine.STATUS_KEY_BOX)
     with pytest.raises(RuntimeError, match="bounding box"):
         engine.check_status(DEV)
+
+
+@pytest.mark.needs_grad
+def test_small_unet_trains_one_step():
+    """The whole network is differentiable: a training step on a small batch changes the
+    loss and leaves finite gradients on every parameter."""
+    torch.manual_seed(1)
+    rng = np.random.default_rng(7)
+    coords, bd = synth.random_small_batch(rng, 2, 2000, 30)
+    feats = torch.as_tensor(rng.random((len(coords), 3)).astype(np.float32), device=DEV)
+    labels = torch.as_tensor(rng.integers(0, 5, len(coords)), device=DEV)
+    net = SparseUNet(3, num_classes=5, channels=(8, 16), stem_channels=8).to(DEV).train()
+    cache = minuet.nn.KernelMapCache(ndim=3, dtype=torch.int32, device=DEV)
+    minuet.set_kernel_map_cache(net, cache)
+    opt = torch.optim.SGD(net.parameters(), lr=0.05)
+    x = minuet.SparseTensor(feats, torch.as_tensor(coords, device=DEV),
+                            batch_dims=torch.as_tensor(bd, device=DEV))
+    losses = []
+    for _ in range(3):
+        cache.reset()
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(net(x).F, labels)
+        loss.backward()
+        for name, p in net.named_parameters():
+            assert p.grad is not None and torch.isfinite(p.grad).all(), name
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < losses[0]
