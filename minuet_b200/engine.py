@@ -53,8 +53,23 @@ def np_ptr(a: Optional[np.ndarray]):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 
 
+def _device_index(device) -> int:
+    if isinstance(device, int):
+        return device
+    if not isinstance(device, torch.device):
+        device = torch.device(device)
+    return torch.cuda.current_device() if device.index is None else device.index
+
+
+def raw_stream(device) -> int:
+    """The current stream of ``device`` as an integer handle (the raw query costs a
+    fraction of a microsecond; building a ``torch.cuda.Stream`` object costs several, and
+    the map step asks for the stream a dozen times per build)."""
+    return torch._C._cuda_getCurrentRawStream(_device_index(device))
+
+
 def stream_ptr(device) -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    return ctypes.c_void_p(raw_stream(device))
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -63,8 +78,24 @@ def dtype_code(dtype: torch.dtype) -> int:
     return _DTYPE_CODE[dtype]
 
 
+_WORKSPACE_CACHE_BYTES = 64 << 20
+_workspaces = {}
+
+
 def workspace(nbytes: int, device) -> torch.Tensor:
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    """Scratch bytes for one library call.  Requests up to 64 MiB share one grow-only
+    buffer per (device, stream): calls on one stream run in order, so the next call may
+    overwrite what the previous one left.  Larger requests get a buffer of their own."""
+    nbytes = max(int(nbytes), 256)
+    if nbytes > _WORKSPACE_CACHE_BYTES:
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    key = (_device_index(device), raw_stream(device))
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8,
+                          device=torch.device("cuda", key[0]))
+        _workspaces[key] = buf
+    return buf
 
 
 def as_i32_coords(coords: torch.Tensor) -> torch.Tensor:
@@ -103,9 +134,8 @@ def control_block(device) -> torch.Tensor:
     """The ``MN_CTRL_WORDS`` int32 control block of (device, current stream): word 0
     is the status word, the rest is grid-barrier state of the cooperative kernels.
     One block per stream, because kernels of different streams may overlap."""
-    dev = torch.device(device)
-    index = dev.index if dev.index is not None else torch.cuda.current_device()
-    key = (index, torch.cuda.current_stream(index).cuda_stream)
+    index = _device_index(device)
+    key = (index, raw_stream(index))
     block = _status.get(key)
     if block is None:
         block = torch.zeros(_lib.MN_CTRL_WORDS, dtype=torch.int32,

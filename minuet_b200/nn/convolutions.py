@@ -205,15 +205,20 @@ def build_kernel_map(source_keys: torch.Tensor, target_keys: torch.Tensor, offse
     lib = engine.lib()
     source_masks = torch.empty((O, S), dtype=torch.int32, device=device)
     target_masks = torch.empty((O, T), dtype=torch.int32, device=device)
-    order = torch.empty(O, dtype=torch.int32, device=device)
-    sizes_status = torch.empty(O + 1, dtype=torch.int32, device=device)   # sizes, status word
+    # one allocation for the small outputs: order [O], sizes + status word [O + 1] and the
+    # per-row hit words [S], [T] (each part starts on a 256-byte boundary)
+    pad = lambda n: -(-n // 64) * 64
+    small = torch.empty(2 * pad(O + 1) + pad(S) + pad(T), dtype=torch.int32, device=device)
+    order = small[:O]
+    sizes_status = small[pad(O + 1):pad(O + 1) + O + 1]                  # sizes, status word
     sizes = sizes_status[:O]
     ws = engine.workspace(lib.mn_map_workspace_bytes(S, T, O), device)
     stream = engine.stream_ptr(device)
     if O <= 32:
         # per-row hit words in mask-row order, kept with the masks for the forward kernels
-        source_bits = torch.empty(S, dtype=torch.int32, device=device)
-        target_bits = torch.empty(T, dtype=torch.int32, device=device)
+        base = 2 * pad(O + 1)
+        source_bits = small[base:base + S]
+        target_bits = small[base + pad(S):base + pad(S) + T]
         same = source_keys.data_ptr() == target_keys.data_ptr() and S == T
         _lib.check(lib.mn_build_kernel_map(
             engine.ptr(source_keys), S, engine.ptr(source_keys if same else target_keys), T,
