@@ -314,7 +314,7 @@ size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O, i
 /* With perm_out (int32 [T]) the rows of the table are a permutation of the targets:
  * perm_out[r] is the target row at table position r, chosen so that targets with the
  * same set of offsets (equal hit words, target_bits as written by mn_build_kernel_map;
- * stable sort on the bit-reversed word) sit in the same 128-row tiles and tiles can skip the offsets none of their rows has.
+ * stable sort on the Gray-sequence rank of the bit-reversed word) sit in the same 128-row tiles and tiles can skip the offsets none of their rows has.
  * nbr_out and tile_bits_out are then in table order; the forward pass takes perm and
  * writes every output row at its own place.  perm_out NULL: table order = target order
  * (target_bits and ctrl are then not read). */

@@ -327,6 +327,8 @@ def test_neighbor_table_sorted_by_hit_word(oracle_lib):
     p = perm.cpu().numpy()
     assert np.array_equal(np.sort(p), np.arange(len(src)))
     rev = np.array([int(format(int(w), "027b")[::-1], 2) for w in words], dtype=np.int64)
+    for shift in (1, 2, 4, 8, 16):      # rank of the reversed word in the reflected Gray sequence
+        rev ^= rev >> shift
     assert np.array_equal(p, np.argsort(rev, kind="stable"))     # rare offsets = high key bits
     # only the (tile, offset) blocks whose tile bit is set are written; the others have no pair
     got, ref, tb = nbr.cpu().numpy(), nat.cpu().numpy()[:, p], tile_bits.cpu().numpy()
