@@ -848,8 +848,15 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
             sum_flops += flops
             sum_bound += bound
             sum_meas += meas
+            # fused layers: pairs / (128 rows x (tile, offset) stages issued) = the share of the
+            # MMA rows that carry a pair (the rest are zero rows of tiles that hold the offset)
+            useful = None
+            if e.get("tile_bits") is not None:
+                tb = e["tile_bits"].to(torch.int64) & 0xffffffff
+                stages_issued = int(((tb[:, None] >> torch.arange(32, device=tb.device)) & 1).sum())
+                useful = round(e["E"] / max(128 * stages_issued, 1), 3)
             layers.append([e["S"], e["T"], e["O"], e["E"], e["c_in"], e["c_out"], e["algorithm"],
-                           round(bound, 4), round(meas, 4)])
+                           round(bound, 4), round(meas, 4), useful])
         # the nine kernel maps of the forward (one per stride level and kernel size)
         map_bytes = 0
         seen = set()
@@ -865,7 +872,7 @@ def unet_section(args, torch, dist, dev, rank, world, lib):
             "peak_source": peak_kind + (" (sustained bf16 figure: the layers run inside a long step)"
                                         if "bf16_tflops_sustained" in peaks else ""),
             "layer_columns": ["S", "T", "O", "E", "c_in", "c_out", "algorithm", "bound_ms",
-                              "measured_ms"],
+                              "measured_ms", "useful_mma_row_fraction"],
             "layers": layers,
             "sum_layer_bytes": int(sum_bytes), "sum_layer_flops": sum_flops,
             "sum_layer_bound_ms": round(sum_bound, 3), "sum_layer_measured_ms": round(sum_meas, 3),

@@ -305,6 +305,7 @@ class SparseConv(Module):
                                 'sub_tiles': 0}
         self._tuning_data = None
         self._tuning_maps = None
+        self._tuning_epilogue = (False, False, False, False)
         self._frozen_kernel_t = None
 
     def reset_parameters(self):
@@ -392,7 +393,7 @@ class SparseConv(Module):
         untimed pass, which builds whatever the algorithm derives from the map once:
         pair lists, neighbour tables)."""
         kw = dict(allow_shortcut_matmul=self._allow_shortcut_matmul, algorithm=algorithm,
-                  sub_tiles=sub_tiles)
+                  sub_tiles=sub_tiles, epilogue=self._tuning_epilogue)
         for sm, tm, order, sz in self._tuning_maps:
             F.time_forward(self.kernel, sm, tm, order, sz, **kw)
         times = [F.time_forward(self.kernel, sm, tm, order, sz,
@@ -400,7 +401,8 @@ class SparseConv(Module):
                                 algorithm=algorithm, sub_tiles=sub_tiles,
                                 gather_tile_size=self._tunable_config['gather_tile_size'],
                                 scatter_tile_size=self._tunable_config['scatter_tile_size'],
-                                threshold=self._tunable_config['threshold'])
+                                threshold=self._tunable_config['threshold'],
+                                epilogue=self._tuning_epilogue)
                  for _ in range(self.__NUM_TUNING_ROUNDS__)
                  for sm, tm, order, sz in self._tuning_maps]
         return float(np.mean(times))
@@ -549,6 +551,9 @@ class SparseConv(Module):
             return SparseTensor(out, inputs.C, stride=inputs.stride, batch_dims=inputs.batch_dims)
         coordinates, stride, batch_dims, source_masks, target_masks, order, sizes = \
             self._lookup(inputs)
+        if self._tuning_data is not None:     # the tuner times the layer with the epilogue it runs
+            self._tuning_epilogue = (scale is not None, shift is not None, residual is not None,
+                                     bool(relu))
         out = F.sparse_convolution_forward_fused(
             sources=features, weights=self.kernel, source_masks=source_masks,
             target_masks=target_masks, kernel_map_order=order, kernel_map_sizes=sizes,

@@ -361,6 +361,8 @@ def _implicit_forward(sources, weights, source_masks, target_masks, order, sizes
     device = sources.device
     nbr, tile_bits, perm = engine.neighbor_table(source_masks, target_masks, sizes_host,
                                                  reorder=REORDER_ROWS)
+    if engine.LAYER_LOG:      # benchmarks read the per-tile offset bits of the logged layer
+        engine.LAYER_LOG[-1]["tile_bits"] = tile_bits
     lib = engine.lib()
     ws = engine.workspace(lib.mn_implicit_workspace_bytes(O, c_in, c_out), device)
     _lib.check(lib.mn_sparse_convolution_forward_implicit(
@@ -468,19 +470,25 @@ def _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scat
 def time_forward(weights, source_masks, target_masks, kernel_map_order, kernel_map_sizes,
                  allow_shortcut_matmul: bool = False, algorithm: str = "explicit",
                  sub_tiles: int = 0, gather_tile_size: int = 1, scatter_tile_size: int = 1,
-                 threshold: Optional[float] = -1) -> float:
+                 threshold: Optional[float] = -1, epilogue=(False, False, False, False)) -> float:
     """Milliseconds of one whole forward pass with the given algorithm on buffers whose
-    contents do not matter (what the layer autotuner compares)."""
+    contents do not matter (what the layer autotuner compares).  ``epilogue`` =
+    (scale, shift, residual, relu) flags of the fused epilogue the layer runs with."""
     engine.require_cuda(weights, source_masks, target_masks)
     weights = weights.detach().contiguous()
     sm, tm, order = _i32(source_masks), _i32(target_masks), _i32(kernel_map_order)
     S, T, O, c_in, c_out, sizes_host = _prepare(weights, sm, tm, kernel_map_sizes)
-    sources = torch.zeros((S, c_in), dtype=weights.dtype, device=weights.device)
-    stream = torch.cuda.current_stream(weights.device)
+    device = weights.device
+    sources = torch.zeros((S, c_in), dtype=weights.dtype, device=device)
+    scale = torch.ones(c_out, dtype=torch.float32, device=device) if epilogue[0] else None
+    shift = torch.zeros(c_out, dtype=torch.float32, device=device) if epilogue[1] else None
+    residual = torch.zeros((T, c_out), dtype=weights.dtype, device=device) if epilogue[2] else None
+    stream = torch.cuda.current_stream(device)
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record(stream)
     _forward(sources, weights, sm, tm, order, sizes_host, gather_tile_size, scatter_tile_size,
-             allow_shortcut_matmul, threshold, algorithm=algorithm, sub_tiles=sub_tiles)
+             allow_shortcut_matmul, threshold, scale, shift, residual, bool(epilogue[3]),
+             algorithm=algorithm, sub_tiles=sub_tiles)
     end.record(stream)
     end.synchronize()
     return begin.elapsed_time(end)
