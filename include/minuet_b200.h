@@ -89,7 +89,7 @@ typedef struct {
 /* Version of this interface; mn_version() returns the value the library was
  * built with.  A binding should refuse a library whose version differs from the
  * header it was written against: argument lists change between versions. */
-#define MN_ABI_VERSION 13
+#define MN_ABI_VERSION 14
 
 const char *mn_last_error(void);
 int mn_version(void);
@@ -317,10 +317,12 @@ size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, int64_t O, i
  * stable sort on the Gray-sequence rank of the bit-reversed word) sit in the same 128-row tiles and tiles can skip the offsets none of their rows has.
  * nbr_out and tile_bits_out are then in table order; the forward pass takes perm and
  * writes every output row at its own place.  perm_out NULL: table order = target order
- * (target_bits and ctrl are then not read). */
+ * (ctrl is then not read).  source_bits / target_bits (each may be NULL) let the build
+ * read only the mask entries that hold a pair instead of whole mask rows. */
 mn_status mn_build_neighbor_table(const int32_t *source_masks, const int32_t *target_masks,
                                   const int32_t *sizes_host, int64_t O, int64_t S, int64_t T,
-                                  const uint32_t *target_bits, int32_t *nbr_out,
+                                  const uint32_t *source_bits, const uint32_t *target_bits,
+                                  int32_t *nbr_out,
                                   uint32_t *tile_bits_out, int32_t *perm_out, int32_t *ctrl,
                                   void *ws, size_t ws_bytes, void *stream);
 

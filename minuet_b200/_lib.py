@@ -15,7 +15,7 @@ MN_F32, MN_F16, MN_BF16 = 0, 1, 2
 MN_MAX_NDIM = 4
 MN_MAX_OFFSETS = 128
 MN_CTRL_WORDS = 1024
-ABI_VERSION = 13         # must equal MN_ABI_VERSION of the header the library was built from
+ABI_VERSION = 14         # must equal MN_ABI_VERSION of the header the library was built from
 
 c_i32p = ctypes.c_void_p
 c_ptr = ctypes.c_void_p
@@ -85,7 +85,7 @@ PROTOTYPES = {
     "mn_implicit_supported": (c_int, [c_i64, c_i64, c_i64, c_int]),
     "mn_neighbor_table_workspace_bytes": (c_size, [c_ptr, c_i64, c_i64]),
     "mn_build_neighbor_table": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_ptr, c_ptr, c_ptr,
-                                        c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+                                        c_ptr, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
     "mn_implicit_workspace_bytes": (c_size, [c_i64, c_i64, c_i64]),
     "mn_sparse_convolution_forward_implicit": (c_int, [c_i64, c_i64, c_i64, c_i64, c_i64, c_int,
                                                        c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,

@@ -478,6 +478,22 @@ rank_to_source_kernel(const int32_t *__restrict__ source_masks, int64_t S, int O
   }
 }
 
+// the same from the sources' hit words: a source row reads only the mask entries of the
+// offsets it takes part in (E entries instead of O * S)
+__global__ void __launch_bounds__(256)
+rank_to_source_bits_kernel(const int32_t *__restrict__ source_masks,
+                           const uint32_t *__restrict__ source_bits, int64_t S,
+                           const __grid_constant__ CumSizes cs, int32_t *__restrict__ src_of_rank) {
+  const int64_t gsz = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < S; s += gsz) {
+    for (uint32_t rest = __ldg(source_bits + s); rest != 0u; rest &= rest - 1u) {
+      const int p = __ffs(rest) - 1;
+      const int m = __ldg(source_masks + (int64_t)p * S + s);
+      if (m >= 0) src_of_rank[cs.cum[p] + m] = (int32_t)s;
+    }
+  }
+}
+
 // nbr[p, r] = source row feeding target perm[r] (perm == NULL: target r) under mask row p
 // (or -1); bit p of tile_bits[r / 128] is set when any row of that 128-row tile has such a
 // source.  With the targets' hit words (`bits`) only the (tile, p) blocks whose bit is set
@@ -615,7 +631,8 @@ extern "C" size_t mn_neighbor_table_workspace_bytes(const int32_t *sizes_host, i
 extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
                                              const int32_t *target_masks,
                                              const int32_t *sizes_host, int64_t O, int64_t S,
-                                             int64_t T, const uint32_t *target_bits,
+                                             int64_t T, const uint32_t *source_bits,
+                                             const uint32_t *target_bits,
                                              int32_t *nbr_out, uint32_t *tile_bits_out,
                                              int32_t *perm_out, int32_t *ctrl, void *ws_ptr,
                                              size_t ws_bytes, void *stream) {
@@ -651,7 +668,14 @@ extern "C" mn_status mn_build_neighbor_table(const int32_t *source_masks,
     MN_CHECK_CUDA(cudaMemcpyAsync(perm_out, in_tmp ? vals_tmp : vals, (size_t)T * sizeof(int32_t),
                                   cudaMemcpyDeviceToDevice, st));
   }
-  if (S > 0) {
+  // a scattered 4-byte read costs a 32-byte sector: worth it while the pairs are fewer than
+  // an eighth of the mask entries
+  if (S > 0 && source_bits != nullptr && cs.cum[O] * 8 < O * S) {
+    const int blocks = (int)std::min<int64_t>(kNumSMs * 16, div_up(S, 256));
+    MN_LAUNCH("rank_to_source_bits_kernel", st,
+              rank_to_source_bits_kernel<<<blocks, 256, 0, st>>>(source_masks, source_bits, S, cs,
+                                                                  src_of_rank));
+  } else if (S > 0) {
     const dim3 grid((unsigned)std::min<int64_t>(kNumSMs * 4, div_up(S, 256)), (unsigned)O);
     MN_LAUNCH("rank_to_source_kernel", st,
               rank_to_source_kernel<<<grid, 256, 0, st>>>(source_masks, S, (int)O, cs, src_of_rank));

@@ -378,7 +378,9 @@ def neighbor_table(source_masks: torch.Tensor, target_masks: torch.Tensor,
     perm = torch.empty(T, dtype=torch.int32, device=device) if bits is not None else None
     ws = workspace(lib().mn_neighbor_table_workspace_bytes(np_ptr(sizes_host), O, T), device)
     _lib.check(lib().mn_build_neighbor_table(ptr(source_masks), ptr(target_masks),
-                                             np_ptr(sizes_host), O, S, T, ptr(bits), ptr(nbr),
+                                             np_ptr(sizes_host), O, S, T,
+                                             ptr(hit_bits(source_masks) if bits is not None else None),
+                                             ptr(bits), ptr(nbr),
                                              ptr(tile_bits), ptr(perm), ptr(control_block(device)),
                                              ptr(ws), ws.numel(), stream_ptr(device)),
                "build_neighbor_table")
